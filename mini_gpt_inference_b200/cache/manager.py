@@ -1,0 +1,212 @@
+"""Host-side cache manager: page tables per request and per layer group, state slots.
+
+It owns no tensors.  Layers with equal needs (``PagedKVSpec``) form a group; each group
+has a page pool of its own and every request has one block table per group, shared by
+the group's layers — the same page id indexes every layer's storage, as in the
+reference (src/minigpt_infer/cache/paged.py:122-123, 154-155).  Pages are given back
+when a request is released (src/minigpt_infer/cache/paged.py:79-81) or, in a group with
+a window, as soon as no later query can read them.  A request also holds one slot of
+the state pool from admission to release, whether or not any layer keeps state.
+
+Growth is asked for in two halves so that a caller can back out: ``reserve`` takes the
+pages a request needs to reach a length (all groups or none), ``advance`` records that
+the tokens are now in the cache.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+from .page_pool import PagePool, PoolError, SlotPool
+from .spec import FixedStateSpec, PagedKVSpec
+
+NO_PAGE = -1
+
+
+class CacheFullError(RuntimeError):
+    """Not enough free pages (or slots) for what was asked."""
+
+
+@dataclass
+class CacheGroup:
+    spec: PagedKVSpec
+    layers: list[int]
+    pool: PagePool
+
+
+@dataclass
+class RequestCache:
+    request_id: str
+    state_slot: int
+    length: int = 0                                   # tokens in the cache
+    tables: list[list[int]] = field(default_factory=list)   # per group: page id per page index
+
+
+class CacheManager:
+    def __init__(self, layer_specs, page_tokens: int, num_pages: int, max_requests: int) -> None:
+        if page_tokens <= 0:
+            raise ValueError("page_tokens must be positive")
+        self.page_tokens = page_tokens
+        self.num_pages = num_pages
+        self.max_requests = max_requests
+        self.groups: list[CacheGroup] = []
+        self.group_of_layer: dict[int, int] = {}
+        self.state_layers: dict[int, FixedStateSpec] = {}
+        for layer, spec in enumerate(layer_specs):
+            if spec is None:
+                continue
+            if isinstance(spec, FixedStateSpec):
+                self.state_layers[layer] = spec
+            elif isinstance(spec, PagedKVSpec):
+                for g, group in enumerate(self.groups):
+                    if group.spec == spec:
+                        group.layers.append(layer)
+                        self.group_of_layer[layer] = g
+                        break
+                else:
+                    self.group_of_layer[layer] = len(self.groups)
+                    self.groups.append(CacheGroup(spec, [layer], PagePool(num_pages)))
+            else:
+                raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
+        self.slots = SlotPool(max_requests)
+        self.requests: dict[str, RequestCache] = {}
+
+    # ---- sizes -------------------------------------------------------------------
+    def pages_for(self, num_tokens: int) -> int:
+        return (num_tokens + self.page_tokens - 1) // self.page_tokens
+
+    def max_pages_per_request(self, max_tokens: int) -> int:
+        return max(1, self.pages_for(max_tokens))
+
+    def _first_live_page(self, group: CacheGroup, length: int) -> int:
+        """Index of the first page that a query at position >= length may still read."""
+        if group.spec.window is None:
+            return 0
+        first_key = max(0, length - group.spec.window + 1)
+        return first_key // self.page_tokens
+
+    def _missing(self, req: RequestCache, new_length: int) -> list[int]:
+        """Pages each group still needs so that positions < new_length have a page."""
+        need = []
+        for g, group in enumerate(self.groups):
+            have = len(req.tables[g])
+            need.append(max(0, self.pages_for(new_length) - have))
+        return need
+
+    # ---- life of a request ----------------------------------------------------------
+    def admit(self, request_id: str) -> RequestCache:
+        if request_id in self.requests:
+            raise PoolError(f"request {request_id!r} is already admitted")
+        if self.slots.num_free == 0:
+            raise CacheFullError("no state slot free")
+        req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups])
+        self.requests[request_id] = req
+        return req
+
+    def has(self, request_id: str) -> bool:
+        return request_id in self.requests
+
+    def get(self, request_id: str) -> RequestCache:
+        try:
+            return self.requests[request_id]
+        except KeyError:
+            raise PoolError(f"request {request_id!r} is not admitted") from None
+
+    def pages_needed(self, request_id: str | None, new_length: int) -> list[int]:
+        """Per group, pages that would have to be taken to reach ``new_length``."""
+        if request_id is None or request_id not in self.requests:
+            return [self.pages_for(new_length) for _ in self.groups]
+        return self._missing(self.requests[request_id], new_length)
+
+    def can_reserve(self, request_id: str | None, new_length: int) -> bool:
+        need = self.pages_needed(request_id, new_length)
+        return all(n <= group.pool.num_free for n, group in zip(need, self.groups))
+
+    def reserve(self, request_id: str, new_length: int) -> bool:
+        """Take the pages needed to hold ``new_length`` tokens.  All groups or none:
+        returns False and changes nothing if any group is short."""
+        req = self.get(request_id)
+        need = self._missing(req, new_length)
+        if any(n > group.pool.num_free for n, group in zip(need, self.groups)):
+            return False
+        for g, (n, group) in enumerate(zip(need, self.groups)):
+            req.tables[g].extend(group.pool.take(n))
+        return True
+
+    def advance(self, request_id: str, new_length: int) -> None:
+        """Tokens up to ``new_length`` are written.  Gives back pages a window has passed."""
+        req = self.get(request_id)
+        if new_length < req.length:
+            raise PoolError("a request's cache cannot shrink; release and recompute instead")
+        for g in range(len(self.groups)):
+            if self.pages_for(new_length) > len(req.tables[g]):
+                raise PoolError(f"request {request_id!r} advanced past its reserved pages")
+        req.length = new_length
+        for g, group in enumerate(self.groups):
+            first = self._first_live_page(group, new_length)
+            table = req.tables[g]
+            passed = [p for p in table[:first] if p != NO_PAGE]
+            if passed:
+                group.pool.give_back(passed)
+                for i in range(min(first, len(table))):
+                    table[i] = NO_PAGE
+
+    def release(self, request_id: str) -> None:
+        req = self.get(request_id)
+        for g, group in enumerate(self.groups):
+            group.pool.give_back([p for p in req.tables[g] if p != NO_PAGE])
+            req.tables[g] = []
+        self.slots.give_back([req.state_slot])
+        del self.requests[request_id]
+
+    # ---- what a step needs ------------------------------------------------------------
+    def block_table(self, request_id: str, group: int) -> list[int]:
+        return self.get(request_id).tables[group]
+
+    def slot_of(self, request_id: str, group: int, position: int) -> int:
+        """Flat index of a position's row in the group's storage."""
+        page = self.get(request_id).tables[group][position // self.page_tokens]
+        if page == NO_PAGE:
+            raise PoolError(f"position {position} of {request_id!r} was given back already")
+        return page * self.page_tokens + position % self.page_tokens
+
+    # ---- accounting ---------------------------------------------------------------------
+    def num_free_pages(self, group: int = 0) -> int:
+        return self.groups[group].pool.num_free if self.groups else 0
+
+    def stats(self) -> dict[str, int]:
+        """As src/minigpt_infer/cache/paged.py:83-94, summed over groups."""
+        held = sum(sum(1 for p in t if p != NO_PAGE) for r in self.requests.values()
+                   for t in r.tables)
+        used_tokens = 0
+        for r in self.requests.values():
+            for g, group in enumerate(self.groups):
+                first = self._first_live_page(group, r.length) * self.page_tokens
+                used_tokens += max(0, r.length - first)
+        return {
+            "free_blocks": sum(g.pool.num_free for g in self.groups),
+            "allocated_blocks": sum(g.pool.num_used for g in self.groups),
+            "internal_fragmentation_slots": held * self.page_tokens - used_tokens,
+            "free_state_slots": self.slots.num_free,
+            "live_requests": len(self.requests),
+        }
+
+    def check(self) -> None:
+        """Every page is either free or in exactly one table; the same for slots."""
+        for g, group in enumerate(self.groups):
+            group.pool.check()
+            seen: set[int] = set()
+            for r in self.requests.values():
+                for p in r.tables[g]:
+                    if p == NO_PAGE:
+                        continue
+                    if p in seen:
+                        raise PoolError(f"page {p} of group {g} is held twice")
+                    seen.add(p)
+            if len(seen) != group.pool.num_used:
+                raise PoolError(
+                    f"group {g}: {group.pool.num_used} pages out, {len(seen)} in tables")
+        self.slots.check()
+        slots = [r.state_slot for r in self.requests.values()]
+        if len(set(slots)) != len(slots) or len(slots) != self.slots.num_used:
+            raise PoolError("state slots and requests disagree")

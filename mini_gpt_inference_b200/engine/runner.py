@@ -1,0 +1,203 @@
+"""The step function: run a batch of (request, its next tokens) from the cache.
+
+``ModelRunner.step(entries)`` takes, per request, the tokens that follow what the cache
+already holds for it — a portion of a prompt of any length, or one decoded token — and
+the places among them whose logits are wanted.  All entries run as one flat batch; new
+keys and values go to the request's pages; logits come back as ``[wanted, vocab]``
+32-bit, in the order of the entries and of their ``want`` lists.
+
+The reference's step is either one whole-prompt forward per admitted request or one
+rectangular single-token forward over all running requests
+(src/minigpt_infer/engine/engine.py:101-118, 210-283); its index tensors are rebuilt
+from Python lists and copied every step.  Here the step's integers are packed into one
+pinned buffer and cross to the device in one copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import NO_PAGE, CacheFullError, CacheManager
+from ..cache.storage import CacheStorage
+from ..parts.context import StepContext
+from ..parts.model import DecoderModel
+
+
+class StepError(ValueError):
+    """A step that cannot run: bad token ids, positions past the table, empty entry."""
+
+
+@dataclass
+class StepEntry:
+    request_id: str
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
+                 ops, act_dtype: torch.dtype, device, max_context: int | None = None) -> None:
+        self.model = model
+        self.manager = manager
+        self.storage = storage
+        self.ops = ops
+        self.act_dtype = act_dtype
+        self.device = torch.device(device)
+        self.vocab_size = model.spec.vocab_size
+        limit = model.max_positions
+        self.max_context = limit if max_context is None else (
+            max_context if limit is None else min(limit, max_context))
+        if self.max_context is None:
+            self.max_context = manager.num_pages * manager.page_tokens
+        self.max_pages = manager.max_pages_per_request(self.max_context)
+        self._pinned = None
+        self._pinned_size = 0
+
+    # ---- requests ---------------------------------------------------------------------
+    def length_of(self, request_id: str) -> int:
+        return self.manager.get(request_id).length if self.manager.has(request_id) else 0
+
+    def finish(self, request_id: str) -> None:
+        """Give back everything the request holds."""
+        if self.manager.has(request_id):
+            self.manager.release(request_id)
+
+    # ---- one step -----------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise StepError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"request {e.request_id!r} brings no tokens")
+            for t in e.tokens:
+                if not (0 <= int(t) < self.vocab_size):
+                    raise StepError(f"token id {t} of request {e.request_id!r} is outside "
+                                    f"the vocabulary (0..{self.vocab_size - 1})")
+            for w in e.want:
+                if not (0 <= int(w) < n):
+                    raise StepError(f"request {e.request_id!r} wants logits at {w}, "
+                                    f"but brings {n} tokens")
+            end = self.length_of(e.request_id) + n
+            if end > self.max_context:
+                raise StepError(
+                    f"request {e.request_id!r} would reach {end} tokens; the model's "
+                    f"position table ends at {self.max_context}")
+
+    def _reserve(self, entries: Sequence[StepEntry]) -> None:
+        m = self.manager
+        need = [0] * len(m.groups)
+        new_requests = 0
+        for e in entries:
+            known = m.has(e.request_id)
+            new_requests += 0 if known else 1
+            end = self.length_of(e.request_id) + len(e.tokens)
+            for g, n in enumerate(m.pages_needed(e.request_id if known else None, end)):
+                need[g] += n
+        for g, n in enumerate(need):
+            if n > m.groups[g].pool.num_free:
+                raise CacheFullError(
+                    f"step needs {n} new pages in cache group {g}, {m.groups[g].pool.num_free} free")
+        if new_requests > m.slots.num_free:
+            raise CacheFullError("step admits more requests than there are free state slots")
+        for e in entries:
+            if not m.has(e.request_id):
+                m.admit(e.request_id)
+            ok = m.reserve(e.request_id, m.get(e.request_id).length + len(e.tokens))
+            assert ok, "pages were counted a moment ago"
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Pack the step's integers, copy them to the device once, and describe the batch."""
+        m = self.manager
+        n_groups = len(m.groups)
+        R = len(entries)
+        N = sum(len(e.tokens) for e in entries)
+        W = sum(len(e.want) for e in entries)
+        P = self.max_pages
+        # layout of the packed int32 buffer
+        sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups
+        offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        total = int(offsets[-1])
+        buf = np.empty(max(total, 1), dtype=np.int32)
+
+        def seg(i):
+            return buf[offsets[i]: offsets[i + 1]]
+
+        token_ids, positions, token_request = seg(0), seg(1), seg(2)
+        q_start, q_len, ctx_before, state_slot, logit_rows = seg(3), seg(4), seg(5), seg(6), seg(7)
+        tables = [seg(8 + g).reshape(R, P) for g in range(n_groups)]
+        slots = [seg(8 + n_groups + g) for g in range(n_groups)]
+        row = 0
+        w = 0
+        pt = m.page_tokens
+        for r, e in enumerate(entries):
+            req = m.get(e.request_id)
+            n = len(e.tokens)
+            q_start[r], q_len[r], ctx_before[r], state_slot[r] = row, n, req.length, req.state_slot
+            token_ids[row: row + n] = np.asarray(e.tokens, dtype=np.int32)
+            pos = np.arange(req.length, req.length + n, dtype=np.int32)
+            positions[row: row + n] = pos
+            token_request[row: row + n] = r
+            for g in range(n_groups):
+                table = np.asarray(req.tables[g], dtype=np.int32)
+                tables[g][r, :len(table)] = table
+                tables[g][r, len(table):] = NO_PAGE
+                pages = table[pos // pt]
+                if (pages == NO_PAGE).any():
+                    raise StepError(f"request {e.request_id!r} writes to a page it gave back")
+                slots[g][row: row + n] = pages * pt + pos % pt
+            for k in e.want:
+                logit_rows[w] = row + int(k)
+                w += 1
+            row += n
+
+        dev = self._to_device(buf, total)
+
+        def dseg(i):
+            return dev[int(offsets[i]): int(offsets[i + 1])]
+
+        host_q_len = [len(e.tokens) for e in entries]
+        host_ctx = [m.get(e.request_id).length for e in entries]
+        return StepContext(
+            ops=self.ops, act_dtype=self.act_dtype, num_tokens=N, num_requests=R,
+            token_ids=dseg(0), positions=dseg(1), token_request=dseg(2),
+            req_q_start=dseg(3), req_q_len=dseg(4), req_ctx_before=dseg(5),
+            req_state_slot=dseg(6), logit_rows=dseg(7),
+            block_tables=[dseg(8 + g).view(R, P) for g in range(n_groups)],
+            slot_mapping=[dseg(8 + n_groups + g) for g in range(n_groups)],
+            host_q_len=host_q_len, host_ctx_before=host_ctx,
+            host_state_slot=[m.get(e.request_id).state_slot for e in entries],
+            max_q_len=max(host_q_len), max_ctx_after=max(a + b for a, b in zip(host_q_len, host_ctx)),
+            decode_only=all(n == 1 for n in host_q_len), storage=self.storage)
+
+    def _to_device(self, buf: np.ndarray, total: int) -> torch.Tensor:
+        if self.device.type != "cuda":
+            return torch.from_numpy(buf[:total].copy())
+        if self._pinned is None or self._pinned_size < total:
+            self._pinned_size = max(total, 2 * self._pinned_size, 4096)
+            self._pinned = torch.empty(self._pinned_size, dtype=torch.int32, pin_memory=True)
+        else:
+            # The last step's copy out of the pinned buffer must be over before it is reused.
+            torch.cuda.current_stream(self.device).synchronize()
+        self._pinned[:total].numpy()[:] = buf[:total]
+        return self._pinned[:total].to(self.device, non_blocking=True)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        """Run the entries as one batch.  Returns ``[wanted, vocab]`` float32 logits on the
+        device (None if nothing was wanted)."""
+        entries = list(entries)
+        if not entries:
+            return None
+        self._validate(entries)
+        self._reserve(entries)
+        ctx = self.build_context(entries)
+        logits = self.model.forward(ctx)
+        for e in entries:
+            self.manager.advance(e.request_id, self.manager.get(e.request_id).length + len(e.tokens))
+        return logits

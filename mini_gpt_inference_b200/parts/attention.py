@@ -1,0 +1,71 @@
+"""Causal multi-head attention over the paged cache.
+
+One fused projection gives q, k, v in that order, head ``h`` in columns
+``[h*D, (h+1)*D)`` of each (src/minigpt_infer/model.py:43, 50-53).  New keys and values
+are written to their pages, then every query attends to the keys of its own request at
+positions up to its own (scale ``1/sqrt(D)`` unless given; softmax in 32-bit) — always
+from the pages, whether a key arrived in this step or an earlier one, so that the result
+does not depend on how the tokens were cut into steps.  The reference gathers the pages
+into a dense tensor and calls a library attention (src/minigpt_infer/model.py:55-87,
+src/minigpt_infer/cache/paged.py:139-165).  The output projection adds into the
+residual stream (src/minigpt_infer/model.py:90, 113).
+
+Heads may share keys (``n_kv_head`` divides ``n_head``) and may look back only
+``window`` positions; this architecture uses neither, the part takes them as parameters.
+"""
+
+from __future__ import annotations
+
+import math
+
+from ..cache.spec import PagedKVSpec
+from .base import Mixer, register_mixer
+from .spec import TensorSpec
+
+
+@register_mixer("causal_attention")
+class CausalAttention(Mixer):
+    def __init__(self, prefix: str, width: int, n_head: int, head_dim: int, bias: bool,
+                 n_kv_head: int | None = None, scale: float | None = None,
+                 window: int | None = None, position=None) -> None:
+        super().__init__(prefix)
+        self.width, self.n_head, self.head_dim = width, n_head, head_dim
+        self.n_kv_head = n_head if n_kv_head is None else n_kv_head
+        if self.n_head % self.n_kv_head != 0:
+            raise ValueError(f"n_head {n_head} is not a multiple of n_kv_head {self.n_kv_head}")
+        self.has_bias = bool(bias)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.window = window
+        self.position = position
+        self.qkv_weight = self.qkv_bias = self.proj_weight = self.proj_bias = None
+
+    @property
+    def qkv_width(self) -> int:
+        return (self.n_head + 2 * self.n_kv_head) * self.head_dim
+
+    def tensor_specs(self):
+        p = self.prefix
+        specs = {
+            p + "qkv.weight": TensorSpec((self.qkv_width, self.width), "matrix"),
+            p + "proj.weight": TensorSpec((self.width, self.n_head * self.head_dim), "matrix",
+                                          "residual_proj"),
+        }
+        if self.has_bias:
+            specs[p + "qkv.bias"] = TensorSpec((self.qkv_width,), "vector", "bias")
+            specs[p + "proj.bias"] = TensorSpec((self.width,), "vector", "bias")
+        return specs
+
+    def cache_spec(self):
+        return PagedKVSpec(self.n_kv_head, self.head_dim, self.window)
+
+    def forward(self, ctx, cache, y, residual32) -> None:
+        ops = ctx.ops
+        qkv = ops.linear(y, self.qkv_weight, self.qkv_bias, "none", ctx.act_dtype)
+        if self.position is not None:
+            self.position.rotate(ctx, qkv, self.n_head, self.n_kv_head, self.head_dim)
+        if cache.writes:
+            ops.kv_store(qkv, self.n_head, self.n_kv_head, self.head_dim, cache,
+                         ctx.slot_mapping[cache.group])
+        out = ops.paged_attention(qkv, self.n_head, self.n_kv_head, self.head_dim, self.scale,
+                                  cache, ctx)
+        ops.linear_residual(out, self.proj_weight, self.proj_bias, residual32)

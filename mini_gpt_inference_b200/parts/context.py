@@ -1,0 +1,45 @@
+"""The batch one step runs on, as the parts see it.
+
+Tokens of all requests lie flat, request after request (``N`` rows).  A request brings
+``q_len`` new tokens that follow ``ctx_before`` tokens already in the cache; a single
+decoded token and a portion of a prompt differ in nothing but ``q_len``.  The reference
+has rectangular ``(B, T)`` batches that are either all prompts or all single tokens
+(src/minigpt_infer/batch.py:19-64); this flat form is what lets one step mix them.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+
+
+@dataclass
+class StepContext:
+    ops: Any                              # the kernel set the parts call
+    act_dtype: torch.dtype                # compute dtype between norm and projection
+    num_tokens: int
+    num_requests: int
+    # device, int32
+    token_ids: torch.Tensor               # [N]
+    positions: torch.Tensor               # [N] absolute position of each token
+    token_request: torch.Tensor           # [N] index of the token's request in this batch
+    req_q_start: torch.Tensor             # [R] first row of the request
+    req_q_len: torch.Tensor               # [R] new tokens of the request
+    req_ctx_before: torch.Tensor          # [R] tokens in the cache before this step
+    req_state_slot: torch.Tensor          # [R] slot of the state pool
+    block_tables: list[torch.Tensor]      # per cache group [R, max_pages], -1 = no page
+    slot_mapping: list[torch.Tensor]      # per cache group [N] flat row of each new token
+    logit_rows: torch.Tensor              # [W] rows whose logits are wanted
+    # host mirrors for parts that plan on the host
+    host_q_len: list[int] = field(default_factory=list)
+    host_ctx_before: list[int] = field(default_factory=list)
+    host_state_slot: list[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_ctx_after: int = 0                # longest context once this step's tokens are in
+    decode_only: bool = False             # every request brings exactly one token
+    storage: Any = None                   # cache.storage.CacheStorage
+
+    def cache_view(self, cache_layer: int, writes: bool = True):
+        return self.storage.layer_view(cache_layer, writes) if self.storage is not None else None
