@@ -1,0 +1,60 @@
+// Shared helpers of the sm_100a kernel library: error reporting, type conversion, reductions.
+//
+// Every exported function is plain C (`extern "C"`), takes raw device pointers and a
+// stream, launches asynchronously and returns 0, or a negative code after storing a
+// message that `mg_last_error()` returns.  Nothing here allocates device memory.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define MG_OK 0
+#define MG_ERR_ARG -1
+#define MG_ERR_CUDA -2
+#define MG_ERR_UNSUPPORTED -3
+
+#define MG_API extern "C" __attribute__((visibility("default")))
+
+int mg_set_error(int code, const char* fmt, ...);
+
+#define MG_REQUIRE(cond, ...)                                   \
+    do {                                                        \
+        if (!(cond)) return mg_set_error(MG_ERR_ARG, __VA_ARGS__); \
+    } while (0)
+
+#define MG_CHECK_LAUNCH(name)                                                       \
+    do {                                                                            \
+        cudaError_t e_ = cudaGetLastError();                                        \
+        if (e_ != cudaSuccess)                                                      \
+            return mg_set_error(MG_ERR_CUDA, "%s: %s", name, cudaGetErrorString(e_)); \
+    } while (0)
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// tanh-GELU evaluated in 32-bit: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))).
+__device__ __forceinline__ float gelu_tanh(float u) {
+    const float k = 0.7978845608028654f;  // sqrt(2/pi)
+    return 0.5f * u * (1.0f + tanhf(k * (u + 0.044715f * u * u * u)));
+}
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

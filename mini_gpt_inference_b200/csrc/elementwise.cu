@@ -1,0 +1,133 @@
+// Row-wise kernels: embedding with position add, LayerNorm, row gather, KV page write.
+#include "common.cuh"
+
+// ---- embedding + learned position add ---------------------------------------------------
+// x[n, :] = tok_emb[id[n], :] + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
+                             const TW* __restrict__ tok, const TW* __restrict__ ptab,
+                             float* __restrict__ out, int width) {
+    const int n = blockIdx.x;
+    const TW* trow = tok + (size_t)ids[n] * width;
+    const TW* prow = ptab ? ptab + (size_t)pos[n] * width : nullptr;
+    float* orow = out + (size_t)n * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_float(trow[c]);
+        if (prow) v += to_float(prow[c]);
+        orow[c] = v;
+    }
+}
+
+MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void* ptab, float* out,
+                    int n_tokens, int width, int weights_bf16, void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && width > 0, "embed: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    int threads = width >= 256 ? 256 : 128;
+    if (weights_bf16)
+        embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, pos, (const bf16*)tok, (const bf16*)ptab, out, width);
+    else
+        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)tok, (const float*)ptab, out, width);
+    MG_CHECK_LAUNCH("embed");
+    return MG_OK;
+}
+
+// ---- LayerNorm -----------------------------------------------------------------------------
+// One warp per row.  Mean, then the biased variance of the centred values, then the affine
+// map; all in 32-bit.  y = (x - mean) * rsqrt(var + eps) * gain (+ shift).
+template <typename TOut>
+__global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
+                                 const float* __restrict__ shift, TOut* __restrict__ y,
+                                 int rows, int width, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (row >= rows) return;
+    const float* xr = x + (size_t)row * width;
+    float sum = 0.f;
+    for (int c = lane; c < width; c += 32) sum += xr[c];
+    const float mean = warp_sum(sum) / (float)width;
+    float sq = 0.f;
+    for (int c = lane; c < width; c += 32) {
+        float d = xr[c] - mean;
+        sq += d * d;
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    TOut* yr = y + (size_t)row * width;
+    for (int c = lane; c < width; c += 32) {
+        float v = (xr[c] - mean) * rstd * gain[c];
+        if (shift) v += shift[c];
+        yr[c] = from_float<TOut>(v);
+    }
+}
+
+MG_API int mg_layernorm(const float* x, const float* gain, const float* shift, void* y, int rows,
+                        int width, float eps, int out_bf16, void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && width > 0, "layernorm: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    dim3 grid(ceil_div(rows, warps)), block(32 * warps);
+    if (out_bf16)
+        layernorm_kernel<bf16><<<grid, block, 0, s>>>(x, gain, shift, (bf16*)y, rows, width, eps);
+    else
+        layernorm_kernel<float><<<grid, block, 0, s>>>(x, gain, shift, (float*)y, rows, width, eps);
+    MG_CHECK_LAUNCH("layernorm");
+    return MG_OK;
+}
+
+// ---- row gather (32-bit) ----------------------------------------------------------------------
+__global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                                   float* __restrict__ out, int width) {
+    const float* src = x + (size_t)rows[blockIdx.x] * width;
+    float* dst = out + (size_t)blockIdx.x * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+}
+
+MG_API int mg_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
+                          void* stream) {
+    if (n_rows == 0) return MG_OK;
+    MG_REQUIRE(n_rows > 0 && width > 0, "gather_rows: bad sizes");
+    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>(x, rows, out, width);
+    MG_CHECK_LAUNCH("gather_rows");
+    return MG_OK;
+}
+
+// ---- write new keys and values into their pages --------------------------------------------------
+// qkv row layout: [q: H*D | k: Hkv*D | v: Hkv*D].  Pages: [page, kv head, token in page, D].
+// slot = page * page_tokens + token in page; a negative slot is skipped (padding rows).
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ qkv, const int* __restrict__ slots,
+                                T* __restrict__ k_pages, T* __restrict__ v_pages, int qkv_width,
+                                int q_width, int n_kv_head, int head_dim, int page_tokens) {
+    const int n = blockIdx.x;
+    const int slot = slots[n];
+    if (slot < 0) return;
+    const int page = slot / page_tokens, off = slot - page * page_tokens;
+    const int kv_width = n_kv_head * head_dim;
+    const T* krow = qkv + (size_t)n * qkv_width + q_width;
+    const T* vrow = krow + kv_width;
+    for (int i = threadIdx.x; i < kv_width; i += blockDim.x) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        const size_t dst = (((size_t)page * n_kv_head + h) * page_tokens + off) * head_dim + d;
+        k_pages[dst] = krow[i];
+        v_pages[dst] = vrow[i];
+    }
+}
+
+MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v_pages, int n_tokens,
+                       int n_head, int n_kv_head, int head_dim, int page_tokens, int is_bf16,
+                       void* stream) {
+    if (n_tokens == 0) return MG_OK;
+    MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && head_dim > 0 && page_tokens > 0,
+               "kv_store: bad sizes");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int q_width = n_head * head_dim, qkv_width = (n_head + 2 * n_kv_head) * head_dim;
+    if (is_bf16)
+        kv_store_kernel<bf16><<<n_tokens, 128, 0, s>>>((const bf16*)qkv, slots, (bf16*)k_pages, (bf16*)v_pages,
+                                                     qkv_width, q_width, n_kv_head, head_dim, page_tokens);
+    else
+        kv_store_kernel<float><<<n_tokens, 128, 0, s>>>((const float*)qkv, slots, (float*)k_pages, (float*)v_pages,
+                                                      qkv_width, q_width, n_kv_head, head_dim, page_tokens);
+    MG_CHECK_LAUNCH("kv_store");
+    return MG_OK;
+}

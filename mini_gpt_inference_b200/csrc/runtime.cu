@@ -1,0 +1,32 @@
+// Error message store and device queries of the kernel library.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int mg_set_error(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+MG_API const char* mg_last_error() { return g_error; }
+
+// Compute capability of `device` as major * 10 + minor, or a negative error code.
+MG_API int mg_device_arch(int device) {
+    int major = 0, minor = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, device) != cudaSuccess)
+        return mg_set_error(MG_ERR_CUDA, "cannot query device %d", device);
+    return major * 10 + minor;
+}
+
+MG_API int mg_set_device(int device) {
+    cudaError_t e = cudaSetDevice(device);
+    if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+    return MG_OK;
+}

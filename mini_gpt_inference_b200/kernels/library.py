@@ -1,0 +1,74 @@
+"""Load the kernel library and declare its C functions.
+
+The library is the only way the engine computes: if it cannot be built or loaded, or
+if the device is not sm_100, importing the kernel set fails with a clear error.  There
+is no fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+from .build import library_path
+
+_P = c_void_p
+_I = c_int
+_F = c_float
+
+_SIGNATURES = {
+    "mg_device_arch": [_I],
+    "mg_set_device": [_I],
+    "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
+    "mg_gather_rows": [_P, _P, _P, _I, _I, _P],
+    "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "mg_argmax": [_P, _P, _I, _I, _I, _P],
+}
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+_lib = None
+
+
+def load(verbose: bool = True):
+    """The loaded library (built first if needed), with argument types declared."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = library_path(verbose=verbose)
+    try:
+        lib = ctypes.CDLL(str(path))
+    except OSError as exc:
+        raise KernelLibraryError(f"cannot load the kernel library {path}: {exc}") from exc
+    lib.mg_last_error.restype = ctypes.c_char_p
+    lib.mg_last_error.argtypes = []
+    for name, argtypes in _SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            raise KernelLibraryError(f"the kernel library lacks {name}; rebuild it") from None
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    _lib = lib
+    return lib
+
+
+def declare(name: str, argtypes) -> None:
+    """Declare a further function (used by kernels added after the table above)."""
+    _SIGNATURES[name] = argtypes
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = c_int
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = load().mg_last_error().decode(errors="replace")
+        raise KernelLibraryError(f"{what} failed ({code}): {msg}")

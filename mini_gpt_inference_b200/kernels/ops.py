@@ -1,0 +1,180 @@
+"""The CUDA kernel set: what the parts call.
+
+Each method checks its tensors (device, dtype, contiguity, shapes), allocates the output
+with torch and launches a hand-written kernel of the library on torch's current stream.
+torch is the tensor container and allocator here, nothing more: no torch operator
+computes anything on this path.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .library import KernelLibraryError, check
+
+EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+class CudaOps:
+    name = "cuda-sm100a"
+
+    def __init__(self, device="cuda:0") -> None:
+        if not torch.cuda.is_available():
+            raise KernelLibraryError(
+                "no CUDA device: this engine runs only on its sm_100a kernels and has no "
+                "CPU path")
+        self.device = torch.device(device)
+        self.index = self.device.index or 0
+        self.lib = library.load()
+        torch.cuda.init()
+        with torch.cuda.device(self.index):
+            torch.empty(1, device=self.device)      # make sure the primary context exists
+        arch = self.lib.mg_device_arch(self.index)
+        if arch < 0:
+            check(arch, "device query")
+        if arch // 10 != 10:
+            raise KernelLibraryError(
+                f"device {self.index} has compute capability {arch / 10:.1f}; the kernels "
+                "are built for sm_100a (NVIDIA B200) only")
+        check(self.lib.mg_set_device(self.index), "set device")
+
+    # ---- helpers --------------------------------------------------------------------------
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def _want(self, t, dtype, name, dims=None):
+        if t.device != self.device:
+            raise KernelLibraryError(f"{name}: tensor on {t.device}, kernels run on {self.device}")
+        if dtype is not None and t.dtype != dtype:
+            raise KernelLibraryError(f"{name}: dtype {t.dtype}, expected {dtype}")
+        if not t.is_contiguous():
+            raise KernelLibraryError(f"{name}: tensor must be contiguous")
+        if dims is not None and t.dim() != dims:
+            raise KernelLibraryError(f"{name}: expected {dims} dims, got shape {tuple(t.shape)}")
+        return t
+
+    @staticmethod
+    def _is_bf16(t) -> int:
+        if t.dtype == torch.bfloat16:
+            return 1
+        if t.dtype == torch.float32:
+            return 0
+        raise KernelLibraryError(f"dtype {t.dtype} is neither bfloat16 nor float32")
+
+    # ---- embedding and norms --------------------------------------------------------------------
+    def embed(self, token_ids, positions, tok_emb, pos_table):
+        self._want(token_ids, torch.int32, "token_ids", 1)
+        self._want(positions, torch.int32, "positions", 1)
+        self._want(tok_emb, None, "tok_emb", 2)
+        if pos_table is not None:
+            self._want(pos_table, tok_emb.dtype, "pos_table", 2)
+            if pos_table.shape[1] != tok_emb.shape[1]:
+                raise KernelLibraryError("embed: position table and embedding differ in width")
+        n, width = token_ids.numel(), tok_emb.shape[1]
+        out = torch.empty((n, width), dtype=torch.float32, device=self.device)
+        check(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
+                                _ptr(out), n, width, self._is_bf16(tok_emb), self._stream()),
+              "embed")
+        return out
+
+    def layernorm(self, x32, gain, shift, eps, out_dtype):
+        self._want(x32, torch.float32, "layernorm input", 2)
+        self._want(gain, torch.float32, "layernorm gain", 1)
+        if shift is not None:
+            self._want(shift, torch.float32, "layernorm shift", 1)
+        rows, width = x32.shape
+        if gain.numel() != width:
+            raise KernelLibraryError("layernorm: gain does not match the width")
+        out = torch.empty((rows, width), dtype=out_dtype, device=self.device)
+        check(self.lib.mg_layernorm(_ptr(x32), _ptr(gain), _ptr(shift), _ptr(out), rows, width,
+                                    float(eps), self._is_bf16(out), self._stream()), "layernorm")
+        return out
+
+    def gather_rows(self, x32, rows):
+        self._want(x32, torch.float32, "gather input", 2)
+        self._want(rows, torch.int32, "rows", 1)
+        out = torch.empty((rows.numel(), x32.shape[1]), dtype=torch.float32, device=self.device)
+        check(self.lib.mg_gather_rows(_ptr(x32), _ptr(rows), _ptr(out), rows.numel(), x32.shape[1],
+                                      self._stream()), "gather_rows")
+        return out
+
+    # ---- projections ----------------------------------------------------------------------------
+    def _linear(self, x, weight, bias, epilogue, out, residual):
+        self._want(x, None, "linear input", 2)
+        self._want(weight, x.dtype, "linear weight", 2)
+        if bias is not None:
+            self._want(bias, torch.float32, "linear bias", 1)
+        m, k = x.shape
+        n = weight.shape[0]
+        if weight.shape[1] != k or (bias is not None and bias.numel() != n):
+            raise KernelLibraryError(
+                f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
+        out_bf16 = self._is_bf16(out) if out is not None else 0
+        check(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                      m, n, k, epilogue, self._is_bf16(x), out_bf16, self._stream()),
+              "linear")
+
+    def linear(self, x, weight, bias, activation, out_dtype):
+        if activation not in ("none", "gelu_tanh"):
+            raise KernelLibraryError(f"linear: no epilogue for activation {activation!r}")
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
+        self._linear(x, weight, bias, EPILOGUES[activation], out, None)
+        return out
+
+    def linear_residual(self, x, weight, bias, residual32):
+        self._want(residual32, torch.float32, "residual", 2)
+        if residual32.shape != (x.shape[0], weight.shape[0]):
+            raise KernelLibraryError("linear_residual: residual has the wrong shape")
+        self._linear(x, weight, bias, EPILOGUES["residual"], None, residual32)
+
+    def logits(self, y, tok_emb):
+        return self.linear(y, tok_emb, None, "none", torch.float32)
+
+    # ---- attention ------------------------------------------------------------------------------
+    def kv_store(self, qkv, n_head, n_kv_head, head_dim, cache, slot_mapping):
+        self._want(qkv, cache.k_pages.dtype, "qkv", 2)
+        self._want(slot_mapping, torch.int32, "slot_mapping", 1)
+        self._want(cache.k_pages, None, "k_pages", 4)
+        self._want(cache.v_pages, cache.k_pages.dtype, "v_pages", 4)
+        if qkv.shape[1] != (n_head + 2 * n_kv_head) * head_dim:
+            raise KernelLibraryError("kv_store: qkv width does not match the head sizes")
+        if tuple(cache.k_pages.shape[1:]) != (n_kv_head, cache.page_tokens, head_dim):
+            raise KernelLibraryError("kv_store: page storage does not match the head sizes")
+        check(self.lib.mg_kv_store(_ptr(qkv), _ptr(slot_mapping), _ptr(cache.k_pages),
+                                   _ptr(cache.v_pages), qkv.shape[0], n_head, n_kv_head, head_dim,
+                                   cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
+
+    def paged_attention(self, qkv, n_head, n_kv_head, head_dim, scale, cache, ctx):
+        self._want(qkv, cache.k_pages.dtype, "qkv", 2)
+        table = self._want(ctx.block_tables[cache.group], torch.int32, "block_table", 2)
+        n = qkv.shape[0]
+        out = torch.empty((n, n_head * head_dim), dtype=qkv.dtype, device=self.device)
+        check(self.lib.mg_paged_attention_generic(
+            _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
+            _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,
+            cache.page_tokens, table.shape[1], int(cache.window or 0), float(scale),
+            self._is_bf16(qkv), self._stream()), "paged_attention")
+        return out
+
+    # ---- sampling -------------------------------------------------------------------------------
+    def argmax(self, logits, vocab_limit=None):
+        self._want(logits, torch.float32, "logits", 2)
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=self.device)
+        check(self.lib.mg_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
+                                 int(vocab_limit or 0), self._stream()), "argmax")
+        return out
+
+
+_default = {}
+
+
+def default_ops(device="cuda:0") -> CudaOps:
+    key = str(torch.device(device))
+    if key not in _default:
+        _default[key] = CudaOps(device)
+    return _default[key]

@@ -1,0 +1,147 @@
+"""The engine's step function on the GPU against the plain implementation: every way of
+cutting the same requests into steps must give the same logits, in 32-bit and bfloat16."""
+
+from __future__ import annotations
+
+import itertools
+
+import pytest
+import torch
+
+from harness import (PAGE_TOKENS, TOLERANCE, assert_close, gpu_runner, make_tensors, plain_logits,
+                     tiny_config, tokens_for)
+from mini_gpt_inference_b200.engine.runner import StepEntry
+
+pytestmark = pytest.mark.gpu
+
+CASES = list(itertools.product("AB", ["float32", "bfloat16"], [False, True]))
+IDS = [f"{w}-{d}-{'sharp' if s else 'soft'}" for w, d, s in CASES]
+
+
+def _setup(which, dtype, sharp, num_pages=64, seed=3):
+    cfg = tiny_config(which)
+    tensors = make_tensors(cfg, seed, dtype, sharp)
+    runner = gpu_runner(cfg, tensors, dtype, PAGE_TOKENS[which], num_pages)
+    # A sharpened softmax amplifies bfloat16 rounding of q and k; 32-bit is unaffected.
+    tol = TOLERANCE[dtype] * (4 if sharp and dtype == "bfloat16" else 1)
+    return cfg, tensors, runner, tol
+
+
+@pytest.mark.parametrize("which,dtype,sharp", CASES, ids=IDS)
+def test_whole_prompt_alone(which, dtype, sharp):
+    cfg, tensors, runner, tol = _setup(which, dtype, sharp)
+    for length, seed in [(cfg.n_positions, 1), (37, 2), (1, 3), (2, 4), (PAGE_TOKENS[which] + 1, 5)]:
+        tokens = tokens_for(cfg, length, seed)
+        want = plain_logits(cfg, tensors, tokens)
+        got = runner.step([StepEntry("r", tokens, list(range(length)))])
+        runner.finish("r")
+        assert got.shape == (length, cfg.vocab_size) and got.dtype == torch.float32
+        assert_close(got, want, tol, f"whole prompt of {length}")
+    runner.manager.check()
+    assert runner.manager.stats()["allocated_blocks"] == 0
+
+
+@pytest.mark.parametrize("which,dtype,sharp", CASES, ids=IDS)
+def test_last_32_tokens_one_by_one(which, dtype, sharp):
+    cfg, tensors, runner, tol = _setup(which, dtype, sharp)
+    length = cfg.n_positions
+    tokens = tokens_for(cfg, length, 7)
+    want = plain_logits(cfg, tensors, tokens)
+    head = length - 32
+    outs = [runner.step([StepEntry("r", tokens[:head], list(range(head)))])]
+    for t in range(head, length):
+        outs.append(runner.step([StepEntry("r", tokens[t: t + 1], [0])]))
+    assert_close(torch.cat(outs), want, tol, "prefill then 32 single tokens")
+
+
+@pytest.mark.parametrize("which,dtype,sharp", CASES, ids=IDS)
+def test_portions_of_changing_size(which, dtype, sharp):
+    cfg, tensors, runner, tol = _setup(which, dtype, sharp)
+    length = cfg.n_positions - 3
+    tokens = tokens_for(cfg, length, 8)
+    want = plain_logits(cfg, tensors, tokens)
+    sizes = itertools.cycle([13, 7, 2, 5, 2, 1, 3, 16, 2, 9])
+    outs, pos = [], 0
+    while pos < length:
+        n = min(next(sizes), length - pos)
+        outs.append(runner.step([StepEntry("r", tokens[pos: pos + n], list(range(n)))]))
+        pos += n
+    assert_close(torch.cat(outs), want, tol, "portions of changing size")
+
+
+@pytest.mark.parametrize("which,dtype,sharp", CASES, ids=IDS)
+def test_mixed_requests_with_page_reuse(which, dtype, sharp):
+    """Up to four live requests; portions of some beside decoded tokens of others; a pool so
+    small that the pages of finished requests are handed out again."""
+    cfg = tiny_config(which)
+    pt = PAGE_TOKENS[which]
+    lengths = [cfg.n_positions, 29, cfg.n_positions - 9, 3, 41, 2 * pt, 17, cfg.n_positions // 2]
+    # room for the four longest at once, no more
+    pool = sum(sorted(-(-n // pt) for n in lengths)[-4:])
+    cfg, tensors, runner, tol = _setup(which, dtype, sharp, num_pages=pool)
+    reqs = {f"q{i}": tokens_for(cfg, n, 20 + i) for i, n in enumerate(lengths)}
+    want = {rid: plain_logits(cfg, tensors, toks) for rid, toks in reqs.items()}
+    got = {rid: [] for rid in reqs}
+    waiting = list(reqs)
+    live: dict[str, int] = {}
+    sizes = itertools.cycle([5, 1, 2, 11, 1, 1, 7, 3, 1, 2])
+    gen = torch.Generator().manual_seed(99)
+    steps = 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, order = [], []
+        for rid in list(live):
+            if len(live) > 1 and torch.rand((), generator=gen).item() < 0.25:
+                continue                                   # left out of this step
+            pos = live[rid]
+            n = min(next(sizes), len(reqs[rid]) - pos)
+            entries.append(StepEntry(rid, reqs[rid][pos: pos + n], list(range(n))))
+            order.append((rid, n))
+            live[rid] = pos + n
+        if not entries:
+            continue
+        logits = runner.step(entries)
+        row = 0
+        for rid, n in order:
+            got[rid].append(logits[row: row + n])
+            row += n
+        for rid in [r for r, p in live.items() if p == len(reqs[r])]:
+            runner.finish(rid)
+            del live[rid]
+        runner.manager.check()
+        steps += 1
+    assert runner.manager.stats()["allocated_blocks"] == 0
+    for rid in reqs:
+        assert_close(torch.cat(got[rid]), want[rid], tol, f"mixed batch, request {rid}")
+
+
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "float32")])
+def test_cuttings_agree_bitwise_in_32bit(which, dtype):
+    """In 32-bit every (token, head) and every output element is computed by the same
+    instruction sequence however the batch is cut, so the logits are equal bit for bit."""
+    cfg, tensors, runner, _ = _setup(which, dtype, False)
+    tokens = tokens_for(cfg, 50, 11)
+    whole = runner.step([StepEntry("a", tokens, list(range(50)))])
+    other = tokens_for(cfg, 23, 12)
+    runner.step([StepEntry("o", other[:9], [])])
+    outs = [runner.step([StepEntry("b", tokens[:20], list(range(20))), StepEntry("o", other[9:10], [0])])[:20]]
+    outs.append(runner.step([StepEntry("o", other[10:23], []), StepEntry("b", tokens[20:50], list(range(30)))]))
+    assert torch.equal(torch.cat(outs), whole)
+
+
+def test_step_errors_are_clear():
+    cfg, tensors, runner, _ = _setup("A", "float32", False, num_pages=4)
+    from mini_gpt_inference_b200.cache import CacheFullError
+    from mini_gpt_inference_b200.engine.runner import StepError
+
+    with pytest.raises(StepError, match="vocabulary"):
+        runner.step([StepEntry("x", [cfg.vocab_size], [0])])
+    with pytest.raises(StepError, match="position table"):
+        runner.step([StepEntry("x", [1] * (cfg.n_positions + 1), [])])
+    with pytest.raises(StepError, match="wants logits"):
+        runner.step([StepEntry("x", [1, 2], [2])])
+    runner.step([StepEntry("x", [1] * 60, [])])
+    with pytest.raises(CacheFullError):
+        runner.step([StepEntry("y", [1] * 20, [])])
+    runner.manager.check()
