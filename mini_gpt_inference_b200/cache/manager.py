@@ -122,6 +122,17 @@ class CacheManager:
         need = self.pages_needed(request_id, new_length)
         return all(n <= group.pool.num_free for n, group in zip(need, self.groups))
 
+    def tokens_that_fit(self, request_id: str, length: int | None = None) -> int:
+        """How many tokens beyond ``length`` (default: what the cache holds) the request could
+        store using its pages and all free ones."""
+        req = self.get(request_id)
+        length = req.length if length is None else length
+        room = None
+        for g, group in enumerate(self.groups):
+            cap = (len(req.tables[g]) + group.pool.num_free) * self.page_tokens - length
+            room = cap if room is None else min(room, cap)
+        return max(0, room) if room is not None else 1 << 30
+
     def reserve(self, request_id: str, new_length: int) -> bool:
         """Take the pages needed to hold ``new_length`` tokens.  All groups or none:
         returns False and changes nothing if any group is short."""

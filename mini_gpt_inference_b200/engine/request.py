@@ -1,0 +1,90 @@
+"""What a caller asks for and what the engine keeps about it.
+
+As in the reference (src/minigpt_infer/engine/request.py:20-75): an immutable ``Request``,
+a mutable ``SequenceState`` whose ``num_computed_tokens`` counts the tokens that are in the
+cache, and a ``RequestOutput`` per step.  No torch in this module.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from enum import Enum, auto
+
+from ..config.engine_config import SamplingParams
+
+
+class SequenceStatus(Enum):
+    WAITING = auto()
+    RUNNING = auto()
+    FINISHED = auto()
+
+
+@dataclass
+class Request:
+    request_id: str
+    prompt_token_ids: list[int]
+    sampling_params: SamplingParams = field(default_factory=SamplingParams)
+    eot_token_id: int | None = None
+
+
+@dataclass
+class SequenceState:
+    request: Request
+    output_token_ids: list[int] = field(default_factory=list)
+    status: SequenceStatus = SequenceStatus.WAITING
+    # Tokens whose keys and values are in the cache.  The next token to run is always the one
+    # at this position (src/minigpt_infer/engine/request.py:40-45).
+    num_computed_tokens: int = 0
+    finish_reason: str | None = None
+    seed: int = 0
+    arrival: int = 0
+
+    @property
+    def request_id(self) -> str:
+        return self.request.request_id
+
+    @property
+    def prompt_len(self) -> int:
+        return len(self.request.prompt_token_ids)
+
+    @property
+    def num_tokens(self) -> int:
+        """Prompt plus everything generated so far."""
+        return self.prompt_len + len(self.output_token_ids)
+
+    @property
+    def num_pending_tokens(self) -> int:
+        """Tokens not yet in the cache: one in steady decoding, more while a prompt (or a
+        recomputation after preemption) is under way."""
+        return self.num_tokens - self.num_computed_tokens
+
+    def token_at(self, i: int) -> int:
+        p = self.prompt_len
+        return self.request.prompt_token_ids[i] if i < p else self.output_token_ids[i - p]
+
+    def tokens(self, start: int, count: int) -> list[int]:
+        allt = self.request.prompt_token_ids + self.output_token_ids
+        return allt[start: start + count]
+
+    def is_finished(self) -> bool:
+        return self.status == SequenceStatus.FINISHED
+
+
+@dataclass
+class RequestOutput:
+    request_id: str
+    new_token_ids: list[int]
+    text_delta: str = ""
+    finished: bool = False
+    finish_reason: str | None = None
+
+
+@dataclass
+class ScheduledChunk:
+    """A request's share of one step: ``count`` tokens from position ``start``; ``samples`` if
+    the chunk ends at the request's last token, so that its logits give the next token."""
+
+    seq: SequenceState
+    start: int
+    count: int
+    samples: bool

@@ -26,6 +26,7 @@ _SIGNATURES = {
     "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
+    "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
 

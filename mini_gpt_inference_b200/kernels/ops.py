@@ -169,6 +169,28 @@ class CudaOps:
                                  int(vocab_limit or 0), self._stream()), "argmax")
         return out
 
+    def sample(self, logits, temperature, top_k, top_p, seed_lo, seed_hi, counter, vocab_limit=None):
+        """One draw per row.  temperature float32 [rows]; top_k int32 [rows] or None (<= 0: off);
+        top_p float32 [rows] or None (>= 1: off); seed_lo, seed_hi, counter: int32 [rows] holding
+        the 32-bit words of each row's seed and the number of its draw."""
+        self._want(logits, torch.float32, "logits", 2)
+        rows = logits.shape[0]
+        self._want(temperature, torch.float32, "temperature", 1)
+        for name, t in (("top_k", top_k), ("seed_lo", seed_lo), ("seed_hi", seed_hi),
+                        ("counter", counter)):
+            if t is not None:
+                self._want(t, torch.int32, name, 1)
+        if top_p is not None:
+            self._want(top_p, torch.float32, "top_p", 1)
+        for t in (temperature, top_k, top_p, seed_lo, seed_hi, counter):
+            if t is not None and t.numel() != rows:
+                raise KernelLibraryError("sample: per-row parameters do not match the rows")
+        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        check(self.lib.mg_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+                                 _ptr(seed_lo), _ptr(seed_hi), _ptr(counter), _ptr(out), rows,
+                                 logits.shape[1], int(vocab_limit or 0), self._stream()), "sample")
+        return out
+
 
 _default = {}
 

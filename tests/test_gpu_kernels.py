@@ -1,0 +1,276 @@
+"""Each kernel alone against a plain 32-bit torch reference of the same operation, at sizes
+other than the engine's tiny configurations: odd widths, tails of tiles, head sizes in steps
+of 16, grouped heads, windows, page edges."""
+
+from __future__ import annotations
+
+import math
+from types import SimpleNamespace
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+import plain_gpt
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    return default_ops("cuda:0")
+
+
+def _tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.6e-2) * scale
+
+
+def randn(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,vocab", [(96, 509), (520, 1000), (33, 77)])
+def test_embed(ops, dtype, width, vocab):
+    tok, pos = randn(vocab, width, dtype=dtype, seed=1), randn(300, width, dtype=dtype, seed=2)
+    ids = torch.randint(0, vocab, (45,), dtype=torch.int32).cuda()
+    positions = torch.randint(0, 300, (45,), dtype=torch.int32).cuda()
+    got = ops.embed(ids, positions, tok, pos)
+    want = tok.float()[ids.long()] + pos.float()[positions.long()]
+    assert got.dtype == torch.float32 and torch.equal(got, want)
+    assert torch.equal(ops.embed(ids, positions, tok, None), tok.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,width,eps,bias", [(7, 96, 3e-4, False), (130, 520, 1e-5, True),
+                                                 (1, 33, 1e-2, True), (64, 2048, 1e-5, True)])
+def test_layernorm(ops, dtype, rows, width, eps, bias):
+    x = randn(rows, width, seed=3, scale=3.0) + 1.5          # a mean far from zero
+    gain = randn(width, seed=4) + 1.0
+    shift = randn(width, seed=5) if bias else None
+    got = ops.layernorm(x, gain, shift, eps, dtype)
+    want = F.layer_norm(x.double(), (width,), gain.double(), None if shift is None else shift.double(), eps)
+    assert got.dtype == dtype
+    assert (got.double() - want).abs().max() <= _tol(dtype, 4.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("m,n,k", [(1, 509, 96), (45, 200, 96), (130, 96, 200), (64, 1536, 512),
+                                   (3, 77, 33), (257, 65, 129)])
+def test_linear_and_epilogues(ops, dtype, m, n, k):
+    x = randn(m, k, dtype=dtype, seed=6)
+    w = randn(n, k, dtype=dtype, seed=7, scale=1 / math.sqrt(k))
+    b = randn(n, seed=8)
+    ref = x.double() @ w.double().T
+    assert (ops.linear(x, w, None, "none", dtype).double() - ref).abs().max() <= _tol(dtype, 3)
+    assert (ops.linear(x, w, b, "none", dtype).double() - (ref + b.double())).abs().max() <= _tol(dtype, 3)
+    gelu = plain_gpt.gelu_tanh(ref + b.double())
+    assert (ops.linear(x, w, b, "gelu_tanh", dtype).double() - gelu).abs().max() <= _tol(dtype, 3)
+    logits = ops.logits(x, w)
+    assert logits.dtype == torch.float32
+    assert (logits.double() - ref).abs().max() <= 2e-5        # inputs exact, 32-bit sums and output
+    res = randn(m, n, seed=9)
+    before = res.clone()
+    ops.linear_residual(x, w, b, res)
+    assert (res.double() - (before.double() + ref + b.double())).abs().max() <= 3e-5
+
+
+def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window, lengths, q_lens,
+                    seed=0):
+    """Requests with `lengths[i]` tokens in total, of which the last `q_lens[i]` are new."""
+    g = torch.Generator().manual_seed(seed)
+    R = len(lengths)
+    max_pages = max(-(-n // page_tokens) for n in lengths) + 1
+    num_pages = sum(-(-n // page_tokens) for n in lengths) + 3
+    perm = torch.randperm(num_pages, generator=g).tolist()       # pages in scattered order
+    tables = torch.full((R, max_pages), -1, dtype=torch.int32)
+    k_all, v_all = [], []
+    k_pages = torch.full((num_pages, n_kv_head, page_tokens, head_dim), float("nan"))
+    v_pages = torch.full((num_pages, n_kv_head, page_tokens, head_dim), float("nan"))
+    for r, n in enumerate(lengths):
+        k = torch.randn(n, n_kv_head, head_dim, generator=g).to(dtype).float()
+        v = torch.randn(n, n_kv_head, head_dim, generator=g).to(dtype).float()
+        k_all.append(k)
+        v_all.append(v)
+        for i in range(-(-n // page_tokens)):
+            page = perm.pop()
+            tables[r, i] = page
+            chunk = slice(i * page_tokens, min(n, (i + 1) * page_tokens))
+            k_pages[page, :, : chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
+            v_pages[page, :, : chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+    # unused rows of pages hold NaN: reading past a request's length would poison the output
+    qkv_rows, token_request, positions, want = [], [], [], []
+    scale = 1.0 / math.sqrt(head_dim)
+    for r, (n, ql) in enumerate(zip(lengths, q_lens)):
+        q = torch.randn(ql, n_head, head_dim, generator=g).to(dtype).float() * 2.0
+        for i in range(ql):
+            p = n - ql + i
+            lo = 0 if not window else max(0, p - window + 1)
+            row = torch.zeros(n_head, head_dim, dtype=torch.float64)
+            for h in range(n_head):
+                kh = h // (n_head // n_kv_head)
+                s = (k_all[r][lo: p + 1, kh].double() @ q[i, h].double()) * scale
+                row[h] = torch.softmax(s, 0) @ v_all[r][lo: p + 1, kh].double()
+            want.append(row.reshape(-1))
+            filler = torch.zeros(2 * n_kv_head * head_dim)
+            qkv_rows.append(torch.cat([q[i].reshape(-1), filler]))
+            token_request.append(r)
+            positions.append(p)
+    cache = SimpleNamespace(k_pages=k_pages.to(dtype).cuda(), v_pages=v_pages.to(dtype).cuda(),
+                            group=0, page_tokens=page_tokens, window=window or None, writes=False)
+    ctx = SimpleNamespace(block_tables=[tables.cuda()],
+                          token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
+                          positions=torch.tensor(positions, dtype=torch.int32).cuda())
+    qkv = torch.stack(qkv_rows).to(dtype).cuda()
+    got = ops.paged_attention(qkv, n_head, n_kv_head, head_dim, scale, cache, ctx)
+    return got.double().cpu(), torch.stack(want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,window", [
+    (8, 8, 64, 16, 0), (3, 3, 32, 8, 0), (5, 1, 48, 4, 0), (6, 2, 16, 16, 0), (4, 4, 80, 32, 0),
+    (2, 2, 128, 16, 0), (4, 2, 256, 64, 0), (4, 4, 32, 8, 5), (6, 3, 64, 16, 33)])
+def test_paged_attention_general(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window):
+    pt = page_tokens
+    lengths = [1, 2, pt - 1, pt, pt + 1, 2 * pt, 3 * pt + 1, 150]
+    q_lens = [1, 2, 1, pt, 3, 1, 2 * pt + 1, 31]
+    got, want = _attention_case(ops, dtype, n_head, n_kv_head, head_dim, pt, window, lengths, q_lens)
+    assert not torch.isnan(got).any(), "attention read a cache row beyond a request's length"
+    assert (got - want).abs().max() <= _tol(dtype, 1.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_far_key_among_hundreds_decides(ops, dtype):
+    """One key far back gets a score that dominates: the output must be that key's value."""
+    n_head, head_dim, pt, n = 2, 64, 16, 700
+    g = torch.Generator().manual_seed(5)
+    k = torch.randn(n, n_head, head_dim, generator=g) * 0.1
+    v = torch.randn(n, n_head, head_dim, generator=g)
+    q = torch.randn(1, n_head, head_dim, generator=g)
+    far = 3                                                      # in the first page
+    k[far] = q[0] * 4.0                                          # score ~ 4 |q|^2 / 8 >> the rest
+    pages = -(-n // pt)
+    kp = torch.zeros(pages, n_head, pt, head_dim)
+    vp = torch.zeros(pages, n_head, pt, head_dim)
+    for i in range(pages):
+        sl = slice(i * pt, min(n, (i + 1) * pt))
+        kp[i, :, : sl.stop - sl.start] = k[sl].transpose(0, 1)
+        vp[i, :, : sl.stop - sl.start] = v[sl].transpose(0, 1)
+    cache = SimpleNamespace(k_pages=kp.to(dtype).cuda(), v_pages=vp.to(dtype).cuda(), group=0,
+                            page_tokens=pt, window=None, writes=False)
+    ctx = SimpleNamespace(block_tables=[torch.arange(pages, dtype=torch.int32)[None].cuda()],
+                          token_request=torch.zeros(1, dtype=torch.int32).cuda(),
+                          positions=torch.tensor([n - 1], dtype=torch.int32).cuda())
+    qkv = torch.cat([q.reshape(1, -1), torch.zeros(1, 2 * n_head * head_dim)], 1).to(dtype).cuda()
+    got = ops.paged_attention(qkv, n_head, n_head, head_dim, 1 / math.sqrt(head_dim), cache, ctx)
+    want = v[far].to(dtype).float().reshape(-1)
+    assert (got.float().cpu()[0] - want).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_kv_store_places_rows(ops, dtype):
+    n_head, n_kv, d, pt, pages = 6, 2, 48, 8, 9
+    qkv = randn(11, (n_head + 2 * n_kv) * d, dtype=dtype, seed=3)
+    slots = torch.tensor([5, 70, 8, 9, 63, 0, 33, 34, 35, 71, -1], dtype=torch.int32).cuda()
+    cache = SimpleNamespace(k_pages=torch.zeros(pages, n_kv, pt, d, dtype=dtype).cuda(),
+                            v_pages=torch.zeros(pages, n_kv, pt, d, dtype=dtype).cuda(),
+                            page_tokens=pt)
+    ops.kv_store(qkv, n_head, n_kv, d, cache, slots)
+    k = qkv[:, n_head * d: (n_head + n_kv) * d].reshape(11, n_kv, d)
+    v = qkv[:, (n_head + n_kv) * d:].reshape(11, n_kv, d)
+    want_k = torch.zeros_like(cache.k_pages)
+    want_v = torch.zeros_like(cache.v_pages)
+    for i, s in enumerate(slots.tolist()):
+        if s >= 0:
+            want_k[s // pt, :, s % pt] = k[i]
+            want_v[s // pt, :, s % pt] = v[i]
+    assert torch.equal(cache.k_pages, want_k) and torch.equal(cache.v_pages, want_v)
+
+
+def test_gather_rows_and_argmax(ops):
+    x = randn(40, 77, seed=1)
+    rows = torch.tensor([3, 3, 39, 0], dtype=torch.int32).cuda()
+    assert torch.equal(ops.gather_rows(x, rows), x[rows.long()])
+    logits = randn(9, 50304, seed=2)
+    logits[4, 50300] = 99.0
+    logits[5, 17] = logits[5, 4000] = 50.0                     # a tie: the lower index wins
+    got = ops.argmax(logits)
+    assert got.tolist() == logits.argmax(-1).tolist() or got[5] == 17
+    assert got[4] == 50300 and got[5] == 17
+    limited = ops.argmax(logits, 50257)
+    assert limited[4] == logits[4, :50257].argmax()
+
+
+def _draws(ops, logits_row, temperature, top_k, top_p, n, seed=1234):
+    rows = logits_row[None].expand(n, -1).contiguous()
+    i32 = lambda v: torch.full((n,), v, dtype=torch.int32).cuda()          # noqa: E731
+    f32 = lambda v: torch.full((n,), v, dtype=torch.float32).cuda()        # noqa: E731
+    counter = torch.arange(n, dtype=torch.int32).cuda()
+    return ops.sample(rows, f32(temperature), None if top_k is None else i32(top_k),
+                      None if top_p is None else f32(top_p), i32(seed & 0xFFFF), i32(seed >> 16),
+                      counter)
+
+
+@pytest.mark.parametrize("vocab", [509, 50304])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, None, None), (0.7, 5, None),
+                                                     (1.3, None, 0.6), (0.9, 40, 0.8)])
+def test_sampler_draws_from_the_reference_distribution(ops, vocab, temperature, top_k, top_p):
+    g = torch.Generator().manual_seed(3)
+    logits = (torch.randn(vocab, generator=g) * 2.5).cuda()
+    want = plain_gpt.sampling_distribution(logits.cpu(), temperature, top_k, top_p)
+    n = 40000
+    ids = _draws(ops, logits, temperature, top_k, top_p, n).long().cpu()
+    counts = torch.bincount(ids, minlength=vocab).double()
+    # nothing outside the support (allowing the one token at the top-p edge to differ by rounding)
+    outside = counts[want == 0].sum().item()
+    assert outside <= (0 if top_p is None else 0.002 * n), outside
+    # frequencies follow the probabilities: compare on the 20 likeliest tokens
+    top = want.topk(20).indices
+    freq = counts[top] / n
+    sigma = (want[top] * (1 - want[top]) / n).sqrt()
+    assert ((freq - want[top]).abs() <= 5 * sigma + 2e-3).all(), (freq, want[top])
+
+
+def test_sampler_is_greedy_at_zero_and_repeatable_by_seed(ops):
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(6, 1000, generator=g).cuda()
+    zeros = torch.zeros(6).cuda()
+    i32 = lambda v: torch.full((6,), v, dtype=torch.int32).cuda()          # noqa: E731
+    got = ops.sample(logits, zeros, None, None, i32(1), i32(2), i32(3))
+    assert got.tolist() == logits.argmax(-1).tolist()
+    # mixed rows: greedy and stochastic side by side (tests/test_sampling.py:63-78)
+    temps = torch.tensor([0.0, 1.0, 0.0, 1.0, 1.0, 0.0]).cuda()
+    a = ops.sample(logits, temps, None, None, i32(7), i32(0), i32(5))
+    b = ops.sample(logits, temps, None, None, i32(7), i32(0), i32(5))
+    c = ops.sample(logits, temps, None, None, i32(8), i32(0), i32(5))
+    assert a.tolist() == b.tolist()
+    assert [a[i].item() for i in (0, 2, 5)] == [logits[i].argmax().item() for i in (0, 2, 5)]
+    assert a.tolist() != c.tolist()
+    # a row's draw does not depend on the rows beside it
+    alone = ops.sample(logits[3:4].contiguous(), temps[3:4].contiguous(), None, None,
+                       i32(7)[:1], i32(0)[:1], i32(5)[:1])
+    assert alone[0] == a[3]
+    # top_k = 1 is greedy whatever the temperature
+    k1 = ops.sample(logits, torch.full((6,), 5.0).cuda(), i32(1), None, i32(7), i32(0), i32(5))
+    assert k1.tolist() == logits.argmax(-1).tolist()
+
+
+def test_refusals_are_clear(ops):
+    from mini_gpt_inference_b200.kernels.library import KernelLibraryError
+
+    with pytest.raises(KernelLibraryError, match="contiguous"):
+        ops.layernorm(randn(4, 8).T, randn(4), None, 1e-5, torch.float32)
+    with pytest.raises(KernelLibraryError, match="dtype"):
+        ops.linear(randn(4, 8), randn(3, 8, dtype=torch.bfloat16), None, "none", torch.float32)
+    with pytest.raises(KernelLibraryError, match="head_dim"):
+        cache = SimpleNamespace(k_pages=torch.zeros(2, 1, 4, 512).cuda(), v_pages=torch.zeros(2, 1, 4, 512).cuda(),
+                                group=0, page_tokens=4, window=None)
+        ctx = SimpleNamespace(block_tables=[torch.zeros(1, 2, dtype=torch.int32).cuda()],
+                              token_request=torch.zeros(1, dtype=torch.int32).cuda(),
+                              positions=torch.zeros(1, dtype=torch.int32).cuda())
+        ops.paged_attention(torch.zeros(1, 3 * 512).cuda(), 1, 1, 512, 1.0, cache, ctx)

@@ -1,0 +1,293 @@
+"""Each part alone against its plain formula, at sizes of its own; and the framework's
+generality: a toy mixer with per-request state of its own, a toy position encoding and a toy
+architecture, all defined here, are registered, built and stepped without touching the
+framework's files."""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_gpt
+
+from mini_gpt_inference_b200.cache import CacheManager, FixedStateSpec
+from mini_gpt_inference_b200.cache.storage import CacheStorage
+from mini_gpt_inference_b200.config import register_model
+from mini_gpt_inference_b200.engine.build import load_model, make_runner
+from mini_gpt_inference_b200.engine.runner import StepEntry
+from mini_gpt_inference_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, LayerCall, LayerSpec,
+                                           Mixer, ModelSpec, PartSpec, PositionEncoding,
+                                           StepContext, TensorSpec, register_mixer,
+                                           register_position_encoding)
+from mini_gpt_inference_b200.parts.base import EMBEDDINGS, HEADS, POSITION_ENCODINGS
+from mini_gpt_inference_b200.weights import random_tensors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mini_gpt_inference_b200.kernels.ops import default_ops
+
+    return default_ops(DEV)
+
+
+def i32(values):
+    return torch.tensor(values, dtype=torch.int32, device=DEV)
+
+
+def make_ctx(ops, dtype, lengths, manager=None, storage=None, ids=None):
+    """A context in which request r brings `lengths[r]` tokens into an empty cache."""
+    n = sum(lengths)
+    token_request = [r for r, m in enumerate(lengths) for _ in range(m)]
+    positions = [p for m in lengths for p in range(m)]
+    starts = [sum(lengths[:r]) for r in range(len(lengths))]
+    tables, slots = [], []
+    if manager is not None:
+        for g in range(len(manager.groups)):
+            width = max(manager.pages_for(m) for m in lengths)
+            table = torch.full((len(lengths), width), -1, dtype=torch.int32)
+            slot = []
+            for r, m in enumerate(lengths):
+                manager.admit(f"q{r}")
+                manager.reserve(f"q{r}", m)
+                t = manager.block_table(f"q{r}", g)
+                table[r, : len(t)] = torch.tensor(t, dtype=torch.int32)
+                slot += [manager.slot_of(f"q{r}", g, p) for p in range(m)]
+            tables.append(table.to(DEV))
+            slots.append(i32(slot))
+    return StepContext(
+        ops=ops, act_dtype=dtype, num_tokens=n, num_requests=len(lengths),
+        token_ids=i32(ids if ids is not None else [0] * n), positions=i32(positions),
+        token_request=i32(token_request), req_q_start=i32(starts), req_q_len=i32(lengths),
+        req_ctx_before=i32([0] * len(lengths)), req_state_slot=i32(list(range(len(lengths)))),
+        block_tables=tables, slot_mapping=slots, logit_rows=i32(list(range(n))),
+        host_q_len=list(lengths), host_ctx_before=[0] * len(lengths),
+        host_state_slot=list(range(len(lengths))), max_q_len=max(lengths),
+        max_ctx_after=max(lengths), decode_only=False, storage=storage)
+
+
+def rel_err(got, want):
+    """Largest difference relative to the largest wanted value: bfloat16 keeps 8 significant
+    bits, so its error scales with the magnitude of what is computed."""
+    return ((got.double().cpu() - want.double()).abs().max() / want.abs().max()).item()
+
+
+REL = {torch.float32: 1e-5, torch.bfloat16: 2e-2}
+
+
+def bind_random(part, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    cpu, dev = {}, {}
+    for name, spec in part.tensor_specs().items():
+        t = torch.randn(spec.shape, generator=g) * (0.3 if spec.role == "matrix" else 1.0)
+        store = dtype if spec.role == "matrix" else torch.float32
+        cpu[name] = t.to(store).float()
+        dev[name] = t.to(store).to(DEV)
+    part.bind(dev)
+    return cpu
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layernorm_part(ops, dtype):
+    part = NORMS.build(PartSpec("layernorm", {"width": 72, "eps": 2e-3, "bias": True}, "n"), "x.")
+    assert set(part.tensor_specs()) == {"x.n.weight", "x.n.bias"}
+    w = bind_random(part, dtype, 1)
+    x = torch.randn(13, 72, generator=torch.Generator().manual_seed(2)) * 2 + 1
+    got = part.forward(make_ctx(ops, dtype, [13]), x.to(DEV))
+    want = plain_gpt.layer_norm(x.double(), w["x.n.weight"].double(), w["x.n.bias"].double(), 2e-3)
+    assert got.dtype == dtype
+    assert rel_err(got, want) <= REL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_dense_mlp_part(ops, dtype):
+    part = FEED_FORWARDS.build(PartSpec("dense_mlp", {"width": 40, "inner": 136, "bias": True}, "ff"), "")
+    w = bind_random(part, dtype, 3)
+    y = (torch.randn(9, 40, generator=torch.Generator().manual_seed(4))).to(dtype)
+    residual = torch.randn(9, 40, generator=torch.Generator().manual_seed(5))
+    res_dev = residual.to(DEV)
+    part.forward(make_ctx(ops, dtype, [9]), y.to(DEV), res_dev)
+    want = residual.double() + plain_gpt.mlp(y.double(), {k: v.double() for k, v in w.items()}, "ff.")
+    assert rel_err(res_dev, want) <= REL[dtype]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,window", [(4, 4, 16, None), (6, 2, 32, None),
+                                                              (2, 2, 48, 5)])
+def test_attention_part(ops, dtype, n_head, n_kv_head, head_dim, window):
+    width = 56
+    part = MIXERS.build(PartSpec("causal_attention", {
+        "width": width, "n_head": n_head, "n_kv_head": n_kv_head, "head_dim": head_dim,
+        "bias": True, "window": window}, "attn"), "", position=None)
+    w = bind_random(part, dtype, 6)
+    lengths = [19, 1, 8]
+    manager = CacheManager([part.cache_spec()], 8, 16, 4)
+    storage = CacheStorage(manager, dtype, DEV)
+    ctx = make_ctx(ops, dtype, lengths, manager, storage)
+    y = torch.randn(sum(lengths), width, generator=torch.Generator().manual_seed(7)).to(dtype)
+    residual = torch.zeros(sum(lengths), width, device=DEV)
+    part.forward(ctx, ctx.cache_view(0), y.to(DEV), residual)
+    row = 0
+    for m in lengths:
+        want = plain_gpt.causal_attention(y[row: row + m].double(), {k: v.double() for k, v in w.items()},
+                                          "attn.", n_head, window=window, n_kv_head=n_kv_head)
+        got = residual[row: row + m].double().cpu()
+        assert (got - want).abs().max() <= (3e-5 if dtype == torch.float32 else 6e-2)
+        row += m
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embedding_positions_and_head(ops, dtype):
+    emb = EMBEDDINGS.build(PartSpec("token_embedding", {"vocab_size": 301, "width": 24}, "tok_emb"), "")
+    pos = POSITION_ENCODINGS.build(PartSpec("learned_absolute", {"n_positions": 50, "width": 24}, "pos_emb"), "")
+    head = HEADS.build(PartSpec("tied_head", {"vocab_size": 301, "width": 24, "tied_to": "tok_emb.weight"},
+                                "lm_head"), "", embedding=emb)
+    w = {**bind_random(emb, dtype, 8), **bind_random(pos, dtype, 9)}
+    assert pos.max_positions == 50 and head.tensor_specs()["lm_head.weight"].optional_alias_of
+    ids = [5, 300, 0, 17, 17, 299, 1]
+    ctx = make_ctx(ops, dtype, [4, 3], ids=ids)
+    x = emb.forward(ctx, pos)
+    want = torch.cat([plain_gpt.embed(torch.tensor(ids[:4]), w, torch.float64),
+                      plain_gpt.embed(torch.tensor(ids[4:]), w, torch.float64)])
+    assert x.dtype == torch.float32 and (x.double().cpu() - want).abs().max() <= 1e-6
+    y = torch.randn(7, 24, generator=torch.Generator().manual_seed(10)).to(dtype)
+    logits = head.forward(ctx, y.to(DEV))
+    assert logits.dtype == torch.float32
+    assert (logits.double().cpu() - y.double() @ w["tok_emb.weight"].double().T).abs().max() <= 2e-5
+
+
+# ---- toy parts, defined here only ------------------------------------------------------------
+@register_mixer("toy_running_mean")
+class RunningMeanMixer(Mixer):
+    """Output at position t = gain * mean of the inputs at positions 0..t of the same request.
+    Its state per request: the running sum of the inputs and the number of tokens so far."""
+
+    def __init__(self, prefix, width, position=None):
+        super().__init__(prefix)
+        self.width = width
+        self.gain = None
+
+    def tensor_specs(self):
+        return {self.prefix + "gain": TensorSpec((self.width,), "vector", "norm_gain")}
+
+    def cache_spec(self):
+        return FixedStateSpec((self.width + 1,), "float32")
+
+    def forward(self, ctx, cache, y, residual32):
+        start = 0
+        for r, (n, before) in enumerate(zip(ctx.host_q_len, ctx.host_ctx_before)):
+            slot = ctx.host_state_slot[r]
+            if before == 0:
+                cache.state[slot].zero_()                    # a new (or recomputed) request
+            rows = y[start: start + n].float()
+            sums = cache.state[slot, : self.width] + rows.cumsum(0)
+            counts = cache.state[slot, self.width] + torch.arange(1, n + 1, device=y.device)
+            residual32[start: start + n] += self.gain * sums / counts[:, None]
+            if cache.writes:
+                cache.state[slot, : self.width] = sums[-1]
+                cache.state[slot, self.width] = counts[-1]
+            start += n
+
+
+@register_position_encoding("toy_sign_flip")
+class SignFlipPositions(PositionEncoding):
+    """No table; flips the sign of q and k at odd positions (a stand-in for a rotation)."""
+
+    def __init__(self, prefix=""):
+        super().__init__(prefix)
+
+    def rotate(self, ctx, qkv, n_head, n_kv_head, head_dim):
+        sign = (1 - 2 * (ctx.positions % 2)).to(qkv.dtype)[:, None]
+        qkv[:, : (n_head + n_kv_head) * head_dim] *= sign
+
+
+@dataclass(frozen=True)
+class ToyConfig:
+    vocab_size: int
+    width: int
+    architecture: str = "ToyStateLM"
+
+    @classmethod
+    def from_dict(cls, raw, architecture=None):
+        return cls(raw["vocab_size"], raw["width"])
+
+
+@register_model("ToyStateLM", config_class=ToyConfig)
+def describe_toy(cfg: ToyConfig) -> ModelSpec:
+    norm = PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "n1")
+    norm2 = PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "n2")
+    ff = PartSpec("dense_mlp", {"width": cfg.width, "inner": 2 * cfg.width, "bias": False}, "ff")
+    attn = PartSpec("causal_attention", {"width": cfg.width, "n_head": 2, "n_kv_head": 1,
+                                         "head_dim": 16, "bias": False, "window": 6}, "attn")
+    layers = (LayerSpec("l0.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"), ff, norm, norm2),
+              LayerSpec("l1.", attn, ff, norm, norm2),
+              LayerSpec("l2.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"), ff, norm, norm2))
+    return ModelSpec(
+        architecture="ToyStateLM", width=cfg.width, vocab_size=cfg.vocab_size,
+        embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": cfg.width}, "emb"),
+        position=PartSpec("toy_sign_flip", {}, ""),
+        layers=layers,
+        # layer 1 runs twice; its second run reads the cache its first run wrote
+        layer_order=(LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2), LayerCall(1, 1, writes_cache=False)),
+        final_norm=PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "nf"),
+        head=PartSpec("tied_head", {"vocab_size": cfg.vocab_size, "width": cfg.width,
+                                    "tied_to": "emb.weight"}, "head"))
+
+
+def test_toy_mixer_alone_matches_its_formula(ops):
+    part = MIXERS.build(PartSpec("toy_running_mean", {"width": 12}, "mix"), "", position=None)
+    part.bind({"mix.gain": torch.full((12,), 2.0, device=DEV)})
+    manager = CacheManager([part.cache_spec()], 8, 4, 4)
+    storage = CacheStorage(manager, torch.float32, DEV)
+    ctx = make_ctx(ops, torch.float32, [5, 3], manager, storage)
+    y = torch.randn(8, 12, device=DEV)
+    residual = torch.zeros(8, 12, device=DEV)
+    part.forward(ctx, ctx.cache_view(0), y, residual)
+    want = torch.cat([2 * y[:5].cumsum(0) / torch.arange(1, 6, device=DEV)[:, None],
+                      2 * y[5:].cumsum(0) / torch.arange(1, 4, device=DEV)[:, None]])
+    assert torch.allclose(residual, want, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(ops, dtype):
+    from mini_gpt_inference_b200.config import lookup
+    from mini_gpt_inference_b200.parts import DecoderModel
+
+    cfg = ToyConfig(vocab_size=97, width=32)
+    family = lookup("ToyStateLM")
+    model = DecoderModel(family.describe(cfg))
+    specs = model.cache_specs()
+    assert isinstance(specs[0], FixedStateSpec) and isinstance(specs[2], FixedStateSpec)
+    tensors = random_tensors(model, 3, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    loaded = load_model(config=cfg, tensors=tensors, dtype=dtype, device=DEV)
+    runner = make_runner(loaded, ops, page_tokens=4, num_pages=12, max_requests=3)
+    assert len(runner.manager.groups) == 1 and sorted(runner.manager.state_layers) == [0, 2]
+    g = torch.Generator().manual_seed(1)
+    a = torch.randint(0, 97, (30,), generator=g).tolist()
+    b = torch.randint(0, 97, (21,), generator=g).tolist()
+    whole_a = runner.step([StepEntry("a", a, list(range(30)))])
+    whole_b = runner.step([StepEntry("b", b, list(range(21)))])
+    runner.finish("a")
+    runner.finish("b")
+    # the same two requests in portions, side by side, in fresh slots and pages
+    got_a, got_b, pa, pb = [], [], 0, 0
+    for na, nb in [(7, 1), (1, 9), (2, 1), (11, 2), (9, 8)]:
+        out = runner.step([StepEntry("a2", a[pa: pa + na], list(range(na))),
+                           StepEntry("b2", b[pb: pb + nb], list(range(nb)))])
+        got_a.append(out[:na])
+        got_b.append(out[na:])
+        pa, pb = pa + na, pb + nb
+        runner.manager.check()
+    tol = 2e-5 if dtype == "float32" else 3e-2
+    assert (torch.cat(got_a) - whole_a).abs().max() <= tol
+    assert (torch.cat(got_b) - whole_b).abs().max() <= tol
+    # the window (6) let pages go back early: 30 tokens never held more than 3 pages of 4
+    assert runner.manager.groups[0].pool.num_used <= 6
+    runner.finish("a2")
+    runner.finish("b2")
+    assert runner.manager.stats()["allocated_blocks"] == 0
