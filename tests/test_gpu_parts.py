@@ -84,7 +84,7 @@ def bind_random(part, dtype, seed):
     g = torch.Generator().manual_seed(seed)
     cpu, dev = {}, {}
     for name, spec in part.tensor_specs().items():
-        t = torch.randn(spec.shape, generator=g) * (0.3 if spec.role == "matrix" else 1.0)
+        t = torch.randn(spec.shape, generator=g) * (0.15 if spec.role == "matrix" else 1.0)
         store = dtype if spec.role == "matrix" else torch.float32
         cpu[name] = t.to(store).float()
         dev[name] = t.to(store).to(DEV)
@@ -136,8 +136,7 @@ def test_attention_part(ops, dtype, n_head, n_kv_head, head_dim, window):
     for m in lengths:
         want = plain_gpt.causal_attention(y[row: row + m].double(), {k: v.double() for k, v in w.items()},
                                           "attn.", n_head, window=window, n_kv_head=n_kv_head)
-        got = residual[row: row + m].double().cpu()
-        assert (got - want).abs().max() <= (3e-5 if dtype == torch.float32 else 6e-2)
+        assert rel_err(residual[row: row + m], want) <= REL[dtype]
         row += m
 
 
