@@ -1,0 +1,431 @@
+#!/usr/bin/env python3
+"""Serving benchmark: decode tokens per second of the GPT-2 style 50M decoder on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step: every request of the batch advances by one token.  The default
+run has the layer sizes of the 50M configuration (8 layers, width 512, 8 heads of 64, MLP
+2048, vocabulary 50304, 2048 positions, biases on, tied head) with seeded random weights in
+bfloat16, a batch of 8 and contexts that end at 2048 tokens.  One JSON line is printed:
+
+* ``value``: decoded tokens per second from the device time of K decode steps (CUDA events
+  around each step's work on the stream; L2 is flushed between steps, outside the events);
+* ``e2e``: the same through ``LLMEngine.step()`` with host token ids in and out, wall clock;
+* ``prefill``: one 2,048-token prompt; ``roofline``: bytes a decode step must read / its time;
+* ``points``: decode at batch 1 and 64.
+
+The reference's own benchmark times decode the same way — prefill untimed, then per-token
+steps (bench/bench_hardware.py:96-128) — on its static cache; ``--impl reference`` runs that
+unmodified code from ``baseline/_ref`` at the same sizes.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MODEL = dict(vocab_size=50304, n_positions=2048, n_layer=8, n_head=8, n_embd=512, n_inner=2048,
+             bias=True, layer_norm_epsilon=1e-5)
+BASELINE_T4_DECODE_B8 = 1671.8      # tok/s, Tesla T4 fp16, context 8..40 (docs/BENCHMARKS.md:622)
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+PREFILL_TOKENS = 2048
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=MODEL["n_positions"])
+    ap.add_argument("--layers", type=int, default=MODEL["n_layer"],
+                    help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--page-tokens", type=int, default=64)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    return ap.parse_args()
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+                if isinstance(raw.get(key), (int, float)):
+                    out[key] = float(raw[key])
+            return out, "measured"
+        except (json.JSONDecodeError, OSError):
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int = 0) -> None:
+        self.index = index
+        self.proc = None
+        self.lines: list[str] = []
+        self.thread = None
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self) -> None:
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[2:6]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ---- this engine ---------------------------------------------------------------------------------
+def build_engine(args, batch: int, max_tokens_per_request: int):
+    import torch
+
+    from mini_gpt_inference_b200 import EngineConfig, GPTConfig, LLMEngine
+    from mini_gpt_inference_b200.config import lookup
+    from mini_gpt_inference_b200.engine.build import load_model
+    from mini_gpt_inference_b200.parts import DecoderModel
+    from mini_gpt_inference_b200.weights import random_tensors
+
+    cfg = GPTConfig.from_dict({**MODEL, "n_layer": args.layers})
+    key = (args.layers, args.dtype)
+    if key not in build_engine.cache:
+        model = DecoderModel(lookup(cfg.architecture).describe(cfg))
+        store = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+        tensors = random_tensors(model, 0, store)
+        build_engine.cache[key] = load_model(config=cfg, tensors=tensors, dtype=args.dtype,
+                                             device="cuda:0")
+    loaded = build_engine.cache[key]
+    pt = args.page_tokens
+    pages = batch * ((max_tokens_per_request + pt - 1) // pt) + 4
+    ecfg = EngineConfig(block_size=pt, num_blocks=pages, max_batch_size=max(batch, 1),
+                        max_num_batched_tokens=2048, dtype=args.dtype, device="cuda:0")
+    return cfg, LLMEngine(loaded, ecfg, seed=0)
+
+
+build_engine.cache = {}
+
+
+def weight_bytes(cfg, dtype_bytes: int) -> int:
+    """Bytes of every weight a decode step reads once: the matrices in the compute dtype, the
+    vectors (biases, norm gains) in 32-bit, the embedding matrix once (as the output head)."""
+    c, f, n_layer, v = cfg.n_embd, cfg.n_inner, cfg.n_layer, cfg.vocab_size
+    matrices = n_layer * (3 * c * c + c * c + 2 * c * f) + v * c
+    vectors = n_layer * (2 * c + (3 * c + c + f + c + 2 * c if cfg.bias else 0)) + (2 * c if cfg.bias else c)
+    return matrices * dtype_bytes + vectors * 4
+
+
+def kv_bytes(cfg, batch: int, context: float, dtype_bytes: int) -> float:
+    return batch * context * 2 * cfg.n_layer * cfg.n_embd * dtype_bytes
+
+
+def prefill_flops(cfg, tokens: int) -> float:
+    c, f = cfg.n_embd, cfg.n_inner
+    linear = 2.0 * tokens * cfg.n_layer * (3 * c * c + c * c + 2 * c * f)
+    attention = cfg.n_layer * 2.0 * c * tokens * (tokens + 1)      # QK^T and PV over the causal half
+    head = 2.0 * c * cfg.vocab_size                                  # logits of the last row only
+    return linear + attention + head
+
+
+def device_decode(args, batch: int, steps: int, warmup: int):
+    """K decode steps of `batch` requests whose contexts end at args.context; device time."""
+    import torch
+
+    from mini_gpt_inference_b200.config import SamplingParams
+    from mini_gpt_inference_b200.engine.runner import StepEntry
+
+    cfg, engine = build_engine(args, batch, args.context)
+    runner, sampler = engine.runner, engine.sampler
+    prompt_len = args.context - (steps + warmup)
+    gen = torch.Generator().manual_seed(1)
+    rids = [f"d{i}" for i in range(batch)]
+    for rid in rids:                                   # prefill, untimed
+        prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
+        runner.step([StepEntry(rid, prompt, [])])
+    last = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
+    greedy = [SamplingParams(temperature=0.0)] * batch
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    times = []
+    launches_before = getattr(runner.ops, "launches", 0)
+    torch.cuda.synchronize()
+    for step in range(steps + warmup):
+        flush.zero_()                                  # evict L2 between steps, outside the events
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if step == warmup:
+            torch.cuda.synchronize()
+            launches_before = getattr(runner.ops, "launches", 0)
+        start.record()
+        logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)])
+        ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch)
+        end.record()
+        last = ids.tolist()                            # device -> host: the step's result
+        if step >= warmup:
+            times.append(start.elapsed_time(end))
+    torch.cuda.synchronize()
+    launches = getattr(runner.ops, "launches", 0) - launches_before
+    for rid in rids:
+        runner.finish(rid)
+    mean_context = args.context - steps / 2.0
+    return cfg, times, launches, mean_context
+
+
+def e2e_decode(args, batch: int, steps: int, warmup: int):
+    """The same through LLMEngine.step(): host token ids in, sampled ids out, wall clock."""
+    import torch
+
+    from mini_gpt_inference_b200 import Request, SamplingParams
+
+    cfg, engine = build_engine(args, batch, args.context)
+    # requests finish their prompts a few steps apart; leave room so that none runs out of
+    # tokens inside the timed steps
+    max_tokens = steps + warmup + batch + 8
+    prompt_len = args.context - max_tokens
+    gen = torch.Generator().manual_seed(2)
+    for i in range(batch):
+        prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
+        engine.add_request(Request(f"e{i}", prompt, SamplingParams(max_tokens=max_tokens,
+                                                                    temperature=0.0)))
+    # prompts first (untimed), until every request is decoding
+    while any(s.num_pending_tokens > 1 or s.num_computed_tokens == 0
+              for s in list(engine.scheduler.running) + list(engine.scheduler.waiting)):
+        engine.step()
+    for _ in range(warmup - 1):
+        engine.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    produced = 0
+    for _ in range(steps):
+        produced += len(engine.step())
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    h2d = engine.runner.last_h2d_bytes if hasattr(engine.runner, "last_h2d_bytes") else None
+    while engine.has_unfinished_requests():
+        engine.step()
+    return produced / wall, wall / steps * 1e3, h2d, batch * 4
+
+
+def prefill_once(args):
+    import torch
+
+    from mini_gpt_inference_b200.engine.runner import StepEntry
+
+    cfg, engine = build_engine(args, 1, PREFILL_TOKENS)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
+    times = []
+    for rep in range(6):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        logits = runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        assert logits.shape == (1, cfg.vocab_size)
+        runner.finish("p")
+        if rep >= 2:
+            times.append(start.elapsed_time(end))
+    return cfg, statistics.median(times)
+
+
+def run_ours(args) -> dict:
+    import torch
+
+    pk, peak_source = peaks()
+    dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    sampler = ClockSampler(0)
+    sampler.start()
+    cfg, times, launches, mean_ctx = device_decode(args, args.batch, args.steps, args.warmup)
+    clocks = sampler.stop()
+    ms = statistics.fmean(times)
+    value = args.batch / (ms * 1e-3)
+    step_bytes = weight_bytes(cfg, dtype_bytes) + kv_bytes(cfg, args.batch, mean_ctx, dtype_bytes)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    e2e_value, e2e_ms, h2d, d2h = e2e_decode(args, args.batch, args.steps, args.warmup)
+    line = {
+        "metric": "decode tok/s at batch 8, context 2048 (GPT-2 style 50M, random weights)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": round(value / BASELINE_T4_DECODE_B8, 2),
+        "baseline_note": "published reference number is Tesla T4 fp16 at context 8..40 (1671.8 tok/s)",
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
+        "impl": "ours",
+        "config": {
+            "model": "gpt2-style-50M", "global_batch": args.batch, "seq_len": args.context,
+            "parallelism": "single-gpu", "n_layer": args.layers, "n_layer_config": MODEL["n_layer"],
+            "n_embd": cfg.n_embd, "n_head": cfg.n_head, "head_dim": cfg.head_dim,
+            "n_inner": cfg.n_inner, "vocab_size": cfg.vocab_size, "n_positions": cfg.n_positions,
+            "bias": cfg.bias, "tied_head": True, "page_tokens": args.page_tokens,
+            "l2": "flushed between timed steps (256 MiB write)", "weights": "random seed 0",
+            "mean_context": mean_ctx, "peaks": peak_source,
+        },
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "bytes_per_step": int(step_bytes), "of": peak_source},
+    }
+    if not args.no_points:
+        points = {}
+        for b in (1, 64):
+            _, t, _, _ = device_decode(args, b, min(args.steps, 32), max(3, min(args.warmup, 4)))
+            points[f"decode_b{b}"] = round(b / (statistics.fmean(t) * 1e-3), 1)
+        line["points"] = points
+        _, pre_ms = prefill_once(args)
+        flops = prefill_flops(cfg, PREFILL_TOKENS)
+        peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else None
+        line["prefill"] = {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                           "ms": round(pre_ms, 4),
+                           "frac": round(flops / (pre_ms * 1e-3) / (peak * 1e12), 4) if peak else None,
+                           "of": peak_source}
+    torch.cuda.synchronize()
+    return line
+
+
+# ---- the reference, unmodified, from baseline/_ref --------------------------------------------------
+def run_reference(args) -> dict:
+    ref_root = ROOT / "baseline" / "_ref"
+    if not (ref_root / "minigpt_infer").is_dir():
+        return {"impl": "reference",
+                "unavailable": "baseline/_ref is not installed (pip install --no-index --no-deps "
+                               "--target baseline/_ref of the reference has not been run here)"}
+    sys.path.insert(0, str(ref_root))
+    try:
+        import torch
+        from minigpt_infer.batch import ForwardBatch
+        from minigpt_infer.cache.static import StaticKVCache
+        from minigpt_infer.config import GPTConfig as RefConfig
+        from minigpt_infer.model import GPT
+    except Exception as exc:  # noqa: BLE001
+        return {"impl": "reference", "unavailable": f"reference import failed: {type(exc).__name__}: {exc}"}
+    if not torch.cuda.is_available():
+        return {"impl": "reference", "unavailable": "no CUDA device"}
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    torch.manual_seed(0)
+    cfg = RefConfig(vocab_size=MODEL["vocab_size"], block_size=args.context, n_layer=args.layers,
+                    n_head=MODEL["n_head"], n_embd=MODEL["n_embd"], dropout=0.0, bias=MODEL["bias"])
+    model = GPT(cfg).to(device="cuda", dtype=dtype).eval()
+    batch, steps, warmup = args.batch, args.steps, args.warmup
+    prompt_len = args.context - (steps + warmup)
+    gen = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, cfg.vocab_size, (batch, prompt_len), generator=gen).cuda()
+    sampler = ClockSampler(0)
+    with torch.no_grad():
+        # the reference's decode-only timing (bench/bench_hardware.py:63-92): prefill untimed,
+        # then one forward per token on the static cache, argmax on the device
+        cache = StaticKVCache(n_layer=cfg.n_layer, n_head=cfg.n_head, head_dim=model.head_dim,
+                              max_batch_size=batch, max_seq_len=cfg.block_size, device="cuda", dtype=dtype)
+        pos = torch.arange(prompt_len, device="cuda").unsqueeze(0).expand(batch, -1)
+        logits = model(ForwardBatch(input_ids=prompt, position_ids=pos, is_prefill=True, cache=cache))
+        cache.advance(prompt_len, batch)
+        flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+        times, wall = [], 0.0
+        sampler.start()
+        for step in range(steps + warmup):
+            flush.zero_()
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.perf_counter()
+            start.record()
+            next_id = torch.argmax(logits, dim=-1, keepdim=True)
+            cur_len = int(cache.seq_lens[0].item())
+            p = torch.full((batch, 1), cur_len, device="cuda", dtype=torch.long)
+            logits = model(ForwardBatch(input_ids=next_id, position_ids=p, is_prefill=False, cache=cache))
+            cache.advance(1, batch)
+            end.record()
+            host_ids = next_id.cpu()
+            torch.cuda.synchronize()
+            if step >= warmup:
+                times.append(start.elapsed_time(end))
+                wall += time.perf_counter() - t0
+        clocks = sampler.stop()
+        assert host_ids.shape == (batch, 1)
+    ms = statistics.fmean(times)
+    return {
+        "metric": "decode tok/s at batch 8, context 2048 (GPT-2 style 50M, random weights)",
+        "value": round(batch / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": round(batch / (ms * 1e-3) / BASELINE_T4_DECODE_B8, 2),
+        "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic", "impl": "reference",
+        "config": {"model": "gpt2-style-50M", "global_batch": batch, "seq_len": args.context,
+                   "parallelism": "single-gpu", "n_layer": args.layers, "n_layer_config": MODEL["n_layer"],
+                   "path": "GPT + StaticKVCache, eager (bench/bench_hardware.py method)",
+                   "l2": "flushed between timed steps (256 MiB write)"},
+        "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": 0, "d2h_bytes_per_step": batch * 8},
+        "gpu_launches": 0, "clocks": clocks,
+    }
+
+
+def main() -> int:
+    args = parse_args()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.context - args.steps - args.warmup - 80 < 2:
+        print("steps + warmup must leave room for a prompt inside the context", file=sys.stderr)
+        return 2
+    line = run_reference(args) if args.impl == "reference" else run_ours(args)
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -56,6 +56,7 @@ class ModelRunner:
         self.max_pages = manager.max_pages_per_request(self.max_context)
         self._pinned = None
         self._pinned_size = 0
+        self.last_h2d_bytes = 0          # bytes of the last step's one host-to-device copy
 
     # ---- requests ---------------------------------------------------------------------
     def length_of(self, request_id: str) -> int:
@@ -177,6 +178,7 @@ class ModelRunner:
             decode_only=all(n == 1 for n in host_q_len), storage=self.storage)
 
     def _to_device(self, buf: np.ndarray, total: int) -> torch.Tensor:
+        self.last_h2d_bytes = 4 * total
         if self.device.type != "cuda":
             return torch.from_numpy(buf[:total].copy())
         if self._pinned is None or self._pinned_size < total:

@@ -42,8 +42,14 @@ class CudaOps:
                 f"device {self.index} has compute capability {arch / 10:.1f}; the kernels "
                 "are built for sm_100a (NVIDIA B200) only")
         check(self.lib.mg_set_device(self.index), "set device")
+        self.launches = 0          # kernels launched through this object
 
     # ---- helpers --------------------------------------------------------------------------
+    def _run(self, code: int, what: str) -> None:
+        """Check a launch's return code and count it."""
+        check(code, what)
+        self.launches += 1
+
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
@@ -77,7 +83,7 @@ class CudaOps:
                 raise KernelLibraryError("embed: position table and embedding differ in width")
         n, width = token_ids.numel(), tok_emb.shape[1]
         out = torch.empty((n, width), dtype=torch.float32, device=self.device)
-        check(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
+        self._run(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
                                 _ptr(out), n, width, self._is_bf16(tok_emb), self._stream()),
               "embed")
         return out
@@ -91,7 +97,7 @@ class CudaOps:
         if gain.numel() != width:
             raise KernelLibraryError("layernorm: gain does not match the width")
         out = torch.empty((rows, width), dtype=out_dtype, device=self.device)
-        check(self.lib.mg_layernorm(_ptr(x32), _ptr(gain), _ptr(shift), _ptr(out), rows, width,
+        self._run(self.lib.mg_layernorm(_ptr(x32), _ptr(gain), _ptr(shift), _ptr(out), rows, width,
                                     float(eps), self._is_bf16(out), self._stream()), "layernorm")
         return out
 
@@ -99,7 +105,7 @@ class CudaOps:
         self._want(x32, torch.float32, "gather input", 2)
         self._want(rows, torch.int32, "rows", 1)
         out = torch.empty((rows.numel(), x32.shape[1]), dtype=torch.float32, device=self.device)
-        check(self.lib.mg_gather_rows(_ptr(x32), _ptr(rows), _ptr(out), rows.numel(), x32.shape[1],
+        self._run(self.lib.mg_gather_rows(_ptr(x32), _ptr(rows), _ptr(out), rows.numel(), x32.shape[1],
                                       self._stream()), "gather_rows")
         return out
 
@@ -115,7 +121,7 @@ class CudaOps:
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
-        check(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+        self._run(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                       m, n, k, epilogue, self._is_bf16(x), out_bf16, self._stream()),
               "linear")
 
@@ -145,7 +151,7 @@ class CudaOps:
             raise KernelLibraryError("kv_store: qkv width does not match the head sizes")
         if tuple(cache.k_pages.shape[1:]) != (n_kv_head, cache.page_tokens, head_dim):
             raise KernelLibraryError("kv_store: page storage does not match the head sizes")
-        check(self.lib.mg_kv_store(_ptr(qkv), _ptr(slot_mapping), _ptr(cache.k_pages),
+        self._run(self.lib.mg_kv_store(_ptr(qkv), _ptr(slot_mapping), _ptr(cache.k_pages),
                                    _ptr(cache.v_pages), qkv.shape[0], n_head, n_kv_head, head_dim,
                                    cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
 
@@ -154,7 +160,7 @@ class CudaOps:
         table = self._want(ctx.block_tables[cache.group], torch.int32, "block_table", 2)
         n = qkv.shape[0]
         out = torch.empty((n, n_head * head_dim), dtype=qkv.dtype, device=self.device)
-        check(self.lib.mg_paged_attention_generic(
+        self._run(self.lib.mg_paged_attention_generic(
             _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
             _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,
             cache.page_tokens, table.shape[1], int(cache.window or 0), float(scale),
@@ -165,7 +171,7 @@ class CudaOps:
     def argmax(self, logits, vocab_limit=None):
         self._want(logits, torch.float32, "logits", 2)
         out = torch.empty((logits.shape[0],), dtype=torch.int32, device=self.device)
-        check(self.lib.mg_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
+        self._run(self.lib.mg_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
                                  int(vocab_limit or 0), self._stream()), "argmax")
         return out
 
@@ -186,7 +192,7 @@ class CudaOps:
             if t is not None and t.numel() != rows:
                 raise KernelLibraryError("sample: per-row parameters do not match the rows")
         out = torch.empty((rows,), dtype=torch.int32, device=self.device)
-        check(self.lib.mg_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
+        self._run(self.lib.mg_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
                                  _ptr(seed_lo), _ptr(seed_hi), _ptr(counter), _ptr(out), rows,
                                  logits.shape[1], int(vocab_limit or 0), self._stream()), "sample")
         return out
