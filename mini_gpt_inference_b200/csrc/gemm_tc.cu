@@ -1,0 +1,403 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: TMA -> shared memory ->
+// tcgen05.mma -> TMEM -> epilogue.
+//
+//   D[p, q] = sum_k P[p, k] * Q[q, k]        P: [rows_p, K], Q: [rows_q, K], both K-major bf16
+//
+// One CTA computes a 128 x BN tile of D.  Thread 0 is the producer: it arms a "full"
+// mbarrier with the bytes to come and issues two TMA tile loads (128 x 64 of P, BN x 64 of
+// Q, 128-byte swizzle) per k block into a ring of stages.  Thread 32 is the issuer: it waits
+// for a stage, issues four tcgen05.mma (K = 16 each) whose 32-bit accumulator lives in TMEM,
+// and commits them to the stage's "empty" mbarrier, which frees the stage when the tensor
+// core has read it.  After the last k block a commit to a third barrier tells all four warps
+// that the accumulator is complete; each warp reads its 32 TMEM lanes with tcgen05.ld and
+// applies the epilogue: bias, tanh-GELU, conversion, or an add into the 32-bit residual
+// stream.  Edges need no special case on the load side: TMA fills what lies outside the
+// matrices with zeros (also a K that is no multiple of 64); stores are predicated.
+//
+// Two orientations share the kernel.  For many tokens, P is the activations and Q the weights
+// (a thread ends up with one token's row of features).  For a few tokens (decoding), P is
+// the weights and Q the activations: the 128 rows of the tensor-core tile are filled with
+// weight rows and the batch sits on the narrow side (BN = 16, 32 or 64), so no tensor-core
+// work is wasted on padding and a CTA streams 128 x K weights.
+//
+// Every wait on an mbarrier is bounded.  If one runs out, the kernel records a code in
+// `status`, skips the rest of its work, waits a moment for copies in flight, frees its TMEM
+// and returns; the host reads `status` later.  No thread-block clusters and no multicast
+// are used: each CTA loads its own tiles.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define EPI_STORE 0
+#define EPI_GELU 1
+#define EPI_RESIDUAL 2
+
+namespace {
+
+constexpr int TILE_P = 128;         // rows of P per CTA = UMMA M
+constexpr int BLOCK_K = 64;         // bf16 elements per k block = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int MAX_STAGES = 8;
+constexpr uint32_t SPIN_LIMIT = 2000000u;
+constexpr int P_TILE_BYTES = TILE_P * BLOCK_K * 2;
+
+// ---- PTX wrappers ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Bounded wait for the phase with the given parity.  False if it never completed.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t holder, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(cols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrive on an mbarrier once all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane (base lane + t), 32 columns.
+__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzle:
+// start address / 16, leading offset unused (1), 1024 bytes between groups of 8 rows,
+// descriptor version 1 (Blackwell), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
+    d |= (uint64_t)1u << 16;
+    d |= (uint64_t)(1024u >> 4) << 32;
+    d |= (uint64_t)1u << 46;
+    d |= (uint64_t)2u << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: D = F32 (bits 4-5 = 1), A = B = BF16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N / 8 in bits 17-22, M / 16 in bits 24-28.
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+struct __align__(8) Barriers {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t accumulator;
+    uint32_t tmem_base;
+    uint32_t failed;
+};
+
+template <int BN, bool SWAP>
+__global__ void __launch_bounds__(128)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               const float* __restrict__ bias, void* __restrict__ out_ptr, float* __restrict__ residual,
+               int rows_p, int rows_q, int K, int ld_out, int epilogue, int out_bf16, int stages,
+               int* __restrict__ status) {
+    constexpr int Q_TILE_BYTES = BN * BLOCK_K * 2;
+    constexpr int STAGE_BYTES = P_TILE_BYTES + Q_TILE_BYTES;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    extern __shared__ uint8_t smem_raw[];
+    // 128-byte swizzle wants tiles aligned to 1024 bytes
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    Barriers* bars = (Barriers*)(smem + (size_t)stages * STAGE_BYTES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int p0 = blockIdx.x * TILE_P, q0 = blockIdx.y * BN;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+
+    if (tid == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(smem_u32(&bars->full[s]), 1);
+            mbar_init(smem_u32(&bars->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&bars->accumulator), 1);
+        bars->failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(&bars->tmem_base), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+
+    if (tid == 0) {
+        // ---- producer: TMA loads into the ring of stages ----
+        for (int kb = 0; kb < num_kb; ++kb) {
+            const int s = kb % stages;
+            if (!mbar_wait(smem_u32(&bars->empty[s]), ((kb / stages) & 1) ^ 1)) {
+                atomicExch(status, 1);
+                bars->failed = 1;
+                break;
+            }
+            const uint32_t full = smem_u32(&bars->full[s]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+            tma_load_2d(smem_u32(stage), &map_p, full, kb * BLOCK_K, p0);
+            tma_load_2d(smem_u32(stage + P_TILE_BYTES), &map_q, full, kb * BLOCK_K, q0);
+        }
+    } else if (tid == 32) {
+        // ---- issuer: tcgen05.mma over the stages, accumulator in TMEM ----
+        constexpr uint32_t idesc = instr_desc_bf16(TILE_P, BN);
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+            const int s = kb % stages;
+            if (!mbar_wait(smem_u32(&bars->full[s]), (kb / stages) & 1)) {
+                atomicExch(status, 2);
+                bars->failed = 1;
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+            const uint64_t desc_p = smem_desc_sw128(smem_u32(stage));
+            const uint64_t desc_q = smem_desc_sw128(smem_u32(stage + P_TILE_BYTES));
+#pragma unroll
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+                // 16 elements further along K: 32 bytes inside the swizzled row
+                const uint64_t step = (uint64_t)((k * UMMA_K * 2) >> 4);
+                umma_bf16(tmem_base, desc_p + step, desc_q + step, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(smem_u32(&bars->empty[s]));
+        }
+        umma_commit(smem_u32(&bars->accumulator));
+    }
+    __syncwarp();
+
+    // ---- epilogue: all four warps, each on its own 32 lanes of TMEM ----
+    bool good = mbar_wait(smem_u32(&bars->accumulator), 0);
+    if (!good) atomicExch(status, 3);
+    good = good && (*(volatile uint32_t*)&bars->failed == 0);
+    good = __all_sync(0xffffffffu, good);               // tcgen05.ld needs the whole warp
+    tc_fence_after();
+    if (good) {
+        const int p = p0 + warp * 32 + lane;             // this thread's row of D
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        constexpr int CHUNK = BN < 32 ? BN : 32;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CHUNK) {
+            if (q0 + c0 >= rows_q) break;                 // uniform over the CTA
+            uint32_t r[32];
+            if (CHUNK == 32) tmem_load_32(lane_addr + (uint32_t)c0, r);
+            else tmem_load_16(lane_addr + (uint32_t)c0, r);
+            tmem_wait_ld();
+            if (p < rows_p) {
+                if (!SWAP) {
+                    // p is a token, q runs over features: contiguous in the output row
+                    const size_t row = (size_t)p * ld_out;
+#pragma unroll
+                    for (int j = 0; j < CHUNK; ++j) {
+                        const int q = q0 + c0 + j;
+                        if (q < rows_q) {
+                            float v = __uint_as_float(r[j]) + (bias ? bias[q] : 0.f);
+                            if (epilogue == EPI_GELU) v = gelu_tanh(v);
+                            if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
+                            else if (out_bf16) ((bf16*)out_ptr)[row + q] = __float2bfloat16_rn(v);
+                            else ((float*)out_ptr)[row + q] = v;
+                        }
+                    }
+                } else {
+                    // p is a feature, q runs over tokens: a warp writes 32 neighbouring features
+                    const float b = bias ? bias[p] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < CHUNK; ++j) {
+                        const int q = q0 + c0 + j;
+                        if (q < rows_q) {
+                            float v = __uint_as_float(r[j]) + b;
+                            if (epilogue == EPI_GELU) v = gelu_tanh(v);
+                            const size_t idx = (size_t)q * ld_out + p;
+                            if (epilogue == EPI_RESIDUAL) residual[idx] += v;
+                            else if (out_bf16) ((bf16*)out_ptr)[idx] = __float2bfloat16_rn(v);
+                            else ((float*)out_ptr)[idx] = v;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (tid == 0) {
+        // something timed out: give copies that may still be in flight a moment to land
+        for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- host side -----------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    int rows, k, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& m) const {
+        size_t h = std::hash<const void*>()(m.ptr);
+        h = h * 1000003u ^ (size_t)m.rows;
+        h = h * 1000003u ^ (size_t)m.k;
+        return h * 1000003u ^ (size_t)m.box_rows;
+    }
+};
+
+// Tensor map of a row-major [rows, k] bfloat16 matrix, boxes of box_rows x 64, 128-byte swizzle.
+int tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    MapKey key{ptr, rows, k, box_rows};
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return MG_OK; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return mg_set_error(MG_ERR_CUDA, "linear: cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return mg_set_error(MG_ERR_CUDA, "linear: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    if (cache.size() > 8192) cache.clear();
+    cache.emplace(key, *out);
+    return MG_OK;
+}
+
+template <int BN, bool SWAP>
+int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const float* bias, void* out,
+           float* residual, int ld_out, int epilogue, int out_bf16, int* status, cudaStream_t s) {
+    CUtensorMap map_p, map_q;
+    int rc = tensor_map(p, rows_p, K, TILE_P, &map_p);
+    if (rc != MG_OK) return rc;
+    rc = tensor_map(q, rows_q, K, BN, &map_q);
+    if (rc != MG_OK) return rc;
+    constexpr int stage_bytes = P_TILE_BYTES + BN * BLOCK_K * 2;
+    const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > num_kb) stages = num_kb;
+    const size_t smem = (size_t)stages * stage_bytes + sizeof(Barriers) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear: cannot raise shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    dim3 grid(ceil_div(rows_p, TILE_P), ceil_div(rows_q, BN));
+    gemm_tc_kernel<BN, SWAP><<<grid, 128, smem, s>>>(map_p, map_q, bias, out, residual, rows_p, rows_q, K, ld_out,
+                                                    epilogue, out_bf16, stages, status);
+    MG_CHECK_LAUNCH("gemm_tc");
+    return MG_OK;
+}
+
+}  // namespace
+
+// x: [M, K] bf16, w: [N, K] bf16 (both row-major).  Epilogues as mg_linear_simt.  `status` is a
+// device int that receives a non-zero code if a wait inside the kernel ran out.
+// Returns MG_ERR_UNSUPPORTED (and launches nothing) for sizes or alignments TMA cannot take:
+// K not a multiple of 8, pointers not 16-byte aligned.
+MG_API int mg_linear_tc(const void* x, const void* w, const float* bias, void* out, float* residual, int M,
+                        int N, int K, int epilogue, int out_bf16, int* status, void* stream) {
+    if (M == 0) return MG_OK;
+    MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
+    MG_REQUIRE(status != nullptr, "linear: missing status word");
+    if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+        return mg_set_error(MG_ERR_UNSUPPORTED, "linear: tensor-core path needs K %% 8 == 0 and 16-byte aligned operands");
+    cudaStream_t s = (cudaStream_t)stream;
+    if (M <= 64) {
+        // few tokens: weight rows fill the 128-row side of the tile, the batch sits on the narrow side
+        if (ceil_div(N, TILE_P) > 2147483647) return mg_set_error(MG_ERR_ARG, "linear: N too large");
+        if (M <= 16) return launch<16, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+        if (M <= 32) return launch<32, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+        return launch<64, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+    }
+    MG_REQUIRE(ceil_div(N, 64) <= 65535, "linear: N too large for one launch (%d)", N);
+    if (N <= 64 || (long long)ceil_div(M, TILE_P) * ceil_div(N, 128) < 120)
+        return launch<64, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+    return launch<128, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+}

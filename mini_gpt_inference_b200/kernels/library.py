@@ -24,10 +24,14 @@ _SIGNATURES = {
     "mg_gather_rows": [_P, _P, _P, _I, _I, _P],
     "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
+
+
+UNSUPPORTED = -3     # a kernel refused the sizes; the caller may take another path
 
 
 class KernelLibraryError(RuntimeError):

@@ -43,6 +43,9 @@ class CudaOps:
                 "are built for sm_100a (NVIDIA B200) only")
         check(self.lib.mg_set_device(self.index), "set device")
         self.launches = 0          # kernels launched through this object
+        # Kernels with bounded waits record a non-zero code here if a wait ran out.
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.use_tensor_cores = True
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -71,6 +74,13 @@ class CudaOps:
         if t.dtype == torch.float32:
             return 0
         raise KernelLibraryError(f"dtype {t.dtype} is neither bfloat16 nor float32")
+
+    def check_status(self) -> None:
+        """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
 
     # ---- embedding and norms --------------------------------------------------------------------
     def embed(self, token_ids, positions, tok_emb, pos_table):
@@ -121,6 +131,13 @@ class CudaOps:
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
+        if x.dtype == torch.bfloat16 and self.use_tensor_cores:
+            code = self.lib.mg_linear_tc(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                         m, n, k, epilogue, out_bf16, _ptr(self.status),
+                                         self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "linear (tensor cores)")
+                return
         self._run(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                       m, n, k, epilogue, self._is_bf16(x), out_bf16, self._stream()),
               "linear")

@@ -61,7 +61,9 @@ def test_layernorm(ops, dtype, rows, width, eps, bias):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("m,n,k", [(1, 509, 96), (45, 200, 96), (130, 96, 200), (64, 1536, 512),
-                                   (3, 77, 33), (257, 65, 129)])
+                                   (3, 77, 33), (257, 65, 129), (8, 50304, 512), (300, 2048, 512),
+                                   (2048, 512, 2048), (17, 1536, 512), (33, 512, 2048),
+                                   (65, 1536, 512), (128, 128, 64), (129, 130, 72), (16, 16, 8)])
 def test_linear_and_epilogues(ops, dtype, m, n, k):
     x = randn(m, k, dtype=dtype, seed=6)
     w = randn(n, k, dtype=dtype, seed=7, scale=1 / math.sqrt(k))
@@ -78,6 +80,24 @@ def test_linear_and_epilogues(ops, dtype, m, n, k):
     before = res.clone()
     ops.linear_residual(x, w, b, res)
     assert (res.double() - (before.double() + ref + b.double())).abs().max() <= 3e-5
+    ops.check_status()
+
+
+def test_tensor_core_and_cuda_core_products_agree(ops):
+    """The tcgen05 path and the plain FMA path compute the same sums from the same bfloat16
+    inputs; with 32-bit output they differ only by the order of the additions."""
+    for m, n, k in [(5, 300, 512), (200, 136, 200), (64, 50304, 512), (1000, 1536, 512)]:
+        x = randn(m, k, dtype=torch.bfloat16, seed=11)
+        w = randn(n, k, dtype=torch.bfloat16, seed=12, scale=1 / math.sqrt(k))
+        ops.use_tensor_cores = True
+        before = ops.launches
+        fast = ops.logits(x, w)
+        ops.use_tensor_cores = False
+        slow = ops.logits(x, w)
+        ops.use_tensor_cores = True
+        assert ops.launches == before + 2
+        assert (fast - slow).abs().max() <= 1e-5, (m, n, k)
+    ops.check_status()
 
 
 def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window, lengths, q_lens,
