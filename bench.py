@@ -207,7 +207,7 @@ def device_decode(args, batch: int, steps: int, warmup: int):
             torch.cuda.synchronize()
             launches_before = getattr(runner.ops, "launches", 0)
         start.record()
-        logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)])
+        logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
         ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch)
         end.record()
         last = ids.tolist()                            # device -> host: the step's result

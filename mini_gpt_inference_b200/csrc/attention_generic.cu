@@ -34,6 +34,11 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     const int kv_head = head / (n_head / n_kv_head);
     const int qkv_width = (n_head + 2 * n_kv_head) * head_dim;
     const int p = positions[token];
+    if (p < 0) {                                           // padding row of a fixed-size batch
+        T* pad = out + (size_t)token * n_head * head_dim + (size_t)head * head_dim;
+        for (int d = lane; d < head_dim; d += 32) pad[d] = from_float<T>(0.f);
+        return;
+    }
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int* table = block_table + (size_t)token_request[token] * max_pages;
 

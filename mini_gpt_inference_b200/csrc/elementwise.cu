@@ -3,14 +3,19 @@
 
 // ---- embedding + learned position add ---------------------------------------------------
 // x[n, :] = tok_emb[id[n], :] + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
+// A row with a negative position is padding of a fixed-size batch: it becomes zeros.
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ tok, const TW* __restrict__ ptab,
                              float* __restrict__ out, int width) {
     const int n = blockIdx.x;
+    float* orow = out + (size_t)n * width;
+    if (pos[n] < 0) {
+        for (int c = threadIdx.x; c < width; c += blockDim.x) orow[c] = 0.f;
+        return;
+    }
     const TW* trow = tok + (size_t)ids[n] * width;
     const TW* prow = ptab ? ptab + (size_t)pos[n] * width : nullptr;
-    float* orow = out + (size_t)n * width;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = to_float(trow[c]);
         if (prow) v += to_float(prow[c]);

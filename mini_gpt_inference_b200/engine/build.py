@@ -47,7 +47,8 @@ def load_model(model_dir: str | Path | None = None, *, config=None, tensors=None
 
 
 def make_runner(loaded: LoadedModel, ops, page_tokens: int, num_pages: int,
-                max_requests: int) -> ModelRunner:
+                max_requests: int, use_cuda_graphs: bool = True) -> ModelRunner:
     manager = CacheManager(loaded.model.cache_specs(), page_tokens, num_pages, max_requests)
     storage = CacheStorage(manager, loaded.dtype, loaded.device)
-    return ModelRunner(loaded.model, manager, storage, ops, loaded.dtype, loaded.device)
+    return ModelRunner(loaded.model, manager, storage, ops, loaded.dtype, loaded.device,
+                       use_cuda_graphs=use_cuda_graphs)

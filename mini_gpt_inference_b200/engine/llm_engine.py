@@ -39,7 +39,7 @@ class LLMEngine:
         self.config = loaded.config
         self.runner: ModelRunner = make_runner(
             loaded, ops, self.engine_cfg.block_size, self.engine_cfg.num_blocks,
-            self.engine_cfg.max_batch_size)
+            self.engine_cfg.max_batch_size, self.engine_cfg.use_cuda_graphs)
         self.scheduler = Scheduler(self.runner.manager, self.engine_cfg.max_batch_size,
                                    self.engine_cfg.max_num_batched_tokens,
                                    self.engine_cfg.prefill_chunk)
@@ -95,7 +95,7 @@ class LLMEngine:
             return []
         entries = [StepEntry(c.seq.request_id, c.seq.tokens(c.start, c.count),
                              [c.count - 1] if c.samples else []) for c in chunks]
-        logits = self.runner.step(entries)
+        logits = self.runner.step(entries, copy=False)      # sampled before the next step
         self.num_steps += 1
         self.num_tokens_run += sum(c.count for c in chunks)
         for c in chunks:

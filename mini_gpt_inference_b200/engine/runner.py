@@ -38,9 +38,26 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=list)
 
 
+@dataclass
+class _DecodeGraph:
+    """One captured decode step for a fixed number of rows: its static inputs and outputs."""
+
+    rows: int
+    offsets: list
+    meta: torch.Tensor            # device int32: every integer input of the step
+    staging: torch.Tensor         # pinned host copy that is filled each step
+    ctx: StepContext
+    graph: object = None
+    logits: torch.Tensor | None = None
+    kernels: int = 0              # kernel launches inside the graph
+
+
 class ModelRunner:
+    GRAPH_ROWS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
-                 ops, act_dtype: torch.dtype, device, max_context: int | None = None) -> None:
+                 ops, act_dtype: torch.dtype, device, max_context: int | None = None,
+                 use_cuda_graphs: bool = True) -> None:
         self.model = model
         self.manager = manager
         self.storage = storage
@@ -57,6 +74,15 @@ class ModelRunner:
         self._pinned = None
         self._pinned_size = 0
         self.last_h2d_bytes = 0          # bytes of the last step's one host-to-device copy
+        # Steps in which every request brings one token have a fixed shape once the batch is
+        # padded to a few sizes: they are captured as CUDA graphs and replayed (the reference
+        # shows the gain on its own decode step, src/minigpt_infer/graphs.py:96-116).
+        self.use_cuda_graphs = (use_cuda_graphs and self.device.type == "cuda"
+                                and all(getattr(p, "graph_safe", False) for p in model.parts()))
+        self._graphs: dict[int, _DecodeGraph] = {}
+        self._graph_pool = None
+        self._copy_done = None
+        self.graph_replays = 0
 
     # ---- requests ---------------------------------------------------------------------
     def length_of(self, request_id: str) -> int:
@@ -190,16 +216,121 @@ class ModelRunner:
         self._pinned[:total].numpy()[:] = buf[:total]
         return self._pinned[:total].to(self.device, non_blocking=True)
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+    # ---- decode steps as CUDA graphs ---------------------------------------------------------
+    def _graph_layout(self, rows: int):
+        g, pages = len(self.manager.groups), self.max_pages
+        sizes = [rows] * 8 + [rows * pages] * g + [rows] * g
+        offsets = [0]
+        for n in sizes:
+            offsets.append(offsets[-1] + n)
+        return offsets
+
+    def _capture(self, rows: int) -> _DecodeGraph:
+        g, pages = len(self.manager.groups), self.max_pages
+        offsets = self._graph_layout(rows)
+        meta = torch.zeros(offsets[-1], dtype=torch.int32, device=self.device)
+        staging = torch.zeros(offsets[-1], dtype=torch.int32, pin_memory=True)
+
+        def seg(i):
+            return meta[offsets[i]: offsets[i + 1]]
+
+        ctx = StepContext(
+            ops=self.ops, act_dtype=self.act_dtype, num_tokens=rows, num_requests=rows,
+            token_ids=seg(0), positions=seg(1), token_request=seg(2), req_q_start=seg(3),
+            req_q_len=seg(4), req_ctx_before=seg(5), req_state_slot=seg(6), logit_rows=seg(7),
+            block_tables=[seg(8 + i).view(rows, pages) for i in range(g)],
+            slot_mapping=[seg(8 + g + i) for i in range(g)],
+            host_q_len=[1] * rows, host_ctx_before=[0] * rows, host_state_slot=[0] * rows,
+            max_q_len=1, max_ctx_after=self.max_context, decode_only=True, storage=self.storage)
+        state = _DecodeGraph(rows, offsets, meta, staging, ctx)
+        self._fill_graph_inputs(state, [])                # all rows are padding: nothing is written
+        meta.copy_(staging)
+        self.model.forward(ctx)                           # warm-up outside the capture
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        launches = getattr(self.ops, "launches", 0)
+        with torch.cuda.graph(graph, pool=self._graph_pool):
+            state.logits = self.model.forward(ctx)
+        state.kernels = getattr(self.ops, "launches", 0) - launches
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        state.graph = graph
+        return state
+
+    def _fill_graph_inputs(self, state: _DecodeGraph, entries: Sequence[StepEntry]) -> None:
+        m = self.manager
+        rows, off = state.rows, state.offsets
+        buf = state.staging.numpy()
+        g, pages, pt = len(m.groups), self.max_pages, m.page_tokens
+        buf[off[0]: off[1]] = 0                                         # token ids
+        buf[off[1]: off[2]] = -1                                        # position -1 marks padding
+        buf[off[2]: off[3]] = np.arange(rows, dtype=np.int32)           # request of each row
+        buf[off[3]: off[4]] = np.arange(rows, dtype=np.int32)
+        buf[off[4]: off[5]] = 0
+        buf[off[5]: off[6]] = 0
+        buf[off[6]: off[7]] = 0
+        buf[off[7]: off[8]] = np.arange(rows, dtype=np.int32)           # logits of every row
+        for i in range(g):
+            buf[off[8 + i]: off[9 + i]] = NO_PAGE
+            buf[off[8 + g + i]: off[9 + g + i]] = -1
+        for r, e in enumerate(entries):
+            req = m.get(e.request_id)
+            buf[off[0] + r] = int(e.tokens[0])
+            buf[off[1] + r] = req.length
+            buf[off[4] + r] = 1
+            buf[off[5] + r] = req.length
+            buf[off[6] + r] = req.state_slot
+            for i in range(g):
+                table = req.tables[i]
+                base = off[8 + i] + r * pages
+                buf[base: base + len(table)] = table
+                page = table[req.length // pt]
+                if page == NO_PAGE:
+                    raise StepError(f"request {e.request_id!r} writes to a page it gave back")
+                buf[off[8 + g + i] + r] = page * pt + req.length % pt
+
+    def _graph_step(self, entries: Sequence[StepEntry], copy: bool):
+        rows = next(b for b in self.GRAPH_ROWS if b >= len(entries))
+        state = self._graphs.get(rows)
+        if state is None:
+            state = self._graphs[rows] = self._capture(rows)
+        if self._copy_done is not None:
+            self._copy_done.synchronize()                 # the staging buffer is free again
+        self._fill_graph_inputs(state, entries)
+        state.meta.copy_(state.staging, non_blocking=True)
+        if self._copy_done is None:
+            self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+        self.last_h2d_bytes = 4 * state.offsets[-1]
+        state.graph.replay()
+        self.graph_replays += 1
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += state.kernels
+        wanted = [r for r, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return None
+        if len(wanted) == len(entries):
+            logits = state.logits[: len(entries)]
+        else:
+            logits = state.logits[wanted]
+            copy = False
+        return logits.clone() if copy else logits
+
+    def step(self, entries: Sequence[StepEntry], copy: bool = True) -> torch.Tensor | None:
         """Run the entries as one batch.  Returns ``[wanted, vocab]`` float32 logits on the
-        device (None if nothing was wanted)."""
+        device (None if nothing was wanted).  With ``copy=False`` the result may be a view of
+        a buffer that the next step overwrites."""
         entries = list(entries)
         if not entries:
             return None
         self._validate(entries)
         self._reserve(entries)
-        ctx = self.build_context(entries)
-        logits = self.model.forward(ctx)
+        if (self.use_cuda_graphs and len(entries) <= self.GRAPH_ROWS[-1]
+                and all(len(e.tokens) == 1 for e in entries)):
+            logits = self._graph_step(entries, copy)
+        else:
+            ctx = self.build_context(entries)
+            logits = self.model.forward(ctx)
         for e in entries:
             self.manager.advance(e.request_id, self.manager.get(e.request_id).length + len(e.tokens))
         return logits

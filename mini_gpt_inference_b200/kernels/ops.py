@@ -46,6 +46,7 @@ class CudaOps:
         # Kernels with bounded waits record a non-zero code here if a wait ran out.
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tensor_cores = True
+        self.use_split_attention = True
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -172,15 +173,31 @@ class CudaOps:
                                    _ptr(cache.v_pages), qkv.shape[0], n_head, n_kv_head, head_dim,
                                    cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
 
+    SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
+
     def paged_attention(self, qkv, n_head, n_kv_head, head_dim, scale, cache, ctx):
         self._want(qkv, cache.k_pages.dtype, "qkv", 2)
         table = self._want(ctx.block_tables[cache.group], torch.int32, "block_table", 2)
         n = qkv.shape[0]
         out = torch.empty((n, n_head * head_dim), dtype=qkv.dtype, device=self.device)
+        window = int(cache.window or 0)
+        if (qkv.dtype == torch.bfloat16 and getattr(ctx, "decode_only", False)
+                and head_dim in self.SPLIT_HEAD_DIMS and self.use_split_attention):
+            # single query tokens: split along the keys, merge afterwards
+            splits = self.lib.mg_attention_split_count(int(ctx.max_ctx_after), window)
+            floats = self.lib.mg_attention_split_scratch_floats(n, n_head, head_dim, splits)
+            scratch = torch.empty((floats,), dtype=torch.float32, device=self.device)
+            self._run(self.lib.mg_paged_attention_split(
+                _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
+                _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), _ptr(scratch), n, n_head,
+                n_kv_head, head_dim, cache.page_tokens, table.shape[1], window, splits, float(scale),
+                self._stream()), "paged_attention (split)")
+            self.launches += 1                      # two kernels: split and merge
+            return out
         self._run(self.lib.mg_paged_attention_generic(
             _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
             _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,
-            cache.page_tokens, table.shape[1], int(cache.window or 0), float(scale),
+            cache.page_tokens, table.shape[1], window, float(scale),
             self._is_bf16(qkv), self._stream()), "paged_attention")
         return out
 

@@ -25,6 +25,8 @@ from .spec import TensorSpec
 
 @register_mixer("causal_attention")
 class CausalAttention(Mixer):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str, width: int, n_head: int, head_dim: int, bias: bool,
                  n_kv_head: int | None = None, scale: float | None = None,
                  window: int | None = None, position=None) -> None:

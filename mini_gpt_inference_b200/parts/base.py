@@ -32,6 +32,9 @@ class Part:
     """Common behaviour: name the tensors wanted under a prefix, and take them."""
 
     kind = ""
+    # True if forward() only launches kernels whose arguments do not change from step to step
+    # (no host-side reads of the batch): such a part can be captured in a CUDA graph.
+    graph_safe = False
 
     def __init__(self, prefix: str = "") -> None:
         self.prefix = prefix

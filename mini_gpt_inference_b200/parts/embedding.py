@@ -14,6 +14,8 @@ from .spec import TensorSpec
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str, vocab_size: int, width: int) -> None:
         super().__init__(prefix)
         self.vocab_size, self.width = vocab_size, width
@@ -29,6 +31,8 @@ class TokenEmbedding(Part):
 
 @register_head("tied_head")
 class TiedHead(Part):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     """Output projection with the embedding's matrix.  A checkpoint may store it again
     under the head's own name; then it must equal the embedding."""
 

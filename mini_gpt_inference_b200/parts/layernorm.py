@@ -13,6 +13,8 @@ from .spec import TensorSpec
 
 @register_norm("layernorm")
 class LayerNorm(Norm):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str, width: int, eps: float, bias: bool) -> None:
         super().__init__(prefix)
         self.width, self.eps, self.has_bias = width, float(eps), bool(bias)

@@ -15,6 +15,8 @@ _ACTIVATIONS = {"gelu_tanh": "gelu_tanh", "gelu_new": "gelu_tanh", "gelu_pytorch
 
 @register_feed_forward("dense_mlp")
 class DenseMLP(FeedForward):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str, width: int, inner: int, bias: bool,
                  activation: str = "gelu_tanh") -> None:
         super().__init__(prefix)

@@ -13,6 +13,8 @@ from .spec import TensorSpec
 
 @register_position_encoding("learned_absolute")
 class LearnedAbsolutePositions(PositionEncoding):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str, n_positions: int, width: int) -> None:
         super().__init__(prefix)
         self.n_positions, self.width = n_positions, width
@@ -28,5 +30,7 @@ class LearnedAbsolutePositions(PositionEncoding):
 
 @register_position_encoding("none")
 class NoPositions(PositionEncoding):
+    graph_safe = True      # launches kernels only; nothing is decided on the host per step
+
     def __init__(self, prefix: str = "") -> None:
         super().__init__(prefix)

@@ -145,9 +145,12 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
                             group=0, page_tokens=page_tokens, window=window or None, writes=False)
     ctx = SimpleNamespace(block_tables=[tables.cuda()],
                           token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
-                          positions=torch.tensor(positions, dtype=torch.int32).cuda())
+                          positions=torch.tensor(positions, dtype=torch.int32).cuda(),
+                          decode_only=all(q == 1 for q in q_lens), max_ctx_after=max(lengths))
     qkv = torch.stack(qkv_rows).to(dtype).cuda()
+    before = ops.launches
     got = ops.paged_attention(qkv, n_head, n_kv_head, head_dim, scale, cache, ctx)
+    _attention_case.kernels = ops.launches - before
     return got.double().cpu(), torch.stack(want)
 
 
@@ -162,6 +165,28 @@ def test_paged_attention_general(ops, dtype, n_head, n_kv_head, head_dim, page_t
     got, want = _attention_case(ops, dtype, n_head, n_kv_head, head_dim, pt, window, lengths, q_lens)
     assert not torch.isnan(got).any(), "attention read a cache row beyond a request's length"
     assert (got - want).abs().max() <= _tol(dtype, 1.0)
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,window", [
+    (8, 8, 64, 16, 0), (8, 8, 64, 64, 0), (3, 3, 32, 8, 0), (6, 2, 16, 16, 0), (2, 2, 128, 16, 0),
+    (4, 2, 256, 64, 0), (4, 4, 32, 8, 5), (6, 3, 64, 16, 300)])
+def test_paged_attention_split_over_keys(ops, n_head, n_kv_head, head_dim, page_tokens, window):
+    """Single query tokens in bfloat16 take the kernel that splits the keys into blocks of 256
+    and merges: lengths around the block edges, one token, long contexts."""
+    lengths = [1, 2, 255, 256, 257, 511, 513, 700, 1025, page_tokens, page_tokens + 1]
+    got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, head_dim, page_tokens, window,
+                                lengths, [1] * len(lengths))
+    assert _attention_case.kernels == 2, "the split kernel and its merge were expected to run"
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max() <= _tol(torch.bfloat16, 1.0)
+    # the general kernel gives the same within rounding
+    ops.use_split_attention = False
+    try:
+        general, _ = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, head_dim, page_tokens, window,
+                                     lengths, [1] * len(lengths))
+    finally:
+        ops.use_split_attention = True
+    assert (general - got).abs().max() <= _tol(torch.bfloat16, 1.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -185,7 +210,8 @@ def test_far_key_among_hundreds_decides(ops, dtype):
                             page_tokens=pt, window=None, writes=False)
     ctx = SimpleNamespace(block_tables=[torch.arange(pages, dtype=torch.int32)[None].cuda()],
                           token_request=torch.zeros(1, dtype=torch.int32).cuda(),
-                          positions=torch.tensor([n - 1], dtype=torch.int32).cuda())
+                          positions=torch.tensor([n - 1], dtype=torch.int32).cuda(),
+                          decode_only=True, max_ctx_after=n)
     qkv = torch.cat([q.reshape(1, -1), torch.zeros(1, 2 * n_head * head_dim)], 1).to(dtype).cuda()
     got = ops.paged_attention(qkv, n_head, n_head, head_dim, 1 / math.sqrt(head_dim), cache, ctx)
     want = v[far].to(dtype).float().reshape(-1)
