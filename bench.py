@@ -43,8 +43,8 @@ PREFILL_TOKENS = 2048
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=MODEL["n_positions"])
@@ -72,61 +72,54 @@ def peaks() -> tuple[dict, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    """Samples the SM clock and the throttle reasons through NVML (read-only) every few
+    milliseconds while a region is timed."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+               "sw_power_cap": 0x4}
 
-    def __init__(self, index: int = 0) -> None:
-        self.index = index
-        self.proc = None
-        self.lines: list[str] = []
-        self.thread = None
+    def __init__(self, index: int = 0, period_s: float = 0.005) -> None:
+        self.index, self.period_s = index, period_s
+        self.sm: list[int] = []
+        self.reason_bits = 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
+        self._handle = None
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
-            return
-        self.thread = threading.Thread(target=self._read, daemon=True)
-        self.thread.start()
+            import pynvml
 
-    def _read(self) -> None:
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            pynvml.nvmlInit()
+            self._nvml = pynvml
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+        except Exception:  # noqa: BLE001 - no NVML: report that instead of clocks
+            self._nvml = None
+            return
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+
+    def _loop(self) -> None:
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.sm.append(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            except Exception:  # noqa: BLE001
+                pass
+            self._stop.wait(self.period_s)
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        if self.thread is not None:
-            self.thread.join(timeout=2)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[2:6]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None,
-                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        if self._nvml is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable"]}
+        self._stop.set()
+        self._thread.join(timeout=2)
+        reasons = sorted(k for k, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.sm) if self.sm else None,
+                "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(self.sm)}
 
 
 # ---- this engine ---------------------------------------------------------------------------------
@@ -179,7 +172,7 @@ def prefill_flops(cfg, tokens: int) -> float:
     return linear + attention + head
 
 
-def device_decode(args, batch: int, steps: int, warmup: int):
+def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None):
     """K decode steps of `batch` requests whose contexts end at args.context; device time."""
     import torch
 
@@ -206,6 +199,8 @@ def device_decode(args, batch: int, steps: int, warmup: int):
         if step == warmup:
             torch.cuda.synchronize()
             launches_before = getattr(runner.ops, "launches", 0)
+            if clock_sampler is not None:
+                clock_sampler.start()                   # clocks of the timed steps only
         start.record()
         logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
         ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch)
@@ -214,11 +209,12 @@ def device_decode(args, batch: int, steps: int, warmup: int):
         if step >= warmup:
             times.append(start.elapsed_time(end))
     torch.cuda.synchronize()
+    clocks = clock_sampler.stop() if clock_sampler is not None else None
     launches = getattr(runner.ops, "launches", 0) - launches_before
     for rid in rids:
         runner.finish(rid)
     mean_context = args.context - steps / 2.0
-    return cfg, times, launches, mean_context
+    return cfg, times, launches, mean_context, clocks
 
 
 def e2e_decode(args, batch: int, steps: int, warmup: int):
@@ -286,10 +282,8 @@ def run_ours(args) -> dict:
 
     pk, peak_source = peaks()
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4
-    sampler = ClockSampler(0)
-    sampler.start()
-    cfg, times, launches, mean_ctx = device_decode(args, args.batch, args.steps, args.warmup)
-    clocks = sampler.stop()
+    cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
+                                                           ClockSampler(0))
     ms = statistics.fmean(times)
     value = args.batch / (ms * 1e-3)
     step_bytes = weight_bytes(cfg, dtype_bytes) + kv_bytes(cfg, args.batch, mean_ctx, dtype_bytes)
@@ -323,7 +317,7 @@ def run_ours(args) -> dict:
     if not args.no_points:
         points = {}
         for b in (1, 64):
-            _, t, _, _ = device_decode(args, b, min(args.steps, 32), max(3, min(args.warmup, 4)))
+            _, t, _, _, _ = device_decode(args, b, min(args.steps, 64), max(3, min(args.warmup, 8)))
             points[f"decode_b{b}"] = round(b / (statistics.fmean(t) * 1e-3), 1)
         line["points"] = points
         _, pre_ms = prefill_once(args)

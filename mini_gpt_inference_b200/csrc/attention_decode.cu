@@ -27,6 +27,7 @@ namespace {
 constexpr int SPLIT_KEYS = 256;
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
+constexpr int UNROLL = 4;
 
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
@@ -75,23 +76,32 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         for (int i = 0; i < 8; ++i) q[i] *= scale_log2e;
     }
 
-    // ---- pass 1: scores ----
-    for (int base = warp * KPW; base < count; base += WARPS * KPW) {
-        const int j = base + grp;
-        float dot = 0.f;
-        if (j < count) {
-            const int pos = start + j;
-            const int page = table[pos / page_tokens];
-            const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
-            const uint4 raw = *reinterpret_cast<const uint4*>(k_pages + row * D + sub * 8);
-            float kf[8];
-            unpack8(raw, kf);
+    // ---- pass 1: scores ----  (UNROLL independent 16-byte loads per lane are in flight at once)
+    for (int base = warp * KPW; base < count; base += WARPS * KPW * UNROLL) {
+        uint4 raw[UNROLL];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dot = fmaf(q[i], kf[i], dot);
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = base + u * WARPS * KPW + grp;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < count) {
+                const int pos = start + j;
+                const int page = table[pos / page_tokens];
+                const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
+                raw[u] = *reinterpret_cast<const uint4*>(k_pages + row * D + sub * 8);
+            }
         }
 #pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (sub == 0 && j < count) scores[j] = dot;
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = base + u * WARPS * KPW + grp;
+            float kf[8];
+            unpack8(raw[u], kf);
+            float dot = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dot = fmaf(q[i], kf[i], dot);
+#pragma unroll
+            for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+            if (sub == 0 && j < count) scores[j] = dot;
+        }
     }
     __syncthreads();
 
@@ -122,16 +132,25 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int base = warp * KPW; base < count; base += WARPS * KPW) {
-        const int j = base + grp;
-        if (j < count) {
-            const int pos = start + j;
-            const int page = table[pos / page_tokens];
-            const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
-            const uint4 raw = *reinterpret_cast<const uint4*>(v_pages + row * D + sub * 8);
+    for (int base = warp * KPW; base < count; base += WARPS * KPW * UNROLL) {
+        uint4 raw[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = base + u * WARPS * KPW + grp;
+            raw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (j < count) {
+                const int pos = start + j;
+                const int page = table[pos / page_tokens];
+                const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
+                raw[u] = *reinterpret_cast<const uint4*>(v_pages + row * D + sub * 8);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int j = base + u * WARPS * KPW + grp;
             float vf[8];
-            unpack8(raw, vf);
-            const float pj = scores[j];
+            unpack8(raw[u], vf);
+            const float pj = j < count ? scores[j] : 0.f;
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[i] = fmaf(pj, vf[i], acc[i]);
         }

@@ -42,7 +42,70 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     }
 }
 
+// Stage 1 of the wide argmax: block (row, part) scans its slice of the row.
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_part_kernel(const float* __restrict__ logits, float* __restrict__ part_v, int* __restrict__ part_i,
+                   int vocab, int limit, int parts, int slice) {
+    __shared__ float best_v[ARGMAX_THREADS / 32];
+    __shared__ int best_i[ARGMAX_THREADS / 32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    const int begin = blockIdx.y * slice, end = min(limit, begin + slice);
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float x = row[i];
+        if (x > v || (x == v && i < idx)) { v = x; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { best_v[warp] = v; best_i[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < ARGMAX_THREADS / 32 ? best_v[lane] : -INFINITY;
+        idx = lane < ARGMAX_THREADS / 32 ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        if (lane == 0) {
+            part_v[(size_t)blockIdx.x * parts + blockIdx.y] = v;
+            part_i[(size_t)blockIdx.x * parts + blockIdx.y] = idx;
+        }
+    }
+}
+
+// Stage 2: one warp per row merges the parts.
+__global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int* __restrict__ out, int parts) {
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int k = threadIdx.x; k < parts; k += 32) {
+        const float x = part_v[(size_t)blockIdx.x * parts + k];
+        const int i = part_i[(size_t)blockIdx.x * parts + k];
+        if (x > v || (x == v && i < idx)) { v = x; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+}
+
+constexpr int ARGMAX_SLICE = 2048;
+
 }  // namespace
+
+// Parts a row is cut into by mg_argmax_wide; its scratch holds rows * parts floats and as many ints.
+MG_API int mg_argmax_parts(int vocab) { return (vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE; }
 
 // logits: [rows, vocab] 32-bit; ids >= limit are never chosen (limit <= 0: the whole vocabulary).
 MG_API int mg_argmax(const float* logits, int* out, int rows, int vocab, int limit, void* stream) {
@@ -51,6 +114,25 @@ MG_API int mg_argmax(const float* logits, int* out, int rows, int vocab, int lim
     if (limit <= 0 || limit > vocab) limit = vocab;
     argmax_kernel<<<rows, ARGMAX_THREADS, 0, (cudaStream_t)stream>>>(logits, out, vocab, limit);
     MG_CHECK_LAUNCH("argmax");
+    return MG_OK;
+}
+
+// The same result with many blocks per row, for wide vocabularies and few rows: a row is cut
+// into slices of 2048 ids, each scanned by a block; a second kernel merges.  The lowest index
+// among equal maxima wins, as in mg_argmax.  scratch_v / scratch_i: rows * mg_argmax_parts(vocab).
+MG_API int mg_argmax_wide(const float* logits, int* out, float* scratch_v, int* scratch_i, int rows, int vocab,
+                          int limit, void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && vocab > 0 && scratch_v && scratch_i, "argmax: bad arguments");
+    if (limit <= 0 || limit > vocab) limit = vocab;
+    const int parts = mg_argmax_parts(vocab);
+    MG_REQUIRE(parts <= 65535, "argmax: vocabulary too wide");
+    cudaStream_t s = (cudaStream_t)stream;
+    argmax_part_kernel<<<dim3(rows, parts), ARGMAX_THREADS, 0, s>>>(logits, scratch_v, scratch_i, vocab, limit, parts,
+                                                                  ARGMAX_SLICE);
+    MG_CHECK_LAUNCH("argmax (parts)");
+    argmax_merge_kernel<<<rows, 32, 0, s>>>(scratch_v, scratch_i, out, parts);
+    MG_CHECK_LAUNCH("argmax (merge)");
     return MG_OK;
 }
 

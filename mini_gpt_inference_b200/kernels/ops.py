@@ -14,6 +14,22 @@ from . import library
 from .library import KernelLibraryError, check
 
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
+SKINNY_ROWS = 8          # most tokens the small-batch projection kernel takes
+
+
+class DeferredNorm:
+    """A LayerNorm that has not run yet: the projection that consumes it may fuse it into its
+    prologue (small batches) or ask for it to be materialised.  ``rows`` optionally selects
+    rows of ``x32`` first."""
+
+    def __init__(self, ops, x32, gain, shift, eps, out_dtype, rows=None) -> None:
+        self.ops, self.x32, self.gain, self.shift, self.eps = ops, x32, gain, shift, float(eps)
+        self.dtype, self.rows = out_dtype, rows
+        self.shape = (x32.shape[0] if rows is None else rows.numel(), x32.shape[1])
+
+    def materialize(self):
+        x = self.x32 if self.rows is None else self.ops.gather_rows(self.x32, self.rows)
+        return self.ops.layernorm(x, self.gain, self.shift, self.eps, self.dtype)
 
 
 def _ptr(t):
@@ -47,6 +63,7 @@ class CudaOps:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tensor_cores = True
         self.use_split_attention = True
+        self.use_skinny = True
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -121,33 +138,79 @@ class CudaOps:
         return out
 
     # ---- projections ----------------------------------------------------------------------------
-    def _linear(self, x, weight, bias, epilogue, out, residual):
-        self._want(x, None, "linear input", 2)
-        self._want(weight, x.dtype, "linear weight", 2)
-        if bias is not None:
-            self._want(bias, torch.float32, "linear bias", 1)
+    def defer_layernorm(self, x32, gain, shift, eps, out_dtype, rows=None):
+        """A LayerNorm to be fused into the projection that consumes it, where that pays."""
+        self._want(x32, torch.float32, "layernorm input", 2)
+        return DeferredNorm(self, x32, gain, shift, eps, out_dtype, rows)
+
+    def _skinny_ok(self, m, k, dtype) -> bool:
+        return (self.use_skinny and dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0
+                and SKINNY_ROWS * k * 2 + 2048 <= 200 * 1024)
+
+    def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None):
+        """x: a tensor [M, K] or a DeferredNorm.  kv_sink: (cache view, slots, n_head, n_kv_head,
+        head_dim) to also write key/value features to the cache.  Returns True if the sink was
+        served inside the projection kernel."""
+        deferred = x if isinstance(x, DeferredNorm) else None
         m, k = x.shape
         n = weight.shape[0]
+        self._want(weight, None, "linear weight", 2)
+        if bias is not None:
+            self._want(bias, torch.float32, "linear bias", 1)
         if weight.shape[1] != k or (bias is not None and bias.numel() != n):
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
+        if self._skinny_ok(m, k, weight.dtype):
+            sink = [None, None, None, 0, 0, 0, 0]
+            if kv_sink is not None:
+                cache, slots, n_head, n_kv_head, head_dim = kv_sink
+                sink = [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim,
+                        n_kv_head, head_dim, cache.page_tokens]
+            if deferred is not None:
+                args = [None, _ptr(deferred.x32), _ptr(deferred.rows), _ptr(deferred.gain),
+                        _ptr(deferred.shift), deferred.eps]
+            else:
+                self._want(x, weight.dtype, "linear input", 2)
+                args = [_ptr(x), None, None, None, None, 0.0]
+            code = self.lib.mg_linear_skinny(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                             m, n, k, epilogue, out_bf16, *sink, self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "linear (small batch)")
+                return kv_sink is not None
+        if deferred is not None:
+            x = deferred.materialize()
+        self._want(x, weight.dtype, "linear input", 2)
         if x.dtype == torch.bfloat16 and self.use_tensor_cores:
             code = self.lib.mg_linear_tc(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                          m, n, k, epilogue, out_bf16, _ptr(self.status),
                                          self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "linear (tensor cores)")
-                return
+                return False
         self._run(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                       m, n, k, epilogue, self._is_bf16(x), out_bf16, self._stream()),
               "linear")
+        return False
 
     def linear(self, x, weight, bias, activation, out_dtype):
         if activation not in ("none", "gelu_tanh"):
             raise KernelLibraryError(f"linear: no epilogue for activation {activation!r}")
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
         self._linear(x, weight, bias, EPILOGUES[activation], out, None)
+        return out
+
+    def linear_qkv(self, x, weight, bias, n_head, n_kv_head, head_dim, cache, slots, out_dtype):
+        """The fused q/k/v projection; new keys and values also go to their cache rows (inside
+        the projection kernel where it can, else with the page-write kernel)."""
+        out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=self.device)
+        sink = None
+        if cache is not None and cache.writes:
+            self._want(slots, torch.int32, "slot_mapping", 1)
+            sink = (cache, slots, n_head, n_kv_head, head_dim)
+        stored = self._linear(x, weight, bias, EPILOGUES["none"], out, None, kv_sink=sink)
+        if sink is not None and not stored:
+            self.kv_store(out, n_head, n_kv_head, head_dim, cache, slots)
         return out
 
     def linear_residual(self, x, weight, bias, residual32):
@@ -204,8 +267,19 @@ class CudaOps:
     # ---- sampling -------------------------------------------------------------------------------
     def argmax(self, logits, vocab_limit=None):
         self._want(logits, torch.float32, "logits", 2)
-        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=self.device)
-        self._run(self.lib.mg_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1],
+        rows, vocab = logits.shape
+        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        if vocab >= 8192 and rows <= 512:
+            # few rows of a wide vocabulary: many blocks per row, then a merge
+            parts = self.lib.mg_argmax_parts(vocab)
+            scratch_v = torch.empty((rows * parts,), dtype=torch.float32, device=self.device)
+            scratch_i = torch.empty((rows * parts,), dtype=torch.int32, device=self.device)
+            self._run(self.lib.mg_argmax_wide(_ptr(logits), _ptr(out), _ptr(scratch_v),
+                                          _ptr(scratch_i), rows, vocab, int(vocab_limit or 0),
+                                          self._stream()), "argmax (wide)")
+            self.launches += 1
+            return out
+        self._run(self.lib.mg_argmax(_ptr(logits), _ptr(out), rows, vocab,
                                  int(vocab_limit or 0), self._stream()), "argmax")
         return out
 

@@ -60,14 +60,27 @@ class CausalAttention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.n_kv_head, self.head_dim, self.window)
 
+    accepts_deferred_norm = True
+
+    def _position_rotates(self) -> bool:
+        from .base import PositionEncoding
+
+        return (self.position is not None
+                and type(self.position).rotate is not PositionEncoding.rotate)
+
     def forward(self, ctx, cache, y, residual32) -> None:
         ops = ctx.ops
-        qkv = ops.linear(y, self.qkv_weight, self.qkv_bias, "none", ctx.act_dtype)
-        if self.position is not None:
-            self.position.rotate(ctx, qkv, self.n_head, self.n_kv_head, self.head_dim)
-        if cache.writes:
-            ops.kv_store(qkv, self.n_head, self.n_kv_head, self.head_dim, cache,
-                         ctx.slot_mapping[cache.group])
+        slots = ctx.slot_mapping[cache.group]
+        if not self._position_rotates() and hasattr(ops, "linear_qkv"):
+            # nothing happens between the projection and the page write: one fused call
+            qkv = ops.linear_qkv(y, self.qkv_weight, self.qkv_bias, self.n_head, self.n_kv_head,
+                                 self.head_dim, cache, slots, ctx.act_dtype)
+        else:
+            qkv = ops.linear(y, self.qkv_weight, self.qkv_bias, "none", ctx.act_dtype)
+            if self.position is not None:
+                self.position.rotate(ctx, qkv, self.n_head, self.n_kv_head, self.head_dim)
+            if cache.writes:
+                ops.kv_store(qkv, self.n_head, self.n_kv_head, self.head_dim, cache, slots)
         out = ops.paged_attention(qkv, self.n_head, self.n_kv_head, self.head_dim, self.scale,
                                   cache, ctx)
         ops.linear_residual(out, self.proj_weight, self.proj_bias, residual32)

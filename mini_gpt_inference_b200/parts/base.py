@@ -53,6 +53,13 @@ class Norm(Part):
     def forward(self, ctx, x32):
         raise NotImplementedError
 
+    def defer(self, ctx, x32, rows=None):
+        """The norm as an object that the consuming projection may fuse (see the consumer's
+        ``accepts_deferred_norm``).  By default it simply runs."""
+        if rows is not None:
+            x32 = ctx.ops.gather_rows(x32, rows)
+        return self.forward(ctx, x32)
+
 
 class PositionEncoding(Part):
     max_positions: int | None = None
@@ -65,6 +72,10 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True if forward() hands its input only to ctx.ops projections, which understand a
+    # deferred norm; then the block passes norm.defer(...) instead of the normalised tensor.
+    accepts_deferred_norm = False
+
     def cache_spec(self):
         return None
 
@@ -73,6 +84,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    accepts_deferred_norm = False
+
     def forward(self, ctx, y, residual32) -> None:
         raise NotImplementedError
 

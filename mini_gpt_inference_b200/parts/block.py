@@ -23,7 +23,10 @@ class Layer:
 
 @register_arrangement("pre_norm")
 def pre_norm(ctx, layer: Layer, cache, residual32) -> None:
-    y = layer.norm1.forward(ctx, residual32)
-    layer.mixer.forward(ctx, cache, y, residual32)
-    y = layer.norm2.forward(ctx, residual32)
-    layer.feed_forward.forward(ctx, y, residual32)
+    mixer, ff = layer.mixer, layer.feed_forward
+    y = (layer.norm1.defer if getattr(mixer, "accepts_deferred_norm", False)
+         else layer.norm1.forward)(ctx, residual32)
+    mixer.forward(ctx, cache, y, residual32)
+    y = (layer.norm2.defer if getattr(ff, "accepts_deferred_norm", False)
+         else layer.norm2.forward)(ctx, residual32)
+    ff.forward(ctx, y, residual32)

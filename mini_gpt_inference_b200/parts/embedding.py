@@ -46,6 +46,8 @@ class TiedHead(Part):
         return {self.prefix + "weight": TensorSpec((self.vocab_size, self.width), "matrix",
                                                    optional_alias_of=self.tied_to)}
 
+    accepts_deferred_norm = True
+
     def bind(self, tensors) -> None:
         return None
 

@@ -29,3 +29,8 @@ class LayerNorm(Norm):
 
     def forward(self, ctx, x32):
         return ctx.ops.layernorm(x32, self.weight, self.bias, self.eps, ctx.act_dtype)
+
+    def defer(self, ctx, x32, rows=None):
+        if not hasattr(ctx.ops, "defer_layernorm"):
+            return super().defer(ctx, x32, rows)
+        return ctx.ops.defer_layernorm(x32, self.weight, self.bias, self.eps, ctx.act_dtype, rows)

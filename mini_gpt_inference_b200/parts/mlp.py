@@ -38,6 +38,8 @@ class DenseMLP(FeedForward):
             specs[p + "proj.bias"] = TensorSpec((self.width,), "vector", "bias")
         return specs
 
+    accepts_deferred_norm = True
+
     def forward(self, ctx, y, residual32) -> None:
         h = ctx.ops.linear(y, self.fc_weight, self.fc_bias, self.activation, ctx.act_dtype)
         ctx.ops.linear_residual(h, self.proj_weight, self.proj_bias, residual32)

@@ -71,5 +71,7 @@ class DecoderModel:
             layer.run(ctx, layer, ctx.cache_view(call.cache_layer, call.writes_cache), x)
         if ctx.logit_rows.numel() == 0:
             return None
+        if getattr(self.head, "accepts_deferred_norm", False):
+            return self.head.forward(ctx, self.final_norm.defer(ctx, x, ctx.logit_rows))
         rows = ctx.ops.gather_rows(x, ctx.logit_rows)
         return self.head.forward(ctx, self.final_norm.forward(ctx, rows))

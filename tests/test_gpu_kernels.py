@@ -100,6 +100,66 @@ def test_tensor_core_and_cuda_core_products_agree(ops):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
+@pytest.mark.parametrize("n,k", [(1536, 512), (512, 2048), (509, 96), (50304, 512), (200, 200)])
+def test_small_batch_projection_with_fused_norm(ops, m, n, k):
+    """Up to 8 tokens take the weight-streaming kernel; with a deferred LayerNorm (and a row
+    gather) fused into its prologue it must agree with the separate kernels."""
+    x32 = randn(m + 3, k, seed=21, scale=2.0) + 0.5
+    rows = torch.tensor([(3 * i + 1) % (m + 3) for i in range(m)], dtype=torch.int32).cuda()
+    gain, shift = randn(k, seed=22) + 1.0, randn(k, seed=23)
+    w = randn(n, k, dtype=torch.bfloat16, seed=24, scale=1 / math.sqrt(k))
+    b = randn(n, seed=25)
+    want = torch.nn.functional.layer_norm(x32[rows.long()].double(), (k,), gain.double(), shift.double(), 1e-5)
+    want = want.to(torch.bfloat16).double() @ w.double().T + b.double()
+    before = ops.launches
+    fused = ops.linear(ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16, rows), w, b, "none",
+                       torch.float32)
+    assert ops.launches == before + 1, "norm, gather and projection were expected in one kernel"
+    assert (fused.double() - want).abs().max() <= 2e-2       # bf16 rounding of the normalised rows
+    ops.use_skinny = False
+    try:
+        apart = ops.linear(ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16, rows), w, b, "none",
+                           torch.float32)
+    finally:
+        ops.use_skinny = True
+    assert (fused - apart).abs().max() <= 2e-5               # same bf16 inputs, 32-bit sums
+    res = randn(m, n, seed=26)
+    keep = res.clone()
+    y = ops.layernorm(ops.gather_rows(x32, rows), gain, shift, 1e-5, torch.bfloat16)
+    ops.linear_residual(y, w, b, res)
+    assert (res.double() - (keep.double() + want)).abs().max() <= 2e-2
+    g = ops.linear(y, w, b, "gelu_tanh", torch.bfloat16)
+    assert (g.double() - plain_gpt.gelu_tanh(want)).abs().max() <= 5e-2
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m", [1, 4, 8, 9, 40])
+def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m):
+    n_head, n_kv, d, pt, pages, k = 6, 2, 32, 8, 12, 96
+    width = (n_head + 2 * n_kv) * d
+    x = randn(m, k, dtype=torch.bfloat16, seed=31)
+    w = randn(width, k, dtype=torch.bfloat16, seed=32, scale=0.1)
+    b = randn(width, seed=33)
+    slots = torch.randperm(pages * pt)[:m].to(torch.int32)
+    slots[0] = -1                                            # a padding row writes nothing
+    slots = slots.cuda()
+    cache = SimpleNamespace(k_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                            v_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                            page_tokens=pt, writes=True)
+    qkv = ops.linear_qkv(x, w, b, n_head, n_kv, d, cache, slots, torch.bfloat16)
+    kk = qkv[:, n_head * d: (n_head + n_kv) * d].reshape(m, n_kv, d)
+    vv = qkv[:, (n_head + n_kv) * d:].reshape(m, n_kv, d)
+    want_k, want_v = torch.zeros_like(cache.k_pages), torch.zeros_like(cache.v_pages)
+    for i, s_ in enumerate(slots.tolist()):
+        if s_ >= 0:
+            want_k[s_ // pt, :, s_ % pt] = kk[i]
+            want_v[s_ // pt, :, s_ % pt] = vv[i]
+    assert torch.equal(cache.k_pages, want_k) and torch.equal(cache.v_pages, want_v)
+    ref = x.double() @ w.double().T + b.double()
+    assert (qkv.double() - ref).abs().max() <= 5e-2
+
+
 def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window, lengths, q_lens,
                     seed=0):
     """Requests with `lengths[i]` tokens in total, of which the last `q_lens[i]` are new."""
