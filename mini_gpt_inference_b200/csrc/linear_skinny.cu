@@ -69,6 +69,45 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = a.K;
 
+    const int ks = a.k_splits;
+    const int groups_per_round = WARPS / ks;
+    const int my_group_in_round = warp / ks, my_slice = warp % ks;
+    // slice edges at multiples of 8 elements
+    const int chunks = K / 8;
+    const int c_begin = (int)((long long)chunks * my_slice / ks), c_end = (int)((long long)chunks * (my_slice + 1) / ks);
+    const int first_group = blockIdx.x * a.groups_per_cta;
+    const int total_groups = (a.N + R - 1) / R;
+
+    // Ask for the first weights of this warp's first task before anything else: they travel
+    // from HBM while the activations are staged (and normalised) below.
+    uint4 first_w[R];
+    bool have_first = false;
+    {
+        const int group = first_group + my_group_in_round;
+        const int c = c_begin + lane;
+        if (my_group_in_round < a.groups_per_cta && group < total_groups && c < c_end) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                first_w[r] = *reinterpret_cast<const uint4*>(a.w + (size_t)min(group * R + r, a.N - 1) * K + c * 8);
+            have_first = true;
+        }
+    }
+
+    // The epilogue's operands (bias, residual rows) are asked for now as well, into L2/L1, so
+    // that the epilogue does not wait on HBM after the sums are done.
+    {
+        const int e = tid;
+        if (e < groups_per_round * R * MT) {
+            const int gi = e / (R * MT), rm = e - gi * (R * MT);
+            const int r = rm / MT, m = rm - r * MT;
+            const int n = (first_group + gi) * R + r;
+            if (gi < a.groups_per_cta && n < a.N && m < a.M) {
+                if (a.bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bias + n));
+                if (a.epilogue == EPI_RESIDUAL) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.residual + (size_t)m * a.N + n));
+            }
+        }
+    }
+
     // ---- stage the activations as bfloat16 (with the LayerNorm prologue if asked) ----
     if (a.x32 != nullptr) {
         for (int m = warp; m < MT; m += WARPS) {
@@ -104,15 +143,6 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     }
     __syncthreads();
 
-    const int ks = a.k_splits;
-    const int groups_per_round = WARPS / ks;
-    const int my_group_in_round = warp / ks, my_slice = warp % ks;
-    // slice edges at multiples of 8 elements
-    const int chunks = K / 8;
-    const int c_begin = (int)((long long)chunks * my_slice / ks), c_end = (int)((long long)chunks * (my_slice + 1) / ks);
-    const int first_group = blockIdx.x * a.groups_per_cta;
-    const int total_groups = (a.N + R - 1) / R;
-
     for (int g0 = 0; g0 < a.groups_per_cta; g0 += groups_per_round) {
         const int group = first_group + g0 + my_group_in_round;
         const bool active = (g0 + my_group_in_round) < a.groups_per_cta && group < total_groups;
@@ -128,8 +158,13 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             for (int r = 0; r < R; ++r) wrow[r] = a.w + (size_t)min(n0 + r, a.N - 1) * K;
             for (int c = c_begin + lane; c < c_end; c += 32) {
                 uint4 wraw[R];
+                if (g0 == 0 && have_first && c == c_begin + lane) {
 #pragma unroll
-                for (int r = 0; r < R; ++r) wraw[r] = *reinterpret_cast<const uint4*>(wrow[r] + c * 8);
+                    for (int r = 0; r < R; ++r) wraw[r] = first_w[r];
+                } else {
+#pragma unroll
+                    for (int r = 0; r < R; ++r) wraw[r] = *reinterpret_cast<const uint4*>(wrow[r] + c * 8);
+                }
                 float wf[R][8];
 #pragma unroll
                 for (int r = 0; r < R; ++r) unpack8(wraw[r], wf[r]);

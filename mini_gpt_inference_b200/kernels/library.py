@@ -28,7 +28,8 @@ _SIGNATURES = {
                          _I, _I, _I, _I, _P],
     "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
-    "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _P],
+    "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
+                                 _F, _P, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -66,7 +67,7 @@ def load(verbose: bool = True):
         fn.restype = c_int
     lib.mg_argmax_parts.argtypes = [c_int]
     lib.mg_argmax_parts.restype = c_int
-    lib.mg_attention_split_count.argtypes = [c_int, c_int]
+    lib.mg_attention_split_count.argtypes = [c_int, c_int, c_int]
     lib.mg_attention_split_count.restype = c_int
     lib.mg_attention_split_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mg_attention_split_scratch_floats.restype = ctypes.c_longlong

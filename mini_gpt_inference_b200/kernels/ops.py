@@ -64,6 +64,7 @@ class CudaOps:
         self.use_tensor_cores = True
         self.use_split_attention = True
         self.use_skinny = True
+        self._counter_buf = None
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -92,6 +93,13 @@ class CudaOps:
         if t.dtype == torch.float32:
             return 0
         raise KernelLibraryError(f"dtype {t.dtype} is neither bfloat16 nor float32")
+
+    def _counters(self, count: int):
+        """Zeroed ints that the split attention kernel uses to find its last block per row and
+        leaves zeroed; kept for the life of the object, grown on demand."""
+        if self._counter_buf is None or self._counter_buf.numel() < count:
+            self._counter_buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=self.device)
+        return self._counter_buf
 
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
@@ -246,16 +254,16 @@ class CudaOps:
         window = int(cache.window or 0)
         if (qkv.dtype == torch.bfloat16 and getattr(ctx, "decode_only", False)
                 and head_dim in self.SPLIT_HEAD_DIMS and self.use_split_attention):
-            # single query tokens: split along the keys, merge afterwards
-            splits = self.lib.mg_attention_split_count(int(ctx.max_ctx_after), window)
+            # single query tokens: split along the keys; the last block of each row merges
+            splits = self.lib.mg_attention_split_count(int(ctx.max_ctx_after), window, head_dim)
             floats = self.lib.mg_attention_split_scratch_floats(n, n_head, head_dim, splits)
             scratch = torch.empty((floats,), dtype=torch.float32, device=self.device)
             self._run(self.lib.mg_paged_attention_split(
                 _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
-                _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), _ptr(scratch), n, n_head,
-                n_kv_head, head_dim, cache.page_tokens, table.shape[1], window, splits, float(scale),
-                self._stream()), "paged_attention (split)")
-            self.launches += 1                      # two kernels: split and merge
+                _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), _ptr(scratch),
+                _ptr(self._counters(n * n_head)), n, n_head, n_kv_head, head_dim, cache.page_tokens,
+                table.shape[1], window, splits, float(scale), _ptr(self.status), self._stream()),
+                "paged_attention (split)")
             return out
         self._run(self.lib.mg_paged_attention_generic(
             _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),

@@ -232,11 +232,12 @@ def test_paged_attention_general(ops, dtype, n_head, n_kv_head, head_dim, page_t
     (4, 2, 256, 64, 0), (4, 4, 32, 8, 5), (6, 3, 64, 16, 300)])
 def test_paged_attention_split_over_keys(ops, n_head, n_kv_head, head_dim, page_tokens, window):
     """Single query tokens in bfloat16 take the kernel that splits the keys into blocks of 256
-    and merges: lengths around the block edges, one token, long contexts."""
-    lengths = [1, 2, 255, 256, 257, 511, 513, 700, 1025, page_tokens, page_tokens + 1]
+    and merges: lengths around the block edges (blocks of 32 to 256 keys by head size), one token, long contexts."""
+    lengths = [1, 2, 63, 64, 65, 127, 129, 255, 256, 257, 511, 513, 700, 1025, page_tokens, page_tokens + 1]
     got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, head_dim, page_tokens, window,
                                 lengths, [1] * len(lengths))
-    assert _attention_case.kernels == 2, "the split kernel and its merge were expected to run"
+    assert _attention_case.kernels == 1, "the split kernel (with its own merge) was expected to run"
+    ops.check_status()
     assert not torch.isnan(got).any()
     assert (got - want).abs().max() <= _tol(torch.bfloat16, 1.0)
     # the general kernel gives the same within rounding
