@@ -254,15 +254,61 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 if (!SWAP) {
                     // p is a token, q runs over features: contiguous in the output row
                     const size_t row = (size_t)p * ld_out;
+                    const int qc = q0 + c0;
+                    const bool full = (CHUNK == 32) && (qc + CHUNK <= rows_q) && (ld_out % 8 == 0);
+                    if (full) {
+                        // whole chunk inside the matrix and 16-byte aligned: vector loads and stores
+                        float v[32];
 #pragma unroll
-                    for (int j = 0; j < CHUNK; ++j) {
-                        const int q = q0 + c0 + j;
-                        if (q < rows_q) {
-                            float v = __uint_as_float(r[j]) + (bias ? bias[q] : 0.f);
-                            if (epilogue == EPI_GELU) v = gelu_tanh(v);
-                            if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
-                            else if (out_bf16) ((bf16*)out_ptr)[row + q] = __float2bfloat16_rn(v);
-                            else ((float*)out_ptr)[row + q] = v;
+                        for (int j = 0; j < 32; j += 4) {
+                            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (bias) b4 = *reinterpret_cast<const float4*>(bias + qc + j);
+                            v[j] = __uint_as_float(r[j]) + b4.x;
+                            v[j + 1] = __uint_as_float(r[j + 1]) + b4.y;
+                            v[j + 2] = __uint_as_float(r[j + 2]) + b4.z;
+                            v[j + 3] = __uint_as_float(r[j + 3]) + b4.w;
+                        }
+                        if (epilogue == EPI_GELU) {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                        }
+                        if (epilogue == EPI_RESIDUAL) {
+                            float4* dst = reinterpret_cast<float4*>(residual + row + qc);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) {
+                                float4 o = dst[j];
+                                o.x += v[4 * j]; o.y += v[4 * j + 1]; o.z += v[4 * j + 2]; o.w += v[4 * j + 3];
+                                dst[j] = o;
+                            }
+                        } else if (out_bf16) {
+                            uint4* dst = reinterpret_cast<uint4*>((bf16*)out_ptr + row + qc);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
+                                __nv_bfloat162 h1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]);
+                                __nv_bfloat162 h3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                                uint4 o;
+                                o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                                o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                                dst[j] = o;
+                            }
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>((float*)out_ptr + row + qc);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) dst[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int q = qc + j;
+                            if (q < rows_q) {
+                                float v = __uint_as_float(r[j]) + (bias ? bias[q] : 0.f);
+                                if (epilogue == EPI_GELU) v = gelu_tanh(v);
+                                if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
+                                else if (out_bf16) ((bf16*)out_ptr)[row + q] = __float2bfloat16_rn(v);
+                                else ((float*)out_ptr)[row + q] = v;
+                            }
                         }
                     }
                 } else {

@@ -64,6 +64,7 @@ class CudaOps:
         self.use_tensor_cores = True
         self.use_split_attention = True
         self.use_skinny = True
+        self.use_prefill_tc = True
         self._counter_buf = None
 
     # ---- helpers --------------------------------------------------------------------------
@@ -265,6 +266,19 @@ class CudaOps:
                 table.shape[1], window, splits, float(scale), _ptr(self.status), self._stream()),
                 "paged_attention (split)")
             return out
+        work = getattr(ctx, "attn_work", None)
+        if (qkv.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0
+                and self.use_tensor_cores and self.use_prefill_tc):
+            # portions of prompts: query tiles of 128 on the tensor cores
+            self._want(work, torch.int32, "attn_work", 2)
+            code = self.lib.mg_attention_prefill_tc(
+                _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(work), _ptr(table),
+                _ptr(ctx.positions), _ptr(out), work.shape[0], n, n_head, n_kv_head, head_dim,
+                cache.page_tokens, cache.k_pages.shape[0], table.shape[1], window, float(scale),
+                _ptr(self.status), self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "paged_attention (prefill, tensor cores)")
+                return out
         self._run(self.lib.mg_paged_attention_generic(
             _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
             _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,

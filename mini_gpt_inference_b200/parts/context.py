@@ -32,6 +32,9 @@ class StepContext:
     block_tables: list[torch.Tensor]      # per cache group [R, max_pages], -1 = no page
     slot_mapping: list[torch.Tensor]      # per cache group [N] flat row of each new token
     logit_rows: torch.Tensor              # [W] rows whose logits are wanted
+    # rows cut into runs of at most 128 consecutive tokens of one request, for kernels that work
+    # on tiles of queries: [items, 3] = (request index, first row, rows); None if not built
+    attn_work: torch.Tensor | None = None
     # host mirrors for parts that plan on the host
     host_q_len: list[int] = field(default_factory=list)
     host_ctx_before: list[int] = field(default_factory=list)

@@ -203,10 +203,16 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
             positions.append(p)
     cache = SimpleNamespace(k_pages=k_pages.to(dtype).cuda(), v_pages=v_pages.to(dtype).cuda(),
                             group=0, page_tokens=page_tokens, window=window or None, writes=False)
+    work, row = [], 0
+    for r, ql in enumerate(q_lens):                              # query tiles of at most 128 rows
+        for b in range(0, ql, 128):
+            work.append((r, row + b, min(128, ql - b)))
+        row += ql
     ctx = SimpleNamespace(block_tables=[tables.cuda()],
                           token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
                           positions=torch.tensor(positions, dtype=torch.int32).cuda(),
-                          decode_only=all(q == 1 for q in q_lens), max_ctx_after=max(lengths))
+                          decode_only=all(q == 1 for q in q_lens), max_ctx_after=max(lengths),
+                          attn_work=torch.tensor(work, dtype=torch.int32).cuda())
     qkv = torch.stack(qkv_rows).to(dtype).cuda()
     before = ops.launches
     got = ops.paged_attention(qkv, n_head, n_kv_head, head_dim, scale, cache, ctx)
@@ -225,6 +231,30 @@ def test_paged_attention_general(ops, dtype, n_head, n_kv_head, head_dim, page_t
     got, want = _attention_case(ops, dtype, n_head, n_kv_head, head_dim, pt, window, lengths, q_lens)
     assert not torch.isnan(got).any(), "attention read a cache row beyond a request's length"
     assert (got - want).abs().max() <= _tol(dtype, 1.0)
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,page_tokens,window", [
+    (8, 8, 16, 0), (2, 2, 8, 0), (4, 1, 64, 0), (2, 2, 128, 0), (2, 1, 256, 0), (3, 3, 32, 0),
+    (4, 2, 16, 33), (2, 2, 64, 200)])
+def test_prompt_portions_on_the_tensor_cores(ops, n_head, n_kv_head, page_tokens, window):
+    """Portions of prompts with head size 64 in bfloat16 take the tcgen05 kernel: query tiles of
+    128 rows over key blocks of 128 from the pages; tiles that start anywhere in a request,
+    tiles of one row, contexts that end at any place inside a block or a page."""
+    lengths = [300, 129, 128, 1000, 1, 77, 513]
+    q_lens = [300, 129, 5, 700, 1, 2, 257]
+    got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, 64, page_tokens, window,
+                                lengths, q_lens, seed=3)
+    ops.check_status()
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max() <= _tol(torch.bfloat16, 1.0)
+    ops.use_prefill_tc = False
+    try:
+        general, _ = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, 64, page_tokens, window,
+                                     lengths, q_lens, seed=3)
+    finally:
+        ops.use_prefill_tc = True
+    assert (general - got).abs().max() <= _tol(torch.bfloat16, 1.0)
+    assert not torch.equal(general, got), "the two kernels were expected to differ in rounding"
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,window", [
