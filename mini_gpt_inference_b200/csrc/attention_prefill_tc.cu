@@ -4,7 +4,7 @@
 // A CTA takes up to 128 consecutive query tokens of one request and one head and walks over the
 // key blocks (128 positions, anchored at absolute multiples of 128) that those queries may see.
 // Keys and values come straight from the cache pages by TMA (one tile load per page and
-// tensor, 128-byte swizzle, double buffered one block ahead); the keys of this very step were
+// tensor, 128-byte swizzle; keys one block ahead, values as soon as their tile is free); the keys of this very step were
 // written to the pages before the launch, so a portion of a prompt and a whole prompt read the
 // same numbers.  Per key block:
 //
@@ -116,7 +116,7 @@ __host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major)
 }
 
 struct __align__(8) Sync {
-    uint64_t q_full, k_full[2], v_full[2], s_done, pv_done;
+    uint64_t q_full, k_full[2], v_full, s_done, pv_done;
     uint32_t tmem_base;
     uint32_t failed;
 };
@@ -125,33 +125,36 @@ __global__ void __launch_bounds__(THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int* __restrict__ work,
                             const int* __restrict__ block_table, const int* __restrict__ positions,
-                            bf16* __restrict__ out, int n_head, int n_kv_head, int page_tokens, int box_rows,
-                            int max_pages, int window, float scale_log2e, int* __restrict__ status) {
+                            bf16* __restrict__ out, float* __restrict__ partial, int n_head, int n_kv_head,
+                            int page_tokens, int box_rows, int max_pages, int window, float scale_log2e,
+                            int* __restrict__ status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_tile = smem;
     uint8_t* k_tiles = q_tile + Q_BYTES;              // 2 stages
-    uint8_t* v_tiles = k_tiles + 2 * KV_BYTES;        // 2 stages
-    uint8_t* p_tile = v_tiles + 2 * KV_BYTES;
+    uint8_t* v_tile = k_tiles + 2 * KV_BYTES;         // 1 stage: reloaded once the product with P is done
+    uint8_t* p_tile = v_tile + KV_BYTES;
     Sync* sync = (Sync*)(p_tile + P_BYTES);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int item = blockIdx.x, head = blockIdx.y;
-    const int req = work[3 * item], row0 = work[3 * item + 1], n_rows = work[3 * item + 2];
+    const int req = work[5 * item], row0 = work[5 * item + 1], n_rows = work[5 * item + 2];
+    const int chunk = work[5 * item + 3], n_chunks = work[5 * item + 4];
     const int kv_head = head / (n_head / n_kv_head);
     const int pos0 = positions[row0];
     const int my_pos = pos0 + tid;                     // query position of this thread's row
     const int last_key = pos0 + n_rows - 1;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-    const int first_blk = lo / BK, last_blk = last_key / BK;
+    // the key blocks this tile may see, and this work item's share of them
+    const int tile_first = lo / BK, tile_blocks = last_key / BK - tile_first + 1;
+    const int first_blk = tile_first + (int)((long long)tile_blocks * chunk / n_chunks);
+    const int last_blk = tile_first + (int)((long long)tile_blocks * (chunk + 1) / n_chunks) - 1;
     const int* table = block_table + (size_t)req * max_pages;
 
     if (tid == 0) {
         mbar_init(smem_u32(&sync->q_full), 1);
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(smem_u32(&sync->k_full[s]), 1);
-            mbar_init(smem_u32(&sync->v_full[s]), 1);
-        }
+        for (int s = 0; s < 2; ++s) mbar_init(smem_u32(&sync->k_full[s]), 1);
+        mbar_init(smem_u32(&sync->v_full), 1);
         mbar_init(smem_u32(&sync->s_done), 1);
         mbar_init(smem_u32(&sync->pv_done), 1);
         sync->failed = 0;
@@ -167,27 +170,28 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const uint32_t tmem_base = sync->tmem_base;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-    // Issue the tile loads of one key block into a stage (thread 0 only).
-    auto load_block = [&](int blk, int stage) {
-        const uint32_t kbar = smem_u32(&sync->k_full[stage]), vbar = smem_u32(&sync->v_full[stage]);
-        mbar_expect_tx(kbar, KV_BYTES);
-        mbar_expect_tx(vbar, KV_BYTES);
-        for (int which = 0; which < 2; ++which) {
-            for (int r = 0; r < BK; r += box_rows) {
-                const int pos = blk * BK + r;
-                const int pi = pos / page_tokens;
-                const int page = pi < max_pages ? table[pi] : -1;   // -1: no such page -> zeros
-                const int y = (page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
-                uint8_t* dst = (which == 0 ? k_tiles : v_tiles) + stage * KV_BYTES + r * (D * 2);
-                tma_load_2d(smem_u32(dst), which == 0 ? &map_k : &map_v, which == 0 ? kbar : vbar, 0, y);
-            }
+    // Issue the tile loads of one key block (thread 0 only): keys into a stage of the ring,
+    // values into the single value tile.
+    auto load_tiles = [&](int blk, bool values, int stage) {
+        const uint32_t bar = values ? smem_u32(&sync->v_full) : smem_u32(&sync->k_full[stage]);
+        mbar_expect_tx(bar, KV_BYTES);
+        for (int r = 0; r < BK; r += box_rows) {
+            const int pos = blk * BK + r;
+            const int pi = pos / page_tokens;
+            const int page = pi < max_pages ? table[pi] : -1;   // -1: no such page -> zeros
+            const int y = (page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
+            uint8_t* dst = (values ? v_tile : k_tiles + stage * KV_BYTES) + r * (D * 2);
+            tma_load_2d(smem_u32(dst), values ? &map_v : &map_k, bar, 0, y);
         }
     };
 
     if (tid == 0) {
         mbar_expect_tx(smem_u32(&sync->q_full), Q_BYTES);
         tma_load_2d(smem_u32(q_tile), &map_q, smem_u32(&sync->q_full), head * D, row0);
-        load_block(first_blk, 0);
+        if (first_blk <= last_blk) {
+            load_tiles(first_blk, false, 0);
+            load_tiles(first_blk, true, 0);
+        }
     }
 
     float o[D];
@@ -199,7 +203,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int blk = first_blk, it = 0; blk <= last_blk; ++blk, ++it) {
         const int stage = it & 1;
         if (tid == 0) {
-            if (blk + 1 <= last_blk) load_block(blk + 1, stage ^ 1);     // one block ahead
+            if (blk + 1 <= last_blk) load_tiles(blk + 1, false, stage ^ 1);   // keys one block ahead
+            if (it > 0) load_tiles(blk, true, 0);           // values: the tile is free since the last product
             bool ok = true;
             if (it == 0) ok = mbar_wait(smem_u32(&sync->q_full), 0);
             ok = ok && mbar_wait(smem_u32(&sync->k_full[stage]), (it >> 1) & 1);
@@ -221,23 +226,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int key0 = blk * BK;
         const int hi = my_pos - key0;                                     // columns <= hi are not in the future
         const int lo_col = (window > 0) ? (my_pos - window + 1 - key0) : -1;   // columns >= lo_col are in the window
-        // first pass over the row of S: the block's maximum
+        // Blocks that lie wholly before the first query of the tile (and inside every window)
+        // need no mask: the common case takes the short path.
+        const bool unmasked = (key0 + BK - 1 <= pos0) && (window <= 0 || key0 >= pos0 + BQ - window);
         float blk_max = -INFINITY;
+        // first pass over the row of S: the block's maximum
 #pragma unroll
         for (int c = 0; c < BK / 32; ++c) {
             uint32_t r[32];
             tmem_load_32(lane_addr + (uint32_t)(c * 32), r);
             tmem_wait_ld();
+            if (unmasked) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                const int col = c * 32 + j;
-                const bool visible = col <= hi && col >= lo_col;
-                blk_max = fmaxf(blk_max, visible ? __uint_as_float(r[j]) * scale_log2e : -INFINITY);
+                for (int j = 0; j < 32; ++j) blk_max = fmaxf(blk_max, __uint_as_float(r[j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = c * 32 + j;
+                    const bool visible = col <= hi && col >= lo_col;
+                    blk_max = fmaxf(blk_max, visible ? __uint_as_float(r[j]) : -INFINITY);
+                }
             }
         }
+        blk_max *= scale_log2e;                                            // scale > 0: max commutes
         const float new_max = fmaxf(run_max, blk_max);
         const bool none = new_max == -INFINITY;                            // no visible key so far
         const float corr = none ? 1.f : exp2f(run_max - new_max);
+        const float shift = none ? 0.f : new_max;
         float blk_sum = 0.f;
         uint8_t* p_row = p_tile + (tid >> 3) * 1024 + (tid & 7) * 128;
         // second pass: P = 2^(s - max) as bfloat16 into the swizzled tile, 8 keys per 16-byte chunk
@@ -246,19 +261,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             uint32_t r[32];
             tmem_load_32(lane_addr + (uint32_t)(c * 32), r);
             tmem_wait_ld();
+            float pv[32];
+            if (unmasked) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) pv[j] = exp2f(fmaf(__uint_as_float(r[j]), scale_log2e, -shift));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    const int col = c * 32 + j;
+                    const bool visible = !none && col <= hi && col >= lo_col;
+                    pv[j] = visible ? exp2f(fmaf(__uint_as_float(r[j]), scale_log2e, -shift)) : 0.f;
+                }
+            }
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
                 uint32_t packed[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int col = c * 32 + g * 8 + 2 * j;
-                    const bool vis0 = !none && col <= hi && col >= lo_col;
-                    const bool vis1 = !none && col + 1 <= hi && col + 1 >= lo_col;
-                    const float p0 = vis0 ? exp2f(__uint_as_float(r[g * 8 + 2 * j]) * scale_log2e - new_max) : 0.f;
-                    const float p1 = vis1 ? exp2f(__uint_as_float(r[g * 8 + 2 * j + 1]) * scale_log2e - new_max) : 0.f;
+                    const float p0 = pv[g * 8 + 2 * j], p1 = pv[g * 8 + 2 * j + 1];
+                    blk_sum += p0 + p1;                                    // the sum stays in 32-bit
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum uses the rounded values, as the product with V does
-                    blk_sum += __low2float(h) + __high2float(h);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
                 const int chunk = c * 4 + g;                               // 16-byte chunk of the 128 keys
@@ -271,10 +293,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         run_max = new_max;
         // Rows of the value tile past the last key of this work item hold whatever the page held
         // before (their P is zero, but 0 * NaN would still poison the product): clear them.
-        if (blk == last_blk && last_key - key0 + 1 < BK) {
-            if (!mbar_wait(smem_u32(&sync->v_full[stage]), (it >> 1) & 1)) { good = false; atomicExch(status, 25); }
+        if (blk == last_key / BK && last_key - key0 + 1 < BK) {
+            if (!mbar_wait(smem_u32(&sync->v_full), it & 1)) { good = false; atomicExch(status, 25); }
             if (tid > last_key - key0) {
-                uint4* vrow = reinterpret_cast<uint4*>(v_tiles + stage * KV_BYTES + tid * (D * 2));
+                uint4* vrow = reinterpret_cast<uint4*>(v_tile + tid * (D * 2));
 #pragma unroll
                 for (int c = 0; c < D * 2 / 16; ++c) vrow[c] = make_uint4(0u, 0u, 0u, 0u);
             }
@@ -286,10 +308,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
         if (tid == 0) {
             tc_fence_after();
-            if (!mbar_wait(smem_u32(&sync->v_full[stage]), (it >> 1) & 1)) { atomicExch(status, 23); sync->failed = 1; }
+            if (!mbar_wait(smem_u32(&sync->v_full), it & 1)) { atomicExch(status, 23); sync->failed = 1; }
             tc_fence_after();
             constexpr uint32_t idesc_pv = instr_desc(BQ, D, true);
-            const uint32_t p_addr = smem_u32(p_tile), v_addr = smem_u32(v_tiles + stage * KV_BYTES);
+            const uint32_t p_addr = smem_u32(p_tile), v_addr = smem_u32(v_tile);
 #pragma unroll
             for (int k = 0; k < BK / 16; ++k) {
                 const uint64_t dp = smem_desc_sw128(p_addr + (k >> 2) * (BQ * 128) + (k & 3) * 32);
@@ -314,19 +336,33 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         if (!__syncthreads_and(good)) { good = false; break; }
     }
 
-    if (good && tid < n_rows) {
-        const float inv = run_sum > 0.f ? 1.0f / run_sum : 0.f;
-        uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(row0 + tid) * n_head + head) * D);
+    if (first_blk > last_blk && tid == 0) {
+        // nothing to walk (a window cut this part away): the query tile is still on its way
+        if (!mbar_wait(smem_u32(&sync->q_full), 0)) { atomicExch(status, 26); good = false; }
+    }
+    if (good && n_chunks == 1) {
+        if (tid < n_rows) {
+            const float inv = run_sum > 0.f ? 1.0f / run_sum : 0.f;
+            uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(row0 + tid) * n_head + head) * D);
 #pragma unroll
-        for (int c = 0; c < D / 8; ++c) {
-            uint32_t packed[4];
+            for (int c = 0; c < D / 8; ++c) {
+                uint32_t packed[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
-                packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                for (int j = 0; j < 4; ++j) {
+                    const __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+                    packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+                }
+                dst[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
-            dst[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         }
+    } else if (good) {
+        // one of several work items of this tile: leave the unnormalised row, its maximum and its
+        // sum for the merge kernel   [item][head][D + 2][row]: neighbouring threads, neighbouring words
+        float* dst = partial + ((size_t)item * n_head + head) * (D + 2) * BQ + tid;
+#pragma unroll
+        for (int d = 0; d < D; ++d) dst[(size_t)d * BQ] = o[d];
+        dst[(size_t)D * BQ] = run_max;
+        dst[(size_t)(D + 1) * BQ] = run_sum;
     }
     if (!good && tid == 0)
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);        // let copies in flight land
@@ -334,6 +370,45 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     __syncthreads();
     if (warp == 0)
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+}
+
+// Merge the work items of each query tile that was cut along the keys: the CTA of the tile's
+// first item (chunk 0) reads the partial rows of all its items and writes the output rows.
+__global__ void __launch_bounds__(THREADS)
+attention_prefill_merge_kernel(const int* __restrict__ work, const float* __restrict__ partial,
+                               bf16* __restrict__ out, int n_head) {
+    const int item = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int row0 = work[5 * item + 1], n_rows = work[5 * item + 2];
+    const int chunk = work[5 * item + 3], n_chunks = work[5 * item + 4];
+    if (chunk != 0 || n_chunks == 1 || tid >= n_rows) return;
+    const size_t stride = (size_t)n_head * (D + 2) * BQ;              // between items
+    const float* base = partial + ((size_t)item * n_head + head) * (D + 2) * BQ + tid;
+    float M = -INFINITY;
+    for (int c = 0; c < n_chunks; ++c) M = fmaxf(M, base[c * stride + (size_t)D * BQ]);
+    float o[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) o[d] = 0.f;
+    float denom = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {                              // chunks in order
+        const float* src = base + c * stride;
+        const float m = src[(size_t)D * BQ];
+        const float w = (m == -INFINITY) ? 0.f : exp2f(m - M);
+        denom += w * src[(size_t)(D + 1) * BQ];
+#pragma unroll
+        for (int d = 0; d < D; ++d) o[d] = fmaf(w, src[(size_t)d * BQ], o[d]);
+    }
+    const float inv = denom > 0.f ? 1.0f / denom : 0.f;
+    uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)(row0 + tid) * n_head + head) * D);
+#pragma unroll
+    for (int c = 0; c < D / 8; ++c) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(o[c * 8 + 2 * j] * inv, o[c * 8 + 2 * j + 1] * inv);
+            packed[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        dst[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -371,19 +446,30 @@ int make_map(const void* ptr, long long rows, long long cols, int box_rows, CUte
 
 }  // namespace
 
-// Attention of prompt portions.  work: [n_items, 3] ints on the device = (request index, first row
-// of the flat batch, rows <= 128), consecutive rows of one request with consecutive positions.
+// Floats of scratch for the partial results of n_items work items.
+MG_API long long mg_attention_prefill_scratch_floats(int n_items, int n_head) {
+    return (long long)n_items * n_head * BQ * (D + 2);
+}
+
+// Attention of prompt portions.  work: [n_items, 5] ints on the device = (request index, first row
+// of the flat batch, rows <= 128, chunk, chunks): consecutive rows of one request with consecutive
+// positions; the tile's visible key blocks are cut evenly into `chunks` parts and this item walks
+// part `chunk`; the items of one tile are consecutive, chunk 0 first.  `partial` holds
+// mg_attention_prefill_scratch_floats() floats (may be null if no tile is cut: merge != 0 says
+// whether any is).
 // qkv: [n_tokens, (n_head + 2 n_kv_head) * 64] bf16; pages: [num_pages, n_kv_head, page_tokens, 64];
 // out: [n_tokens, n_head * 64].  Returns MG_ERR_UNSUPPORTED unless head_dim is 64 and page_tokens
 // is 8, 16, 32, 64, 128 or a multiple of 128.
 MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const void* v_pages, const int* work,
-                                   const int* block_table, const int* positions, void* out, int n_items,
+                                   const int* block_table, const int* positions, void* out, float* partial,
+                                   int merge, int n_items,
                                    int n_tokens, int n_head, int n_kv_head, int head_dim, int page_tokens,
                                    long long num_pages, int max_pages, int window, float scale, int* status,
                                    void* stream) {
     if (n_items == 0) return MG_OK;
     MG_REQUIRE(n_items > 0 && n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && status,
                "attention (prefill): bad arguments");
+    MG_REQUIRE(!merge || partial != nullptr, "attention (prefill): tiles are cut along the keys but no scratch was given");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     const bool pages_ok = (page_tokens % 8 == 0) && ((page_tokens <= 128 && 128 % page_tokens == 0) || page_tokens % 128 == 0);
     if (head_dim != D || !pages_ok || n_head > 65535 || (((uintptr_t)qkv | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15))
@@ -398,7 +484,7 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
     if (rc != MG_OK) return rc;
     rc = make_map(v_pages, kv_rows, D, box_rows, &map_v);
     if (rc != MG_OK) return rc;
-    const size_t smem = Q_BYTES + 4 * KV_BYTES + P_BYTES + sizeof(Sync) + 1024;
+    const size_t smem = Q_BYTES + 3 * KV_BYTES + P_BYTES + sizeof(Sync) + 1024;   // 97 KB: two CTAs per SM
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -407,8 +493,12 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
     }
     dim3 grid(n_items, n_head);
     attention_prefill_tc_kernel<<<grid, THREADS, smem, (cudaStream_t)stream>>>(
-        map_q, map_k, map_v, work, block_table, positions, (bf16*)out, n_head, n_kv_head, page_tokens, box_rows,
-        max_pages, window, scale * 1.4426950408889634f, status);
+        map_q, map_k, map_v, work, block_table, positions, (bf16*)out, partial, n_head, n_kv_head, page_tokens,
+        box_rows, max_pages, window, scale * 1.4426950408889634f, status);
     MG_CHECK_LAUNCH("attention_prefill_tc");
+    if (merge) {
+        attention_prefill_merge_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(work, partial, (bf16*)out, n_head);
+        MG_CHECK_LAUNCH("attention_prefill_merge");
+    }
     return MG_OK;
 }

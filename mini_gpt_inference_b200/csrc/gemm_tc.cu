@@ -403,7 +403,10 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
     if (rc != MG_OK) return rc;
     constexpr int stage_bytes = P_TILE_BYTES + BN * BLOCK_K * 2;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
-    int stages = (200 * 1024) / stage_bytes;
+    // Many tiles: a ring short enough for two CTAs per SM, so that one CTA's epilogue overlaps
+    // another's main loop.  Few tiles (decoding): one CTA per SM with everything in flight.
+    const long long tiles = (long long)ceil_div(rows_p, TILE_P) * ceil_div(rows_q, BN);
+    int stages = ((tiles > 148 ? 100 : 200) * 1024) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > num_kb) stages = num_kb;
     const size_t smem = (size_t)stages * stage_bytes + sizeof(Barriers) + 1024;

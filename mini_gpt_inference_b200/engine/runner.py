@@ -23,7 +23,7 @@ import torch
 
 from ..cache.manager import NO_PAGE, CacheFullError, CacheManager
 from ..cache.storage import CacheStorage
-from ..parts.context import StepContext
+from ..parts.context import StepContext, query_tiles
 from ..parts.model import DecoderModel
 
 
@@ -54,7 +54,6 @@ class _DecodeGraph:
 
 class ModelRunner:
     GRAPH_ROWS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
-    ATTN_TILE = 128          # query rows of one attention tile
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
                  ops, act_dtype: torch.dtype, device, max_context: int | None = None,
@@ -148,16 +147,11 @@ class ModelRunner:
         N = sum(len(e.tokens) for e in entries)
         W = sum(len(e.want) for e in entries)
         P = self.max_pages
-        # runs of at most ATTN_TILE consecutive tokens of one request (query tiles of attention)
-        work = []
-        row = 0
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
-            for b in range(0, n, self.ATTN_TILE):
-                work.append((r, row + b, min(self.ATTN_TILE, n - b)))
-            row += n
+        # work items of the tiled attention kernels (runs of queries x chunks of keys)
+        work = query_tiles([len(e.tokens) for e in entries],
+                           [m.get(e.request_id).length for e in entries])
         # layout of the packed int32 buffer
-        sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [3 * len(work)]
+        sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [5 * len(work)]
         offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
         total = int(offsets[-1])
         buf = np.empty(max(total, 1), dtype=np.int32)
@@ -208,7 +202,7 @@ class ModelRunner:
             req_state_slot=dseg(6), logit_rows=dseg(7),
             block_tables=[dseg(8 + g).view(R, P) for g in range(n_groups)],
             slot_mapping=[dseg(8 + n_groups + g) for g in range(n_groups)],
-            attn_work=dseg(8 + 2 * n_groups).view(len(work), 3),
+            attn_work=dseg(8 + 2 * n_groups).view(len(work), 5),
             host_q_len=host_q_len, host_ctx_before=host_ctx,
             host_state_slot=[m.get(e.request_id).state_slot for e in entries],
             max_q_len=max(host_q_len), max_ctx_after=max(a + b for a, b in zip(host_q_len, host_ctx)),

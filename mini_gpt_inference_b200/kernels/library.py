@@ -30,8 +30,8 @@ _SIGNATURES = {
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _P, _P],
-    "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, ctypes.c_longlong,
-                                _I, _I, _F, _P, _P],
+    "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+                                ctypes.c_longlong, _I, _I, _F, _P, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
@@ -67,6 +67,8 @@ def load(verbose: bool = True):
             raise KernelLibraryError(f"the kernel library lacks {name}; rebuild it") from None
         fn.argtypes = argtypes
         fn.restype = c_int
+    lib.mg_attention_prefill_scratch_floats.argtypes = [c_int, c_int]
+    lib.mg_attention_prefill_scratch_floats.restype = ctypes.c_longlong
     lib.mg_argmax_parts.argtypes = [c_int]
     lib.mg_argmax_parts.restype = c_int
     lib.mg_attention_split_count.argtypes = [c_int, c_int, c_int]

@@ -32,8 +32,7 @@ class StepContext:
     block_tables: list[torch.Tensor]      # per cache group [R, max_pages], -1 = no page
     slot_mapping: list[torch.Tensor]      # per cache group [N] flat row of each new token
     logit_rows: torch.Tensor              # [W] rows whose logits are wanted
-    # rows cut into runs of at most 128 consecutive tokens of one request, for kernels that work
-    # on tiles of queries: [items, 3] = (request index, first row, rows); None if not built
+    # work list of kernels that take tiles of queries: see query_tiles(); None if not built
     attn_work: torch.Tensor | None = None
     # host mirrors for parts that plan on the host
     host_q_len: list[int] = field(default_factory=list)
@@ -46,3 +45,27 @@ class StepContext:
 
     def cache_view(self, cache_layer: int, writes: bool = True):
         return self.storage.layer_view(cache_layer, writes) if self.storage is not None else None
+
+
+QUERY_TILE = 128       # most consecutive tokens of one request in a tile
+KEY_CHUNK = 512        # most key positions one work item walks over
+
+
+def query_tiles(q_lens, ctx_befores):
+    """Cut a ragged batch into work items ``(request, first row, rows, chunk, chunks)``.
+
+    The tokens of each request are cut into runs of at most QUERY_TILE rows.  The keys a run
+    may see (positions 0 .. its last token) are cut into ``chunks`` parts of at most KEY_CHUNK
+    positions, one work item each, so that a long context is spread over several CTAs; their
+    partial results are merged afterwards.  Items of one run are consecutive, chunk 0 first."""
+    items = []
+    row = 0
+    for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
+        for b in range(0, n, QUERY_TILE):
+            rows = min(QUERY_TILE, n - b)
+            keys = before + b + rows
+            chunks = max(1, -(-keys // KEY_CHUNK))
+            for c in range(chunks):
+                items.append((r, row + b, rows, c, chunks))
+        row += n
+    return items

@@ -203,11 +203,9 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
             positions.append(p)
     cache = SimpleNamespace(k_pages=k_pages.to(dtype).cuda(), v_pages=v_pages.to(dtype).cuda(),
                             group=0, page_tokens=page_tokens, window=window or None, writes=False)
-    work, row = [], 0
-    for r, ql in enumerate(q_lens):                              # query tiles of at most 128 rows
-        for b in range(0, ql, 128):
-            work.append((r, row + b, min(128, ql - b)))
-        row += ql
+    from mini_gpt_inference_b200.parts.context import query_tiles
+
+    work = query_tiles(q_lens, [n - ql for n, ql in zip(lengths, q_lens)])
     ctx = SimpleNamespace(block_tables=[tables.cuda()],
                           token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
                           positions=torch.tensor(positions, dtype=torch.int32).cuda(),
@@ -240,8 +238,8 @@ def test_prompt_portions_on_the_tensor_cores(ops, n_head, n_kv_head, page_tokens
     """Portions of prompts with head size 64 in bfloat16 take the tcgen05 kernel: query tiles of
     128 rows over key blocks of 128 from the pages; tiles that start anywhere in a request,
     tiles of one row, contexts that end at any place inside a block or a page."""
-    lengths = [300, 129, 128, 1000, 1, 77, 513]
-    q_lens = [300, 129, 5, 700, 1, 2, 257]
+    lengths = [300, 129, 128, 1000, 1, 77, 513, 1300, 2048]
+    q_lens = [300, 129, 5, 700, 1, 2, 257, 3, 130]
     got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, 64, page_tokens, window,
                                 lengths, q_lens, seed=3)
     ops.check_status()
