@@ -63,8 +63,15 @@ class SequenceState:
         return self.request.prompt_token_ids[i] if i < p else self.output_token_ids[i - p]
 
     def tokens(self, start: int, count: int) -> list[int]:
-        allt = self.request.prompt_token_ids + self.output_token_ids
-        return allt[start: start + count]
+        """``count`` tokens from position ``start`` of prompt + generated, without building
+        the whole list (a decoding step asks for one token of a long sequence)."""
+        p = self.prompt_len
+        end = start + count
+        if end <= p:
+            return self.request.prompt_token_ids[start:end]
+        if start >= p:
+            return self.output_token_ids[start - p: end - p]
+        return self.request.prompt_token_ids[start:] + self.output_token_ids[: end - p]
 
     def is_finished(self) -> bool:
         return self.status == SequenceStatus.FINISHED
