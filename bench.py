@@ -53,6 +53,9 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
+    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+                    help="a small case for profilers: only the device-timed decode steps, or only "
+                         "the 2,048-token prefill (the printed line is then partial)")
     return ap.parse_args()
 
 
@@ -282,6 +285,15 @@ def run_ours(args) -> dict:
 
     pk, peak_source = peaks()
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4
+    if args.only == "prefill":
+        cfg, pre_ms = prefill_once(args)
+        return {"impl": "ours", "partial": "prefill only", "prefill": {
+            "value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4)}}
+    if args.only == "decode":
+        cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup)
+        ms = statistics.fmean(times)
+        return {"impl": "ours", "partial": "decode only", "value": round(args.batch / (ms * 1e-3), 1),
+                "ms_per_step": round(ms, 4), "gpu_launches": launches}
     cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                            ClockSampler(0))
     ms = statistics.fmean(times)

@@ -210,7 +210,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const uint32_t* __restrict__ seed_lo, const uint32_t* __restrict__ seed_hi,
-              const uint32_t* __restrict__ counter, int* __restrict__ out, int vocab, int limit) {
+              const uint32_t* __restrict__ counter, int* __restrict__ out, int vocab, int limit, int cached) {
+    extern __shared__ float row_cache[];      // the scaled row, if the launch gave room for it
     __shared__ float scratch[SAMPLE_THREADS / 32];
     __shared__ unsigned long long hist[256];
     __shared__ uint32_t sh_prefix;
@@ -237,9 +238,16 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     }
 
     const float safe_t = fmaxf(temp, 1e-6f);
+    // One pass over global memory: the scaled row goes to shared memory (a 50304-wide row is
+    // 197 KB and fits), every later pass reads it from there.
     float mx = -INFINITY;
-    for (int i = tid; i < limit; i += SAMPLE_THREADS) mx = fmaxf(mx, lr[i] / safe_t);
-    mx = block_reduce_max(mx, scratch);
+    for (int i = tid; i < limit; i += SAMPLE_THREADS) {
+        const float x = lr[i] / safe_t;
+        if (cached) row_cache[i] = x;
+        mx = fmaxf(mx, x);
+    }
+    mx = block_reduce_max(mx, scratch);     // (its barriers also publish row_cache)
+#define ROW(i) (cached ? row_cache[i] : lr[i] / safe_t)
 
     // top-k: key of the k-th largest scaled logit
     uint32_t thr_key = 0u;
@@ -252,7 +260,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             if (tid < 256) hist[tid] = 0ull;
             __syncthreads();
             for (int i = tid; i < limit; i += SAMPLE_THREADS) {
-                const uint32_t key = order_key(lr[i] / safe_t);
+                const uint32_t key = order_key(ROW(i));
                 if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1ull);
             }
             __syncthreads();
@@ -280,7 +288,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     if (p < 1.f) {
         float part = 0.f;
         for (int i = tid; i < limit; i += SAMPLE_THREADS) {
-            const float x = lr[i] / safe_t;
+            const float x = ROW(i);
             if (order_key(x) >= thr_key) part += expf(x - mx);
         }
         const float z_k = block_reduce_sum(part, scratch);
@@ -292,7 +300,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
             if (tid < 256) hist[tid] = 0ull;
             __syncthreads();
             for (int i = tid; i < limit; i += SAMPLE_THREADS) {
-                const float x = lr[i] / safe_t;
+                const float x = ROW(i);
                 const uint32_t key = order_key(x);
                 if (key >= thr_key && (key & mask) == prefix) {
                     // + 1 so that a token whose probability underflows still marks its bin
@@ -325,7 +333,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
     // normaliser of what is kept, then the inverse-CDF walk in index order
     float part = 0.f;
     for (int i = tid; i < limit; i += SAMPLE_THREADS) {
-        const float x = lr[i] / safe_t;
+        const float x = ROW(i);
         if (order_key(x) >= thr_key) part += expf(x - mx);
     }
     const float z = block_reduce_sum(part, scratch);
@@ -342,7 +350,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         const int i = t0 + tid;
         float e = 0.f;
         if (i < limit) {
-            const float x = lr[i] / safe_t;
+            const float x = ROW(i);
             if (order_key(x) >= thr_key) { e = expf(x - mx); if (e > 0.f) last_kept = i; }
         }
         float incl = e;                                            // inclusive scan in the warp
@@ -374,6 +382,7 @@ sample_kernel(const float* __restrict__ logits, const float* __restrict__ temper
         __syncthreads();
     }
     if (tid == 0) out[row] = sh_found < 0 ? 0 : sh_found;
+#undef ROW
 }
 
 }  // namespace
@@ -387,8 +396,16 @@ MG_API int mg_sample(const float* logits, const float* temperature, const int* t
     MG_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes");
     MG_REQUIRE(temperature && seed_lo && seed_hi && counter, "sample: missing per-row parameters");
     if (limit <= 0 || limit > vocab) limit = vocab;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, temperature, top_k, top_p, seed_lo,
-                                                                    seed_hi, counter, out, vocab, limit);
+    const size_t row_bytes = (size_t)limit * sizeof(float);
+    const int cached = row_bytes <= 220 * 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "sample: cannot raise shared memory: %s", cudaGetErrorString(e));
+        configured = true;
+    }
+    sample_kernel<<<rows, SAMPLE_THREADS, cached ? row_bytes : 0, (cudaStream_t)stream>>>(
+        logits, temperature, top_k, top_p, seed_lo, seed_hi, counter, out, vocab, limit, cached);
     MG_CHECK_LAUNCH("sample");
     return MG_OK;
 }
