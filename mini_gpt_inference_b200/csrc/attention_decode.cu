@@ -94,6 +94,9 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
 
     const int token = blockIdx.x, head = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // The query and the newest key/value row come from the kernel before this one.
+    pdl_trigger();
+    pdl_wait();
     const int p = positions[token];
     if (p < 0) {                                                        // padding row of a fixed-size batch
         if (split == 0)
@@ -283,10 +286,11 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
         configured = true;
     }
     dim3 grid(n_tokens, n_head, max_splits);
-    attention_split_kernel<D><<<grid, THREADS, smem, s>>>(
-        (const bf16*)qkv, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions, (bf16*)out,
-        part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages, window, max_splits,
-        scale * 1.4426950408889634f, status);
+    cudaError_t le = mg_launch(attention_split_kernel<D>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
+                               (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
+                               (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
+                               window, max_splits, scale * 1.4426950408889634f, status);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     return MG_OK;
 }

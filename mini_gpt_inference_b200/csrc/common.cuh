@@ -58,3 +58,34 @@ __device__ __forceinline__ float gelu_tanh(float u) {
 }
 
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// ---- programmatic dependent launch ---------------------------------------------------------
+// A kernel launched with mg_launch(..., dependent = true) may start while the kernel before it on
+// the stream is still running; it must call pdl_wait() before it reads anything that kernel
+// wrote and before it writes anything at all.  What it does before that (index arithmetic,
+// loads of weights) overlaps the predecessor's tail.  pdl_trigger() tells the successor that it
+// may start.  Both are no-ops when the launch carries no such dependency.  The host switch
+// mg_set_dependent_launch() turns the launch attribute on (used while a decode step is captured
+// into a CUDA graph, where every predecessor is a kernel).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+int mg_dependent_launch_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    bool dependent, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (dependent && mg_dependent_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}

@@ -93,20 +93,18 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         }
     }
 
-    // The epilogue's operands (bias, residual rows) are asked for now as well, into L2/L1, so
-    // that the epilogue does not wait on HBM after the sums are done.
+    // The bias is asked for now as well, so that the epilogue does not wait on HBM for it.
     {
         const int e = tid;
-        if (e < groups_per_round * R * MT) {
+        if (e < groups_per_round * R * MT && a.bias) {
             const int gi = e / (R * MT), rm = e - gi * (R * MT);
-            const int r = rm / MT, m = rm - r * MT;
-            const int n = (first_group + gi) * R + r;
-            if (gi < a.groups_per_cta && n < a.N && m < a.M) {
-                if (a.bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bias + n));
-                if (a.epilogue == EPI_RESIDUAL) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.residual + (size_t)m * a.N + n));
-            }
+            const int n = (first_group + gi) * R + rm / MT;
+            if (gi < a.groups_per_cta && n < a.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bias + n));
         }
     }
+    // Weights and bias do not depend on the kernel before this one; everything below does.
+    pdl_trigger();
+    pdl_wait();
 
     // ---- stage the activations as bfloat16 (with the LayerNorm prologue if asked) ----
     if (a.x32 != nullptr) {
@@ -284,12 +282,14 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
         configured = true;
     }
     cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t le;
     switch (mt) {
-        case 1: linear_skinny_kernel<1><<<grid, THREADS, smem, s>>>(a); break;
-        case 2: linear_skinny_kernel<2><<<grid, THREADS, smem, s>>>(a); break;
-        case 4: linear_skinny_kernel<4><<<grid, THREADS, smem, s>>>(a); break;
-        default: linear_skinny_kernel<8><<<grid, THREADS, smem, s>>>(a); break;
+        case 1: le = mg_launch(linear_skinny_kernel<1>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
+        case 2: le = mg_launch(linear_skinny_kernel<2>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
+        case 4: le = mg_launch(linear_skinny_kernel<4>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
+        default: le = mg_launch(linear_skinny_kernel<8>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
     }
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear_skinny: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("linear_skinny");
     return MG_OK;
 }

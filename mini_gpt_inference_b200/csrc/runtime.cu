@@ -30,3 +30,13 @@ MG_API int mg_set_device(int device) {
     if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
     return MG_OK;
 }
+
+static int g_dependent_launch = 0;
+
+int mg_dependent_launch_enabled() { return g_dependent_launch; }
+
+// Turn programmatic dependent launch on (1) or off (0) for the kernels that support it.
+MG_API int mg_set_dependent_launch(int on) {
+    g_dependent_launch = on ? 1 : 0;
+    return MG_OK;
+}

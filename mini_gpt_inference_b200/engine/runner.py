@@ -254,8 +254,17 @@ class ModelRunner:
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         launches = getattr(self.ops, "launches", 0)
-        with torch.cuda.graph(graph, pool=self._graph_pool):
-            state.logits = self.model.forward(ctx)
+        # Inside the graph every kernel follows a kernel, so the ones that can may start while
+        # their predecessor drains (programmatic dependent launch).
+        dependent = getattr(self.ops, "set_dependent_launch", None)
+        if dependent is not None:
+            dependent(True)
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                state.logits = self.model.forward(ctx)
+        finally:
+            if dependent is not None:
+                dependent(False)
         state.kernels = getattr(self.ops, "launches", 0) - launches
         if self._graph_pool is None:
             self._graph_pool = graph.pool()

@@ -65,6 +65,7 @@ class CudaOps:
         self.use_tensor_cores = True
         self.use_split_attention = True
         self.use_skinny = True
+        self.use_dependent_launch = True
         self.use_prefill_tc = True
         self._counter_buf = None
 
@@ -102,6 +103,12 @@ class CudaOps:
         if self._counter_buf is None or self._counter_buf.numel() < count:
             self._counter_buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=self.device)
         return self._counter_buf
+
+    def set_dependent_launch(self, on: bool) -> None:
+        """Let kernels that support it start while the kernel before them drains (used while a
+        decode step is captured into a CUDA graph)."""
+        check(self.lib.mg_set_dependent_launch(1 if (on and self.use_dependent_launch) else 0),
+              "set_dependent_launch")
 
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
