@@ -5,7 +5,8 @@
 // CTA) would leave most SMs idle on a 512- or 1536-row matrix.  Here the work is cut finely:
 // a warp task is R = 4 weight rows times one slice of K; a CTA of 8 warps takes a few such
 // tasks, so that a 512 x 2048 matrix still spreads over 128 CTAs with 16-byte loads from four
-// rows in flight per lane.  The activations sit in shared memory as bfloat16; sums are 32-bit.
+// rows in flight per lane.  The activations sit in shared memory as 32-bit copies of their
+// bfloat16 values; sums are 32-bit.
 //
 // Fused around the product, because at this size every extra kernel costs more than its work:
 //   * prologue: LayerNorm of the 32-bit residual rows (optionally gathered through an index),
@@ -13,8 +14,8 @@
 //   * epilogue: bias, tanh-GELU, bfloat16 or 32-bit store, or add into the 32-bit residual;
 //   * epilogue of the QKV projection: key and value features also go to their cache pages.
 //
-// Every output element sums its K terms in a fixed order (lane-strided within a slice, slices
-// in order), independent of M and of the other rows.  K must be a multiple of 8 and M * K
+// Every output element sums its K terms in a fixed order (lane-strided within a slice, lanes in
+// order, slices in order), independent of M and of the other rows.  K must be a multiple of 8 and M * K
 // bfloat16 must fit the shared memory; other sizes are refused (the tensor-core kernel takes
 // them).
 #include "common.cuh"
@@ -64,8 +65,10 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 template <int MT>   // rows of activations held (1, 2, 4 or 8); a.M <= MT
 __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    bf16* xs = reinterpret_cast<bf16*>(smem_raw);                           // [MT][K], rows >= M are zero
-    float* partial = reinterpret_cast<float*>(smem_raw + (size_t)MT * a.K * sizeof(bf16));  // [WARPS][R*MT]
+    // activations [MT][K] as 32-bit values that are exact bfloat16 numbers; rows >= M are zero
+    float* xs = reinterpret_cast<float*>(smem_raw);
+    float* partial = xs + (size_t)MT * a.K;                                   // [WARPS][R*MT]
+    float* red = partial + WARPS * R * MT;                                    // [WARPS][R*MT][33]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = a.K;
 
@@ -106,15 +109,51 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     pdl_trigger();
     pdl_wait();
 
-    // ---- stage the activations as bfloat16 (with the LayerNorm prologue if asked) ----
+    // ---- stage the activations (with the LayerNorm prologue if asked), rounded to bfloat16 ----
     if (a.x32 != nullptr) {
         for (int m = warp; m < MT; m += WARPS) {
-            bf16* dst = xs + (size_t)m * K;
+            float* dst = xs + (size_t)m * K;
             if (m >= a.M) {
-                for (int c = lane; c < K; c += 32) dst[c] = __float2bfloat16_rn(0.f);
+                for (int c = lane; c < K; c += 32) dst[c] = 0.f;
                 continue;
             }
             const float* src = a.x32 + (size_t)(a.row_index ? a.row_index[m] : m) * K;
+            if (K % 128 == 0 && K <= 1024) {
+                // the row lives in registers between the passes: 16-byte loads, one trip to memory
+                float4 v[8];
+                const int n4 = K / 128;
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n4) {
+                        v[i] = *reinterpret_cast<const float4*>(src + (lane + 32 * i) * 4);
+                        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+                    }
+                const float mean = warp_sum(sum) / (float)K;
+                float sq = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n4) {
+                        const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+                        sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+                    }
+                const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + a.eps);
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (i < n4) {
+                        const int c = (lane + 32 * i) * 4;
+                        const float4 g = *reinterpret_cast<const float4*>(a.gain + c);
+                        float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (a.shift) sh = *reinterpret_cast<const float4*>(a.shift + c);
+                        float4 y;
+                        y.x = __bfloat162float(__float2bfloat16_rn((v[i].x - mean) * rstd * g.x + sh.x));
+                        y.y = __bfloat162float(__float2bfloat16_rn((v[i].y - mean) * rstd * g.y + sh.y));
+                        y.z = __bfloat162float(__float2bfloat16_rn((v[i].z - mean) * rstd * g.z + sh.z));
+                        y.w = __bfloat162float(__float2bfloat16_rn((v[i].w - mean) * rstd * g.w + sh.w));
+                        *reinterpret_cast<float4*>(dst + c) = y;
+                    }
+                continue;
+            }
             float sum = 0.f;
             for (int c = lane; c < K; c += 32) sum += src[c];
             const float mean = warp_sum(sum) / (float)K;
@@ -127,16 +166,18 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             for (int c = lane; c < K; c += 32) {
                 float v = (src[c] - mean) * rstd * a.gain[c];
                 if (a.shift) v += a.shift[c];
-                dst[c] = __float2bfloat16_rn(v);
+                dst[c] = __bfloat162float(__float2bfloat16_rn(v));
             }
         }
     } else {
-        const int chunks = K / 8;
-        for (int i = tid; i < MT * chunks; i += THREADS) {
-            const int m = i / chunks, c = i - m * chunks;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (m < a.M) v = *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + c * 8);
-            *reinterpret_cast<uint4*>(xs + (size_t)m * K + c * 8) = v;
+        const int chunks8 = K / 8;
+        for (int i = tid; i < MT * chunks8; i += THREADS) {
+            const int m = i / chunks8, c = i - m * chunks8;
+            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (m < a.M) unpack8(*reinterpret_cast<const uint4*>(a.x + (size_t)m * K + c * 8), f);
+            float* dst = xs + (size_t)m * K + c * 8;
+            *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
         }
     }
     __syncthreads();
@@ -168,8 +209,9 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
                 for (int r = 0; r < R; ++r) unpack8(wraw[r], wf[r]);
 #pragma unroll
                 for (int m = 0; m < MT; ++m) {
-                    float xf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(xs + (size_t)m * K + c * 8), xf);
+                    const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + c * 8);
+                    const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + c * 8 + 4);
+                    const float xf[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
                     for (int r = 0; r < R; ++r)
 #pragma unroll
@@ -177,21 +219,21 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
                 }
             }
         }
-        // sum over the lanes; lane 0 keeps the totals
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                float v = acc[r][m];
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-                acc[r][m] = v;
-            }
-        if (lane == 0) {
+        // sum over the lanes through shared memory: lane l writes its R*MT sums as a column,
+        // then lane v adds up row v (33-word rows: no bank conflicts); the order is lane 0..31
+        {
+            float* mine = red + (size_t)warp * (R * MT) * 33;
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
-                for (int m = 0; m < MT; ++m) partial[warp * (R * MT) + r * MT + m] = acc[r][m];
+                for (int m = 0; m < MT; ++m) mine[(r * MT + m) * 33 + lane] = acc[r][m];
+            __syncwarp();
+            if (lane < R * MT) {
+                float total = 0.f;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) total += mine[lane * 33 + j];
+                partial[warp * (R * MT) + lane] = total;
+            }
         }
         __syncthreads();
         // ---- epilogue: one thread per (group of the round, row, token) ----
@@ -250,7 +292,7 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
     const int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-    const size_t smem = (size_t)mt * K * sizeof(bf16) + (size_t)WARPS * R * mt * sizeof(float);
+    const size_t smem = ((size_t)mt * K + (size_t)WARPS * R * mt * 34) * sizeof(float);
     if (M > MAX_M || K % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w & 15) || (x && ((uintptr_t)x & 15)))
         return mg_set_error(MG_ERR_UNSUPPORTED, "linear (skinny): needs M <= 8, K %% 8 == 0, aligned operands");
     MG_REQUIRE(k_pages == nullptr || (out_bf16 && epilogue == EPI_STORE && slots && v_pages && head_dim > 0 &&
