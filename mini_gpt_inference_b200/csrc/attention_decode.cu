@@ -259,16 +259,52 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // Merge with all loads in flight at once: one thread per block fetches its maximum and sum,
+    // then each thread adds up its share of the partial rows, eight loads at a time.
     const size_t base = pair * max_splits;
+    float* ml = scores;                                                 // reuse: [splits] weights
     float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
+    for (int s0 = 0; s0 < splits; s0 += THREADS) {
+        const int s = s0 + tid;
+        if (s < splits) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
+    }
+    M = warp_max(M);
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = red[0];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) M = fmaxf(M, red[w]);
+    __syncthreads();
     float denom = 0.f;
-    for (int s = 0; s < splits; ++s) denom += exp2f(__ldcg(&part_ml[(base + s) * 2]) - M) * __ldcg(&part_ml[(base + s) * 2 + 1]);
+    for (int s0 = 0; s0 < splits; s0 += THREADS) {
+        const int s = s0 + tid;
+        if (s < splits) {
+            const float w = exp2f(__ldcg(&part_ml[(base + s) * 2]) - M);
+            if (s < SPLIT) ml[s] = w;
+            denom += w * __ldcg(&part_ml[(base + s) * 2 + 1]);
+        }
+    }
+    denom = warp_sum(denom);
+    if (lane == 0) red[warp] = denom;
+    __syncthreads();
+    denom = red[0];
+#pragma unroll
+    for (int w = 1; w < WARPS; ++w) denom += red[w];
     const float inv = 1.0f / denom;
     for (int d = tid; d < D; d += THREADS) {
         float v = 0.f;
-        for (int s = 0; s < splits; ++s)                                // blocks in order
-            v += exp2f(__ldcg(&part_ml[(base + s) * 2]) - M) * __ldcg(&part_out[(base + s) * D + d]);
+        for (int s0 = 0; s0 < splits; s0 += 8) {                        // blocks in order, 8 loads in flight
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s0 + u < splits) {
+                    const int s = s0 + u;
+                    const float w = s < SPLIT ? ml[s] : exp2f(__ldcg(&part_ml[(base + s) * 2]) - M);
+                    v = fmaf(w, x[u], v);
+                }
+        }
         out[pair * D + d] = __float2bfloat16_rn(v * inv);
     }
 }

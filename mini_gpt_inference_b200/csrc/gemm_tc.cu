@@ -273,10 +273,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
                         }
                         if (epilogue == EPI_RESIDUAL) {
+                            // all loads first, then the adds and stores: a load after a store to the
+                            // same array cannot be moved up by the compiler, and eight dependent
+                            // round trips to memory would follow one another
                             float4* dst = reinterpret_cast<float4*>(residual + row + qc);
+                            float4 old[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) old[j] = dst[j];
 #pragma unroll
                             for (int j = 0; j < 8; ++j) {
-                                float4 o = dst[j];
+                                float4 o = old[j];
                                 o.x += v[4 * j]; o.y += v[4 * j + 1]; o.z += v[4 * j + 2]; o.w += v[4 * j + 3];
                                 dst[j] = o;
                             }
@@ -314,6 +320,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                 } else {
                     // p is a feature, q runs over tokens: a warp writes 32 neighbouring features
                     const float b = bias ? bias[p] : 0.f;
+                    float old[32];
+                    if (epilogue == EPI_RESIDUAL) {
+                        // the residual values of the whole chunk are fetched before any is written back
+#pragma unroll
+                        for (int j = 0; j < CHUNK; ++j) {
+                            const int q = q0 + c0 + j;
+                            old[j] = q < rows_q ? residual[(size_t)q * ld_out + p] : 0.f;
+                        }
+                    }
 #pragma unroll
                     for (int j = 0; j < CHUNK; ++j) {
                         const int q = q0 + c0 + j;
@@ -321,7 +336,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             float v = __uint_as_float(r[j]) + b;
                             if (epilogue == EPI_GELU) v = gelu_tanh(v);
                             const size_t idx = (size_t)q * ld_out + p;
-                            if (epilogue == EPI_RESIDUAL) residual[idx] += v;
+                            if (epilogue == EPI_RESIDUAL) residual[idx] = old[j] + v;
                             else if (out_bf16) ((bf16*)out_ptr)[idx] = __float2bfloat16_rn(v);
                             else ((float*)out_ptr)[idx] = v;
                         }
