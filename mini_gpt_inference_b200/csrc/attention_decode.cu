@@ -249,16 +249,17 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         part_ml[slot * 2 + 1] = l;
     }
     // ---- the CTA that finishes last merges the blocks of this (token, head) ----
-    __threadfence();
+    // The barrier orders every thread's partial writes before thread 0's release on the counter;
+    // the CTA that reads the final count acquires, so it sees the partial rows of all blocks.
     __syncthreads();
     if (tid == 0) {
-        const int done = atomicAdd(&counters[pair], 1);
+        int done;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(done) : "l"(counters + pair) : "memory");
         is_last = (done == splits - 1);
         if (is_last) counters[pair] = 0;                                // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
-    __threadfence();
     // Merge with all loads in flight at once: one thread per block fetches its maximum and sum,
     // then each thread adds up its share of the partial rows, eight loads at a time.
     const size_t base = pair * max_splits;
