@@ -25,6 +25,8 @@ class EngineConfig:
     dtype: str = "bfloat16"              # "bfloat16" | "float32"
     device: str = "cuda:0"
     use_cuda_graphs: bool = True         # replay decode-only steps from CUDA graphs
+    overlap_decode: bool = True          # in steady decoding, feed sampled tokens back on the device
+                                         # and read their ids one step late (outputs lag by a step)
 
     def __post_init__(self) -> None:
         if self.block_size <= 0 or self.num_blocks <= 0:

@@ -136,3 +136,19 @@ MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v
     MG_CHECK_LAUNCH("kv_store");
     return MG_OK;
 }
+
+// ---- feed sampled tokens back without a trip to the host -------------------------------------------
+// token_ids[i] = previous[source[i]] where source[i] >= 0; other rows keep what the host wrote.
+__global__ void gather_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ source,
+                                     const int* __restrict__ previous, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && source[i] >= 0) token_ids[i] = previous[source[i]];
+}
+
+MG_API int mg_gather_tokens(int* token_ids, const int* source, const int* previous, int n, void* stream) {
+    if (n == 0) return MG_OK;
+    MG_REQUIRE(n > 0 && token_ids && source && previous, "gather_tokens: bad arguments");
+    gather_tokens_kernel<<<ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(token_ids, source, previous, n);
+    MG_CHECK_LAUNCH("gather_tokens");
+    return MG_OK;
+}

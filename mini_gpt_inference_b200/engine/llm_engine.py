@@ -14,8 +14,9 @@ files from the network).  Stop conditions are therefore token ids (``stop_token_
 
 from __future__ import annotations
 
+from dataclasses import dataclass
 from pathlib import Path
-from typing import Sequence
+from typing import Any, Sequence
 
 import torch
 
@@ -25,6 +26,16 @@ from .build import LoadedModel, load_model, make_runner
 from .request import Request, RequestOutput, SequenceState
 from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler
+
+
+@dataclass
+class _InFlight:
+    """A decoding step whose sampled ids are still on their way to the host."""
+
+    seqs: list                 # the requests of the step, in row order
+    ids_device: Any            # int32 ids on the device (input of the next step)
+    ids_host: Any              # pinned copy in progress
+    ready: Any                 # event recorded after the copy
 
 
 class LLMEngine:
@@ -46,6 +57,14 @@ class LLMEngine:
         self.sampler = Sampler(ops, loaded.device, vocab_limit, seed)
         self.max_context = self.runner.max_context
         self._sequences: dict[str, SequenceState] = {}
+        # Steady decoding overlaps the host with the device: a step is launched with the tokens
+        # of the step before still on the device, and that step's ids are read while this one
+        # runs.  What step() returns then lags one step behind what the device has computed.
+        self._overlap = (self.engine_cfg.overlap_decode and loaded.device.type == "cuda"
+                         and self.runner.use_cuda_graphs)
+        self._inflight: _InFlight | None = None
+        self._pinned_ids = [None, None]
+        self.num_overlapped_steps = 0
         self.num_steps = 0
         self.num_tokens_run = 0
         self.num_tokens_generated = 0
@@ -82,14 +101,89 @@ class LLMEngine:
         self._sequences[request.request_id] = seq
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     def cancel_request(self, request_id: str) -> bool:
+        self._drain()                                   # (its outputs are dropped: the request is cancelled)
         self._sequences.pop(request_id, None)
         return self.scheduler.cancel_by_id(request_id)
 
     # ---- one step ---------------------------------------------------------------------------
     def step(self) -> list[RequestOutput]:
+        """Advance by one step and return what became known: one RequestOutput per request whose
+        next token the host has read.  In steady decoding these are the tokens of the step before
+        the one just launched."""
+        if self._overlap:
+            rows = self.scheduler.schedule_steady_decode()
+            if rows is not None and self.runner.can_feed_tokens_on_device(len(rows)):
+                return self._step_overlapped(rows)
+            if rows:                                    # reserved pages stay reserved; harmless
+                pass
+        outputs = self._drain()
+        return outputs + self._step_general()
+
+    def _step_overlapped(self, rows: list[SequenceState]) -> list[RequestOutput]:
+        previous = self._inflight
+        if not rows:                                    # everybody is complete by length
+            return self._drain()
+        source_row = {id(s): i for i, s in enumerate(previous.seqs)} if previous else {}
+        entries, sources = [], []
+        for seq in rows:
+            if seq.num_inflight:
+                entries.append(StepEntry(seq.request_id, [0], [0]))     # the token is on the device
+                sources.append(source_row[id(seq)])
+            else:
+                entries.append(StepEntry(seq.request_id, [seq.token_at(seq.num_computed_tokens)], [0]))
+                sources.append(-1)
+        logits = self.runner.step(entries, copy=False, token_sources=sources,
+                                  previous_ids=previous.ids_device if previous else None)
+        self.num_steps += 1
+        self.num_overlapped_steps += 1
+        self.num_tokens_run += len(rows)
+        ids = self.sampler.sample(
+            logits, [s.request.sampling_params for s in rows], [s.seed for s in rows],
+            [s.num_generated for s in rows])
+        slot = self.num_steps % 2
+        if self._pinned_ids[slot] is None or self._pinned_ids[slot].numel() < len(rows):
+            self._pinned_ids[slot] = torch.empty(max(len(rows), self.engine_cfg.max_batch_size),
+                                                 dtype=torch.int32, pin_memory=True)
+        host = self._pinned_ids[slot][: len(rows)]
+        host.copy_(ids, non_blocking=True)
+        ready = torch.cuda.Event()
+        ready.record()
+        for seq in rows:
+            seq.num_computed_tokens += 1
+            seq.num_inflight += 1
+        self._inflight = _InFlight(rows, ids, host, ready)
+        # while the device runs this step, read the ids of the step before
+        return self._process(previous) if previous else []
+
+    def _process(self, flight: _InFlight) -> list[RequestOutput]:
+        """The ids of an earlier step have arrived (or are waited for): record them."""
+        flight.ready.synchronize()
+        outputs = []
+        for seq, token in zip(flight.seqs, flight.ids_host.tolist()):
+            if seq.is_finished():
+                continue                                # it ended a step earlier; this token is dropped
+            seq.num_inflight -= 1
+            seq.output_token_ids.append(int(token))
+            self.num_tokens_generated += 1
+            reason = self._check_finish(seq, int(token))
+            if reason is not None:
+                self.scheduler.finish(seq, reason)
+                self._sequences.pop(seq.request_id, None)
+            outputs.append(RequestOutput(seq.request_id, [int(token)], "", seq.is_finished(),
+                                         seq.finish_reason))
+        return outputs
+
+    def _drain(self) -> list[RequestOutput]:
+        """Read the ids that are still on their way, so that the host knows every token."""
+        if self._inflight is None:
+            return []
+        flight, self._inflight = self._inflight, None
+        return self._process(flight)
+
+    def _step_general(self) -> list[RequestOutput]:
         chunks = self.scheduler.schedule()
         if not chunks:
             return []
@@ -157,7 +251,8 @@ class LLMEngine:
 
     def stats(self) -> dict:
         out = dict(self.runner.manager.stats())
-        out.update(steps=self.num_steps, tokens_run=self.num_tokens_run,
+        out.update(steps=self.num_steps, overlapped_steps=self.num_overlapped_steps,
+                   tokens_run=self.num_tokens_run,
                    tokens_generated=self.num_tokens_generated,
                    preemptions=self.scheduler.num_preemptions,
                    running=len(self.scheduler.running), waiting=len(self.scheduler.waiting))

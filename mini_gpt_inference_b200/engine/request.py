@@ -38,6 +38,9 @@ class SequenceState:
     finish_reason: str | None = None
     seed: int = 0
     arrival: int = 0
+    # Tokens sampled on the device whose ids the host has not read yet (0 or 1): they count as
+    # generated for scheduling, their values arrive one step later.
+    num_inflight: int = 0
 
     @property
     def request_id(self) -> str:
@@ -49,8 +52,13 @@ class SequenceState:
 
     @property
     def num_tokens(self) -> int:
-        """Prompt plus everything generated so far."""
-        return self.prompt_len + len(self.output_token_ids)
+        """Prompt plus everything generated so far (tokens still on their way from the device
+        included)."""
+        return self.prompt_len + len(self.output_token_ids) + self.num_inflight
+
+    @property
+    def num_generated(self) -> int:
+        return len(self.output_token_ids) + self.num_inflight
 
     @property
     def num_pending_tokens(self) -> int:

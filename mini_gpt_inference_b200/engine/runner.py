@@ -224,7 +224,7 @@ class ModelRunner:
     # ---- decode steps as CUDA graphs ---------------------------------------------------------
     def _graph_layout(self, rows: int):
         g, pages = len(self.manager.groups), self.max_pages
-        sizes = [rows] * 8 + [rows * pages] * g + [rows] * g
+        sizes = [rows] * 8 + [rows * pages] * g + [rows] * g + [rows]     # last: token sources
         offsets = [0]
         for n in sizes:
             offsets.append(offsets[-1] + n)
@@ -271,7 +271,8 @@ class ModelRunner:
         state.graph = graph
         return state
 
-    def _fill_graph_inputs(self, state: _DecodeGraph, entries: Sequence[StepEntry]) -> None:
+    def _fill_graph_inputs(self, state: _DecodeGraph, entries: Sequence[StepEntry],
+                           token_sources=None) -> None:
         m = self.manager
         rows, off = state.rows, state.offsets
         buf = state.staging.numpy()
@@ -287,6 +288,10 @@ class ModelRunner:
         for i in range(g):
             buf[off[8 + i]: off[9 + i]] = NO_PAGE
             buf[off[8 + g + i]: off[9 + g + i]] = -1
+        src = off[8 + 2 * g]
+        buf[src: src + rows] = -1                                       # token comes from the host
+        if token_sources is not None:
+            buf[src: src + len(entries)] = token_sources
         for r, e in enumerate(entries):
             req = m.get(e.request_id)
             buf[off[0] + r] = int(e.tokens[0])
@@ -303,19 +308,25 @@ class ModelRunner:
                     raise StepError(f"request {e.request_id!r} writes to a page it gave back")
                 buf[off[8 + g + i] + r] = page * pt + req.length % pt
 
-    def _graph_step(self, entries: Sequence[StepEntry], copy: bool):
+    def _graph_step(self, entries: Sequence[StepEntry], copy: bool, token_sources=None,
+                    previous_ids=None):
         rows = next(b for b in self.GRAPH_ROWS if b >= len(entries))
         state = self._graphs.get(rows)
         if state is None:
             state = self._graphs[rows] = self._capture(rows)
         if self._copy_done is not None:
             self._copy_done.synchronize()                 # the staging buffer is free again
-        self._fill_graph_inputs(state, entries)
+        self._fill_graph_inputs(state, entries, token_sources)
         state.meta.copy_(state.staging, non_blocking=True)
         if self._copy_done is None:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()
         self.last_h2d_bytes = 4 * state.offsets[-1]
+        if token_sources is not None and previous_ids is not None:
+            off = state.offsets
+            g = len(self.manager.groups)
+            self.ops.gather_tokens(state.meta[off[0]: off[1]], state.meta[off[8 + 2 * g]: off[9 + 2 * g]],
+                                   previous_ids)
         state.graph.replay()
         self.graph_replays += 1
         if hasattr(self.ops, "launches"):
@@ -330,18 +341,31 @@ class ModelRunner:
             copy = False
         return logits.clone() if copy else logits
 
-    def step(self, entries: Sequence[StepEntry], copy: bool = True) -> torch.Tensor | None:
+    def can_feed_tokens_on_device(self, n_entries: int) -> bool:
+        """Whether a step of ``n_entries`` single tokens may take its tokens from the ids that the
+        previous step sampled, without the host seeing them first (``token_sources``)."""
+        return self.use_cuda_graphs and 0 < n_entries <= self.GRAPH_ROWS[-1]
+
+    def step(self, entries: Sequence[StepEntry], copy: bool = True, token_sources=None,
+             previous_ids=None) -> torch.Tensor | None:
         """Run the entries as one batch.  Returns ``[wanted, vocab]`` float32 logits on the
         device (None if nothing was wanted).  With ``copy=False`` the result may be a view of
-        a buffer that the next step overwrites."""
+        a buffer that the next step overwrites.
+
+        ``token_sources`` (one int per entry, only for steps of single tokens): where it is
+        >= 0 the entry's token is taken on the device from ``previous_ids[token_sources[i]]``
+        (int32 ids sampled by the step before) and the entry's own token is a placeholder."""
         entries = list(entries)
         if not entries:
             return None
         self._validate(entries)
         self._reserve(entries)
+        if token_sources is not None and not (
+                self.can_feed_tokens_on_device(len(entries)) and all(len(e.tokens) == 1 for e in entries)):
+            raise StepError("tokens can be fed on the device only to steps of single tokens")
         if (self.use_cuda_graphs and len(entries) <= self.GRAPH_ROWS[-1]
                 and all(len(e.tokens) == 1 for e in entries)):
-            logits = self._graph_step(entries, copy)
+            logits = self._graph_step(entries, copy, token_sources, previous_ids)
         else:
             ctx = self.build_context(entries)
             logits = self.model.forward(ctx)

@@ -122,6 +122,33 @@ class Scheduler:
             budget -= count
         return chunks
 
+    def schedule_steady_decode(self) -> list[SequenceState] | None:
+        """If the next step is plain decoding — nobody waits, every running request has exactly
+        its last token pending (or already has all the tokens it may generate) and the pages for
+        one more token each are free — reserve those pages and return the requests to run.
+        Otherwise change nothing and return None: the caller takes the general path.  It looks
+        at token counts only, never at token values, so it can run before the host has seen the
+        tokens of the step before."""
+        if self.waiting or not self.running or len(self.running) > self.max_num_batched_tokens:
+            return None
+        rows = []
+        for seq in self.running:
+            if seq.num_generated >= seq.request.sampling_params.max_tokens:
+                continue                          # complete by length: finishes when its ids arrive
+            if seq.num_pending_tokens != 1:
+                return None
+            rows.append(seq)
+        need = [0] * len(self.cache.groups)
+        for seq in rows:
+            for g, n in enumerate(self.cache.pages_needed(seq.request_id, seq.num_computed_tokens + 1)):
+                need[g] += n
+        if any(n > group.pool.num_free for n, group in zip(need, self.cache.groups)):
+            return None
+        for seq in rows:
+            ok = self.cache.reserve(seq.request_id, seq.num_computed_tokens + 1)
+            assert ok
+        return rows
+
     @staticmethod
     def _chunk(seq: SequenceState, count: int) -> ScheduledChunk:
         start = seq.num_computed_tokens

@@ -23,6 +23,7 @@ _SIGNATURES = {
     "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "mg_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
     "mg_gather_rows": [_P, _P, _P, _I, _I, _P],
+    "mg_gather_tokens": [_P, _P, _P, _I, _P],
     "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_skinny": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,

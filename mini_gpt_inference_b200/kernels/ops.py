@@ -154,6 +154,14 @@ class CudaOps:
                                       self._stream()), "gather_rows")
         return out
 
+    def gather_tokens(self, token_ids, source, previous):
+        """token_ids[i] = previous[source[i]] for rows with source[i] >= 0 (in place): the tokens a
+        step sampled become the next step's inputs without passing through the host."""
+        for name, t in (("token_ids", token_ids), ("source", source), ("previous", previous)):
+            self._want(t, torch.int32, name, 1)
+        self._run(self.lib.mg_gather_tokens(_ptr(token_ids), _ptr(source), _ptr(previous),
+                                            token_ids.numel(), self._stream()), "gather_tokens")
+
     # ---- projections ----------------------------------------------------------------------------
     def defer_layernorm(self, x32, gain, shift, eps, out_dtype, rows=None):
         """A LayerNorm to be fused into the projection that consumes it, where that pays."""

@@ -232,3 +232,40 @@ def test_everything_is_given_back_after_a_busy_run():
     assert cache.num_free_pages() == 10 and cache.slots.num_free == 4
     assert all(q.is_finished() for q in seqs) and s.num_preemptions > 0
     assert all(len(q.output_token_ids) == q.request.sampling_params.max_tokens for q in seqs)
+
+
+def test_steady_decode_schedule_looks_at_counts_only():
+    cache, s = make(num_pages=8, page_tokens=2, max_batch=3, budget=16)
+    a, b = seq("a", 3, max_tokens=3), seq("b", 2, max_tokens=8)
+    s.add_request(a)
+    s.add_request(b)
+    assert s.schedule_steady_decode() is None               # somebody waits: general path
+    run_step(s, s.schedule())                               # prompts in, first tokens sampled
+    rows = s.schedule_steady_decode()
+    assert [q.request_id for q in rows] == ["a", "b"]
+    free = cache.num_free_pages()
+    # the engine launches the step and counts the new tokens as in flight, values unknown
+    for q in rows:
+        q.num_computed_tokens += 1
+        q.num_inflight += 1
+    for q in rows:                                          # ... their ids arrive
+        q.num_inflight -= 1
+        q.output_token_ids.append(7)
+    rows = s.schedule_steady_decode()
+    assert [q.request_id for q in rows] == ["a", "b"] and cache.num_free_pages() <= free
+    for q in rows:
+        q.num_computed_tokens += 1
+        q.num_inflight += 1
+    # a has 3 tokens now (one of them in flight): complete by length, not run again
+    rows = s.schedule_steady_decode()
+    assert [q.request_id for q in rows] == ["b"]
+    # pages short: nothing is reserved and the general path must decide
+    cache.admit("hog")
+    assert cache.reserve("hog", 2 * cache.num_free_pages())
+    b.num_computed_tokens += 1
+    b.num_inflight -= 1
+    b.output_token_ids.append(7)
+    b.num_inflight += 1
+    before = cache.num_free_pages()
+    assert s.schedule_steady_decode() is None or cache.num_free_pages() == before
+    cache.check()
