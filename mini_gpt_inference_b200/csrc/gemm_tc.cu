@@ -174,6 +174,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int p0 = blockIdx.x * TILE_P, q0 = blockIdx.y * BN;
     const int num_kb = (K + BLOCK_K - 1) / BLOCK_K;
+    // The epilogue's operands are asked for while the main loop runs: the tile's slice of the
+    // bias goes to shared memory, the thread's row of the residual stream is pulled towards L2.
+    __shared__ __align__(16) float bias_tile[BN];
+    if (!SWAP) {
+        for (int j = tid; j < BN; j += 128) bias_tile[j] = (bias && q0 + j < rows_q) ? bias[q0 + j] : 0.f;
+        if (epilogue == EPI_RESIDUAL && p0 + tid < rows_p) {
+            const float* rrow = residual + (size_t)(p0 + tid) * ld_out + q0;
+            for (int j = 0; j < BN && q0 + j < rows_q; j += 32) asm volatile("prefetch.global.L2 [%0];" ::"l"(rrow + j));
+        }
+    }
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -261,8 +271,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         float v[32];
 #pragma unroll
                         for (int j = 0; j < 32; j += 4) {
-                            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (bias) b4 = *reinterpret_cast<const float4*>(bias + qc + j);
+                            const float4 b4 = *reinterpret_cast<const float4*>(bias_tile + c0 + j);
                             v[j] = __uint_as_float(r[j]) + b4.x;
                             v[j + 1] = __uint_as_float(r[j + 1]) + b4.y;
                             v[j + 2] = __uint_as_float(r[j + 2]) + b4.z;
@@ -309,7 +318,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                         for (int j = 0; j < CHUNK; ++j) {
                             const int q = qc + j;
                             if (q < rows_q) {
-                                float v = __uint_as_float(r[j]) + (bias ? bias[q] : 0.f);
+                                float v = __uint_as_float(r[j]) + bias_tile[c0 + j];
                                 if (epilogue == EPI_GELU) v = gelu_tanh(v);
                                 if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
                                 else if (out_bf16) ((bf16*)out_ptr)[row + q] = __float2bfloat16_rn(v);
@@ -427,7 +436,7 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
     const size_t smem = (size_t)stages * stage_bytes + sizeof(Barriers) + 1024;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear: cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
