@@ -63,6 +63,7 @@ class LLMEngine:
         self._overlap = (self.engine_cfg.overlap_decode and loaded.device.type == "cuda"
                          and self.runner.use_cuda_graphs)
         self._inflight: _InFlight | None = None
+        self._held_outputs: list[RequestOutput] = []
         self._pinned_ids = [None, None]
         self.num_overlapped_steps = 0
         self.num_steps = 0
@@ -101,10 +102,12 @@ class LLMEngine:
         self._sequences[request.request_id] = seq
 
     def has_unfinished_requests(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return self.scheduler.has_work() or self._inflight is not None or bool(self._held_outputs)
 
     def cancel_request(self, request_id: str) -> bool:
-        self._drain()                                   # (its outputs are dropped: the request is cancelled)
+        # What is still on its way from the device is read first; the next step() returns it
+        # (the cancelled request's own last token included, as it was generated before the call).
+        self._held_outputs.extend(self._drain())
         self._sequences.pop(request_id, None)
         return self.scheduler.cancel_by_id(request_id)
 
@@ -113,12 +116,16 @@ class LLMEngine:
         """Advance by one step and return what became known: one RequestOutput per request whose
         next token the host has read.  In steady decoding these are the tokens of the step before
         the one just launched."""
+        held, self._held_outputs = self._held_outputs, []
+        return held + self._step()
+
+    def _step(self) -> list[RequestOutput]:
         if self._overlap:
             rows = self.scheduler.schedule_steady_decode()
             if rows is not None and self.runner.can_feed_tokens_on_device(len(rows)):
                 return self._step_overlapped(rows)
-            if rows:                                    # reserved pages stay reserved; harmless
-                pass
+            # (pages that the attempt reserved stay with their requests; the general path
+            # reserves the same ones again, which changes nothing)
         outputs = self._drain()
         return outputs + self._step_general()
 

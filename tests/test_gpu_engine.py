@@ -98,3 +98,61 @@ def test_vocab_limit_masks_padding_ids():
                            [SamplingParams(max_tokens=8, temperature=0.0),
                             SamplingParams(max_tokens=8, temperature=1.5, seed=3)])
     assert all(t < 10 for o in outs for t in o["token_ids"])
+
+
+def _run_stream(engine, cfg, arrivals, cancel_at=None):
+    """Drive the engine step by step, adding requests at given step numbers; returns per request
+    (tokens, finish reason) and the number of steps."""
+    results, step = {}, 0
+    pending = sorted(arrivals, key=lambda a: a[0])
+    while pending or engine.has_unfinished_requests():
+        while pending and pending[0][0] <= step:
+            _, req = pending.pop(0)
+            engine.add_request(req)
+            results[req.request_id] = [[], None]
+        if cancel_at and step == cancel_at[0]:
+            engine.cancel_request(cancel_at[1])
+        for out in engine.step():
+            results[out.request_id][0].extend(out.new_token_ids)
+            if out.finished:
+                results[out.request_id][1] = out.finish_reason
+        step += 1
+        assert step < 2000
+    return results
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_overlapped_decoding_gives_the_same_answers_one_step_late(dtype):
+    """With the host one step behind the device (tokens fed back on the device, ids read late),
+    every request gets the same tokens and finish reasons as with the host in lock step: also
+    when a request ends on an end-of-text or stop token that the host sees only after the next
+    step was launched, when requests arrive in the middle, and when one is cancelled."""
+    base = dict(block_size=8, num_blocks=40, max_batch_size=4, max_num_batched_tokens=16, max_prefill_chunk=9)
+    answers = []
+    for overlap in (False, True):
+        cfg, tensors, engine = engine_for("B", dtype, sharp=False, overlap_decode=overlap, **base)
+        prompts = [tokens_for(cfg, n, 80 + i) for i, n in enumerate([7, 3, 12, 5, 9])]
+        # what the first request generates decides its end-of-text and the second's stop token
+        probe = engine.generate([prompts[0], prompts[1]], SamplingParams(max_tokens=9, temperature=0.0))
+        eot = probe[0]["token_ids"][4]
+        stop = probe[1]["token_ids"][6]
+        arrivals = [
+            (0, Request("a", prompts[0], SamplingParams(max_tokens=30, temperature=0.0), eot_token_id=eot)),
+            (0, Request("b", prompts[1], SamplingParams(max_tokens=30, temperature=0.0, stop_token_ids=[stop]))),
+            (3, Request("c", prompts[2], SamplingParams(max_tokens=11, temperature=0.7, top_k=20, seed=5))),
+            (9, Request("d", prompts[3], SamplingParams(max_tokens=1, temperature=0.0))),
+            (10, Request("e", prompts[4], SamplingParams(max_tokens=25, temperature=0.0))),
+        ]
+        results = _run_stream(engine, cfg, arrivals, cancel_at=(14, "e"))
+        assert results["a"][1] == "eot" and results["a"][0][-1] == eot
+        assert results["b"][1] == "stop" and results["b"][0][-1] == stop
+        assert results["c"][1] == "length" and len(results["c"][0]) == 11
+        assert results["d"] == [results["d"][0], "length"] and len(results["d"][0]) == 1
+        assert engine.stats()["allocated_blocks"] == 0 and engine.stats()["free_state_slots"] == 4
+        engine.runner.manager.check()
+        if overlap:
+            assert engine.num_overlapped_steps > 5
+        else:
+            assert engine.num_overlapped_steps == 0
+        answers.append({k: v for k, v in results.items() if k != "e"})
+    assert answers[0] == answers[1]
