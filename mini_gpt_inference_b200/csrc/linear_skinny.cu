@@ -1,12 +1,19 @@
 // Projection of a handful of tokens (decoding at small batch): out[m, n] = x[m, :] . w[n, :].
 //
-// With up to 8 tokens a projection is a stream over the weights: every weight is read once and
-// used M times, far below what tensor cores need, and the tensor-core tile (128 weight rows per
-// CTA) would leave most SMs idle on a 512- or 1536-row matrix.  Here the work is cut finely:
-// a warp task is R = 4 weight rows times one slice of K; a CTA of 8 warps takes a few such
-// tasks, so that a 512 x 2048 matrix still spreads over 128 CTAs with 16-byte loads from four
-// rows in flight per lane.  The activations sit in shared memory as 32-bit copies of their
-// bfloat16 values; sums are 32-bit.
+// With up to 16 tokens a projection is a stream over the weights: every weight is read once,
+// far below what a 128-row tensor-core tile needs, and such tiles would leave most SMs idle on a
+// 512- or 1536-row matrix.  Here the work is cut finely: a warp task is 8 weight rows times one
+// slice of K, a CTA of 8 warps takes a few such tasks, so that a 512 x 2048 matrix still spreads
+// over 64 CTAs, and each lane asks for all its weights (16-byte loads) before it waits for the
+// kernel in front of it.
+//
+// The sums run on the tensor cores through warp-level mma (m16n8k16, bfloat16 in, 32-bit
+// accumulate): the 16 rows of the A operand are the tokens, the 8 columns of B are weight rows.
+// A lane's 16-byte load of weights (8 consecutive k of one row) feeds two mma's; which of the
+// sixteen k slots of an mma a value takes is free as long as A and B agree, so the activations
+// are read from shared memory with the same 16-byte pattern and no shuffle is needed.  What is
+// left of the old cost (unpacking, 256 multiply-adds and a 32-lane reduction per lane) is two
+// instructions; the K slices of a tile are added up in order through shared memory.
 //
 // Fused around the product, because at this size every extra kernel costs more than its work:
 //   * prologue: LayerNorm of the 32-bit residual rows (optionally gathered through an index),
@@ -14,10 +21,9 @@
 //   * epilogue: bias, tanh-GELU, bfloat16 or 32-bit store, or add into the 32-bit residual;
 //   * epilogue of the QKV projection: key and value features also go to their cache pages.
 //
-// Every output element sums its K terms in a fixed order (lane-strided within a slice, lanes in
-// order, slices in order), independent of M and of the other rows.  K must be a multiple of 8 and M * K
-// bfloat16 must fit the shared memory; other sizes are refused (the tensor-core kernel takes
-// them).
+// Every output element sums its K terms in a fixed order (k blocks in order inside a slice,
+// slices in order), independent of M and of the other rows.  K must be a multiple of 8 and the
+// activations must fit the shared memory; other sizes are refused (the tensor-core GEMM takes them).
 #include "common.cuh"
 
 #define EPI_STORE 0
@@ -26,10 +32,12 @@
 
 namespace {
 
-constexpr int MAX_M = 8;
-constexpr int R = 4;                 // weight rows per warp task
+constexpr int MAX_M = 16;
+constexpr int TILE_N = 8;            // weight rows per warp task
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
+constexpr int PRE = 8;               // k blocks (of 32) whose weights a lane holds at once
+constexpr int XPAD = 64;             // bytes between activation rows beyond K bf16 (no bank conflicts)
 
 struct SkinnyArgs {
     const bf16* x;                   // [M, K] bfloat16 activations, or null with a LayerNorm prologue
@@ -43,8 +51,8 @@ struct SkinnyArgs {
     void* out;                       // [M, N]
     float* residual;                 // [M, N] for EPI_RESIDUAL
     int M, N, K, epilogue, out_bf16;
-    int k_splits;                    // warps that share one group of R rows (1, 2, 4 or 8)
-    int groups_per_cta;              // groups of R rows per CTA
+    int k_splits;                    // warps that share one tile of 8 rows (1, 2, 4 or 8)
+    int tiles_per_cta;
     // key/value sink of the QKV projection (k_pages null: none)
     bf16* k_pages;
     bf16* v_pages;
@@ -52,71 +60,67 @@ struct SkinnyArgs {
     int q_width, n_kv_head, head_dim, page_tokens;
 };
 
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 v = __bfloat1622float2(h[i]);
-        f[2 * i] = v.x;
-        f[2 * i + 1] = v.y;
-    }
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int MT>   // rows of activations held (1, 2, 4 or 8); a.M <= MT
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int MT>   // token rows of the A operand: 8 (rows 8..15 are zero) or 16; a.M <= MT
 __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
-    // activations [MT][K] as 32-bit values that are exact bfloat16 numbers; rows >= M are zero
-    float* xs = reinterpret_cast<float*>(smem_raw);
-    float* partial = xs + (size_t)MT * a.K;                                   // [WARPS][R*MT]
-    float* red = partial + WARPS * R * MT;                                    // [WARPS][R*MT][33]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int K = a.K;
+    const int xstride = K * 2 + XPAD;                                         // bytes per token row
+    uint8_t* xs = smem_raw;                                                   // [MT][K] bf16, padded rows
+    float* partial = reinterpret_cast<float*>(smem_raw + (size_t)MT * xstride);   // [WARPS][MT][8]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
 
     const int ks = a.k_splits;
-    const int groups_per_round = WARPS / ks;
-    const int my_group_in_round = warp / ks, my_slice = warp % ks;
-    // slice edges at multiples of 8 elements
-    const int chunks = K / 8;
-    const int c_begin = (int)((long long)chunks * my_slice / ks), c_end = (int)((long long)chunks * (my_slice + 1) / ks);
-    const int first_group = blockIdx.x * a.groups_per_cta;
-    const int total_groups = (a.N + R - 1) / R;
+    const int tiles_per_round = WARPS / ks;
+    const int my_tile_in_round = warp / ks, my_slice = warp % ks;
+    const int kblocks = (K + 31) / 32;
+    const int b_begin = (int)((long long)kblocks * my_slice / ks), b_end = (int)((long long)kblocks * (my_slice + 1) / ks);
+    const int first_tile = blockIdx.x * a.tiles_per_cta;
+    const int total_tiles = (a.N + TILE_N - 1) / TILE_N;
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
-    // Ask for the first weights of this warp's first task before anything else: they travel
-    // from HBM while the activations are staged (and normalised) below.
-    uint4 first_w[R];
-    bool have_first = false;
+    // Ask for the weights of this warp's first task before anything else: they travel from HBM
+    // while the kernel in front drains and the activations are staged (and normalised) below.
+    uint4 first_w[PRE];
     {
-        const int group = first_group + my_group_in_round;
-        const int c = c_begin + lane;
-        if (my_group_in_round < a.groups_per_cta && group < total_groups && c < c_end) {
+        const int tile = first_tile + my_tile_in_round;
+        const bool live = my_tile_in_round < a.tiles_per_cta && tile < total_tiles;
+        const bf16* wrow = a.w + (size_t)min(tile * TILE_N + g, a.N - 1) * K;
 #pragma unroll
-            for (int r = 0; r < R; ++r)
-                first_w[r] = *reinterpret_cast<const uint4*>(a.w + (size_t)min(group * R + r, a.N - 1) * K + c * 8);
-            have_first = true;
+        for (int i = 0; i < PRE; ++i) {
+            const int k = (b_begin + i) * 32 + 8 * t;
+            first_w[i] = (live && b_begin + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow + k) : zero4;
         }
     }
-
-    // The bias is asked for now as well, so that the epilogue does not wait on HBM for it.
+    // The bias of the first result of this thread as well, so that the epilogue does not wait for it.
+    float first_bias = 0.f;
     {
-        const int e = tid;
-        if (e < groups_per_round * R * MT && a.bias) {
-            const int gi = e / (R * MT), rm = e - gi * (R * MT);
-            const int n = (first_group + gi) * R + rm / MT;
-            if (gi < a.groups_per_cta && n < a.N) asm volatile("prefetch.global.L1 [%0];" ::"l"(a.bias + n));
-        }
+        const int ti = tid / (MT * TILE_N), r = tid % TILE_N;
+        const int n = (first_tile + ti) * TILE_N + r;
+        if (a.bias && ti < tiles_per_round && ti < a.tiles_per_cta && n < a.N) first_bias = a.bias[n];
     }
     // Weights and bias do not depend on the kernel before this one; everything below does.
     pdl_trigger();
     pdl_wait();
 
-    // ---- stage the activations (with the LayerNorm prologue if asked), rounded to bfloat16 ----
+    // ---- stage the activations (with the LayerNorm prologue if asked) as bfloat16 ----
+    // Rows at and past M stay as they are: a token's results depend on its own row only.
     if (a.x32 != nullptr) {
-        for (int m = warp; m < MT; m += WARPS) {
-            float* dst = xs + (size_t)m * K;
-            if (m >= a.M) {
-                for (int c = lane; c < K; c += 32) dst[c] = 0.f;
-                continue;
-            }
+        for (int m = warp; m < a.M; m += WARPS) {
+            uint8_t* dst = xs + (size_t)m * xstride;
             const float* src = a.x32 + (size_t)(a.row_index ? a.row_index[m] : m) * K;
             if (K % 128 == 0 && K <= 1024) {
                 // the row lives in registers between the passes: 16-byte loads, one trip to memory
@@ -142,15 +146,13 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
                 for (int i = 0; i < 8; ++i)
                     if (i < n4) {
                         const int c = (lane + 32 * i) * 4;
-                        const float4 g = *reinterpret_cast<const float4*>(a.gain + c);
+                        const float4 gn = *reinterpret_cast<const float4*>(a.gain + c);
                         float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
                         if (a.shift) sh = *reinterpret_cast<const float4*>(a.shift + c);
-                        float4 y;
-                        y.x = __bfloat162float(__float2bfloat16_rn((v[i].x - mean) * rstd * g.x + sh.x));
-                        y.y = __bfloat162float(__float2bfloat16_rn((v[i].y - mean) * rstd * g.y + sh.y));
-                        y.z = __bfloat162float(__float2bfloat16_rn((v[i].z - mean) * rstd * g.z + sh.z));
-                        y.w = __bfloat162float(__float2bfloat16_rn((v[i].w - mean) * rstd * g.w + sh.w));
-                        *reinterpret_cast<float4*>(dst + c) = y;
+                        uint2 y;
+                        y.x = pack_bf16((v[i].x - mean) * rstd * gn.x + sh.x, (v[i].y - mean) * rstd * gn.y + sh.y);
+                        y.y = pack_bf16((v[i].z - mean) * rstd * gn.z + sh.z, (v[i].w - mean) * rstd * gn.w + sh.w);
+                        *reinterpret_cast<uint2*>(dst + c * 2) = y;
                     }
                 continue;
             }
@@ -166,90 +168,79 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             for (int c = lane; c < K; c += 32) {
                 float v = (src[c] - mean) * rstd * a.gain[c];
                 if (a.shift) v += a.shift[c];
-                dst[c] = __bfloat162float(__float2bfloat16_rn(v));
+                reinterpret_cast<bf16*>(dst)[c] = __float2bfloat16_rn(v);
             }
         }
     } else {
         const int chunks8 = K / 8;
-        for (int i = tid; i < MT * chunks8; i += THREADS) {
+        for (int i = tid; i < a.M * chunks8; i += THREADS) {
             const int m = i / chunks8, c = i - m * chunks8;
-            float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            if (m < a.M) unpack8(*reinterpret_cast<const uint4*>(a.x + (size_t)m * K + c * 8), f);
-            float* dst = xs + (size_t)m * K + c * 8;
-            *reinterpret_cast<float4*>(dst) = make_float4(f[0], f[1], f[2], f[3]);
-            *reinterpret_cast<float4*>(dst + 4) = make_float4(f[4], f[5], f[6], f[7]);
+            *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + c * 16) =
+                *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + c * 8);
         }
     }
     __syncthreads();
 
-    for (int g0 = 0; g0 < a.groups_per_cta; g0 += groups_per_round) {
-        const int group = first_group + g0 + my_group_in_round;
-        const bool active = (g0 + my_group_in_round) < a.groups_per_cta && group < total_groups;
-        float acc[R][MT];
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int m = 0; m < MT; ++m) acc[r][m] = 0.f;
+    const uint8_t* xrow0 = xs + (size_t)g * xstride;
+    const uint8_t* xrow1 = xs + (size_t)(g + 8) * xstride;
+    for (int t0 = 0; t0 < a.tiles_per_cta; t0 += tiles_per_round) {
+        const int tile = first_tile + t0 + my_tile_in_round;
+        const bool active = (t0 + my_tile_in_round) < a.tiles_per_cta && tile < total_tiles;
+        // the first result this thread finishes in this round, and what it adds to
+        const int e_ti = tid / (MT * TILE_N), e_rem = tid - e_ti * (MT * TILE_N);
+        const int e_m = e_rem / TILE_N, e_n = (first_tile + t0 + e_ti) * TILE_N + (e_rem - e_m * TILE_N);
+        float e_res = 0.f;
+        if (a.epilogue == EPI_RESIDUAL && e_ti < tiles_per_round && t0 + e_ti < a.tiles_per_cta && e_n < a.N && e_m < a.M)
+            e_res = a.residual[(size_t)e_m * a.N + e_n];
+        float c[4] = {0.f, 0.f, 0.f, 0.f};
         if (active) {
-            const int n0 = group * R;
-            const bf16* wrow[R];
+            const bf16* wrow = a.w + (size_t)min(tile * TILE_N + g, a.N - 1) * K;
+            for (int b0 = b_begin; b0 < b_end; b0 += PRE) {
+                uint4 wv[PRE];
+                if (t0 == 0 && b0 == b_begin) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) wrow[r] = a.w + (size_t)min(n0 + r, a.N - 1) * K;
-            for (int c = c_begin + lane; c < c_end; c += 32) {
-                uint4 wraw[R];
-                if (g0 == 0 && have_first && c == c_begin + lane) {
-#pragma unroll
-                    for (int r = 0; r < R; ++r) wraw[r] = first_w[r];
+                    for (int i = 0; i < PRE; ++i) wv[i] = first_w[i];
                 } else {
 #pragma unroll
-                    for (int r = 0; r < R; ++r) wraw[r] = *reinterpret_cast<const uint4*>(wrow[r] + c * 8);
+                    for (int i = 0; i < PRE; ++i) {
+                        const int k = (b0 + i) * 32 + 8 * t;
+                        wv[i] = (b0 + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow + k) : zero4;
+                    }
                 }
-                float wf[R][8];
 #pragma unroll
-                for (int r = 0; r < R; ++r) unpack8(wraw[r], wf[r]);
-#pragma unroll
-                for (int m = 0; m < MT; ++m) {
-                    const float4 x0 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + c * 8);
-                    const float4 x1 = *reinterpret_cast<const float4*>(xs + (size_t)m * K + c * 8 + 4);
-                    const float xf[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
-#pragma unroll
-                    for (int r = 0; r < R; ++r)
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) acc[r][m] = fmaf(wf[r][i], xf[i], acc[r][m]);
+                for (int i = 0; i < PRE; ++i) {
+                    const int k = (b0 + i) * 32 + 8 * t;
+                    if (b0 + i < b_end) {                                        // uniform in the warp
+                        const bool in = k < K;
+                        const uint4 x0 = in ? *reinterpret_cast<const uint4*>(xrow0 + k * 2) : zero4;
+                        uint4 x1 = zero4;
+                        if (MT == 16 && in) x1 = *reinterpret_cast<const uint4*>(xrow1 + k * 2);
+                        mma_bf16(c, x0.x, x1.x, x0.y, x1.y, wv[i].x, wv[i].y);
+                        mma_bf16(c, x0.z, x1.z, x0.w, x1.w, wv[i].z, wv[i].w);
+                    }
                 }
             }
         }
-        // sum over the lanes through shared memory: lane l writes its R*MT sums as a column,
-        // then lane v adds up row v (33-word rows: no bank conflicts); the order is lane 0..31
+        // c0, c1: token g, rows 2t and 2t+1 of the tile; c2, c3: token g + 8
         {
-            float* mine = red + (size_t)warp * (R * MT) * 33;
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int m = 0; m < MT; ++m) mine[(r * MT + m) * 33 + lane] = acc[r][m];
-            __syncwarp();
-            if (lane < R * MT) {
-                float total = 0.f;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) total += mine[lane * 33 + j];
-                partial[warp * (R * MT) + lane] = total;
-            }
+            float* mine = partial + (size_t)warp * MT * TILE_N;
+            *reinterpret_cast<float2*>(mine + g * TILE_N + 2 * t) = make_float2(c[0], c[1]);
+            if (MT == 16) *reinterpret_cast<float2*>(mine + (g + 8) * TILE_N + 2 * t) = make_float2(c[2], c[3]);
         }
         __syncthreads();
-        // ---- epilogue: one thread per (group of the round, row, token) ----
-        for (int e = tid; e < groups_per_round * R * MT; e += THREADS) {
-            const int gi = e / (R * MT), rm = e - gi * (R * MT);
-            const int r = rm / MT, m = rm - r * MT;
-            const int grp = first_group + g0 + gi;
-            const int n = grp * R + r;
-            if ((g0 + gi) >= a.groups_per_cta || n >= a.N || m >= a.M) continue;
+        // ---- epilogue: one thread per (tile of the round, token, row) ----
+        for (int e = tid; e < tiles_per_round * MT * TILE_N; e += THREADS) {
+            const int ti = e / (MT * TILE_N), rem = e - ti * (MT * TILE_N);
+            const int m = rem / TILE_N, r = rem - m * TILE_N;
+            const int n = (first_tile + t0 + ti) * TILE_N + r;
+            if ((t0 + ti) >= a.tiles_per_cta || n >= a.N || m >= a.M) continue;
             float v = 0.f;
-            for (int s = 0; s < ks; ++s) v += partial[(gi * ks + s) * (R * MT) + rm];   // slices in order
-            if (a.bias) v += a.bias[n];
+            for (int s = 0; s < ks; ++s) v += partial[((size_t)(ti * ks + s) * MT + m) * TILE_N + r];   // slices in order
+            if (a.bias) v += (e == tid && t0 == 0) ? first_bias : a.bias[n];
             if (a.epilogue == EPI_GELU) v = gelu_tanh(v);
             const size_t idx = (size_t)m * a.N + n;
             if (a.epilogue == EPI_RESIDUAL) {
-                a.residual[idx] += v;
+                a.residual[idx] = (e == tid ? e_res : a.residual[idx]) + v;
             } else if (a.out_bf16) {
                 const bf16 hv = __float2bfloat16_rn(v);
                 reinterpret_cast<bf16*>(a.out)[idx] = hv;
@@ -278,10 +269,15 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
 // Largest M this kernel takes.
 MG_API int mg_linear_skinny_max_rows() { return MAX_M; }
 
+// Shared memory the kernel needs for M tokens of width K (the caller checks it against the limit).
+static size_t skinny_smem(int mt, int K) {
+    return (size_t)mt * ((size_t)K * 2 + XPAD) + (size_t)WARPS * mt * TILE_N * sizeof(float);
+}
+
 // x: [M, K] bf16 (or null when x32 is given: then rows row_index[m] (or m) of x32 [*, K] are
 // LayerNorm-ed with gain/shift/eps first).  w: [N, K] bf16.  Epilogues as mg_linear_simt.
 // With k_pages given (QKV projection, bf16 out), features >= q_width also go to the cache rows
-// slots[m].  Returns MG_ERR_UNSUPPORTED for M > 8, K % 8 != 0 or activations beyond shared memory.
+// slots[m].  Returns MG_ERR_UNSUPPORTED for M > 16, K % 8 != 0 or activations beyond shared memory.
 MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_index, const float* gain,
                             const float* shift, float eps, const void* w, const float* bias, void* out,
                             float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
@@ -291,10 +287,11 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
     MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
-    const int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-    const size_t smem = ((size_t)mt * K + (size_t)WARPS * R * mt * 34) * sizeof(float);
-    if (M > MAX_M || K % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w & 15) || (x && ((uintptr_t)x & 15)))
-        return mg_set_error(MG_ERR_UNSUPPORTED, "linear (skinny): needs M <= 8, K %% 8 == 0, aligned operands");
+    const int mt = M <= 8 ? 8 : 16;
+    const size_t smem = skinny_smem(mt, K);
+    if (M > MAX_M || K % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w & 15) || (x && ((uintptr_t)x & 15)) ||
+        (x32 && !x && ((uintptr_t)x32 & 15)) || (gain && ((uintptr_t)gain & 15)) || (shift && ((uintptr_t)shift & 15)))
+        return mg_set_error(MG_ERR_UNSUPPORTED, "linear (skinny): needs M <= 16, K %% 8 == 0, aligned operands");
     MG_REQUIRE(k_pages == nullptr || (out_bf16 && epilogue == EPI_STORE && slots && v_pages && head_dim > 0 &&
                                       n_kv_head > 0 && page_tokens > 0 && N == q_width + 2 * n_kv_head * head_dim),
                "linear: bad key/value sink");
@@ -304,33 +301,28 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
     a.M = M; a.N = N; a.K = K; a.epilogue = epilogue; a.out_bf16 = out_bf16;
     a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages; a.slots = slots;
     a.q_width = q_width; a.n_kv_head = n_kv_head; a.head_dim = head_dim; a.page_tokens = page_tokens;
-    // Cut the work so that a few hundred CTAs exist: groups of R rows, each shared by k_splits warps.
-    const int groups = (N + R - 1) / R;
+    // Cut the work so that every SM gets some and a lane holds all its weights at once: tiles of
+    // 8 rows, each shared by k_splits warps with at least two k blocks (of 32) per warp.
+    const int tiles = (N + TILE_N - 1) / TILE_N;
+    const int kblocks = (K + 31) / 32;
     int ks = 1;
-    while (ks < WARPS && groups * ks < 8 * 296 && (K / 8) / (ks * 2) >= 32) ks *= 2;   // keep >= 32 chunks per slice
+    while (ks < WARPS && kblocks / (ks * 2) >= 2 && (long long)tiles * (ks * 2) / WARPS <= 200) ks *= 2;
     a.k_splits = ks;
     const int per_round = WARPS / ks;
-    int gpc = per_round;                                   // one round per CTA by default
-    while ((groups + gpc - 1) / gpc > 4 * 148) gpc += per_round;
-    a.groups_per_cta = gpc;
-    const int grid = (groups + gpc - 1) / gpc;
+    int tpc = per_round;                                   // one round per CTA by default
+    while ((tiles + tpc - 1) / tpc > 8 * 148) tpc += per_round;
+    a.tiles_per_cta = tpc;
+    const int grid = (tiles + tpc - 1) / tpc;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear (skinny): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    cudaError_t le;
-    switch (mt) {
-        case 1: le = mg_launch(linear_skinny_kernel<1>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
-        case 2: le = mg_launch(linear_skinny_kernel<2>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
-        case 4: le = mg_launch(linear_skinny_kernel<4>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
-        default: le = mg_launch(linear_skinny_kernel<8>, dim3(grid), dim3(THREADS), smem, s, true, a); break;
-    }
+    const cudaError_t le = mt == 8 ? mg_launch(linear_skinny_kernel<8>, dim3(grid), dim3(THREADS), smem, s, true, a)
+                                   : mg_launch(linear_skinny_kernel<16>, dim3(grid), dim3(THREADS), smem, s, true, a);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear_skinny: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("linear_skinny");
     return MG_OK;
