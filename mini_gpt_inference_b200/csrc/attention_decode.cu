@@ -94,11 +94,14 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
 
     const int token = blockIdx.x, head = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // The query and the newest key/value row come from the kernel before this one.
+    // Positions, block tables and every cache row but the newest were written before this step
+    // began; only the query and the newest key/value row come from the kernel in front.  So the
+    // block asks for its old rows right away, while that kernel is still running, and for the
+    // newest row (if it holds it) after the wait.
     pdl_trigger();
-    pdl_wait();
     const int p = positions[token];
     if (p < 0) {                                                        // padding row of a fixed-size batch
+        pdl_wait();                                                     // `out` may still be in use before
         if (split == 0)
             for (int d = tid; d < D; d += THREADS) out[((size_t)token * n_head + head) * D + d] = __float2bfloat16_rn(0.f);
         return;
@@ -118,7 +121,8 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     }
     __syncthreads();
 
-    // ---- ask for all keys and values of the block: one bulk copy per page and tensor ----
+    // ---- ask for the keys and values of the block: one bulk copy per page and tensor ----
+    const bool holds_newest = start + count - 1 == p;
     if (warp == 0) {
         const uint32_t bytes = (uint32_t)count * D * 2;
         if (lane == 0) {
@@ -126,18 +130,28 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
             asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bars[1])), "r"(bytes) : "memory");
         }
         __syncwarp();
-        const int first_page = start / page_tokens, last_page = (start + count - 1) / page_tokens;
-        for (int which = 0; which < 2; ++which) {                       // all key copies first
-            const bf16* pages = which == 0 ? k_pages : v_pages;
-            bf16* tile = which == 0 ? k_tile : v_tile;
-            for (int pi = first_page + lane; pi <= last_page; pi += 32) {
-                const int page = table[pi];
-                const int r0 = max(start, pi * page_tokens), r1 = min(start + count, (pi + 1) * page_tokens);
-                const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (r0 - pi * page_tokens);
-                bulk_copy(smem_u32(tile + (size_t)(r0 - start) * D), pages + row * D, (uint32_t)(r1 - r0) * D * 2,
-                          smem_u32(&bars[which]));
+        const int old_end = holds_newest ? p : start + count;           // rows [start, old_end) are old
+        if (old_end > start) {
+            const int first_page = start / page_tokens, last_page = (old_end - 1) / page_tokens;
+            for (int which = 0; which < 2; ++which) {                   // all key copies first
+                const bf16* pages = which == 0 ? k_pages : v_pages;
+                bf16* tile = which == 0 ? k_tile : v_tile;
+                for (int pi = first_page + lane; pi <= last_page; pi += 32) {
+                    const int page = table[pi];
+                    const int r0 = max(start, pi * page_tokens), r1 = min(old_end, (pi + 1) * page_tokens);
+                    const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (r0 - pi * page_tokens);
+                    bulk_copy(smem_u32(tile + (size_t)(r0 - start) * D), pages + row * D, (uint32_t)(r1 - r0) * D * 2,
+                              smem_u32(&bars[which]));
+                }
             }
         }
+    }
+    pdl_wait();
+    if (holds_newest && tid < 2) {                                      // the row the kernel in front wrote
+        const int pi = p / page_tokens;
+        const size_t row = ((size_t)table[pi] * n_kv_head + kv_head) * page_tokens + (p - pi * page_tokens);
+        bulk_copy(smem_u32((tid == 0 ? k_tile : v_tile) + (size_t)(p - start) * D), (tid == 0 ? k_pages : v_pages) + row * D,
+                  (uint32_t)D * 2, smem_u32(&bars[tid]));
     }
 
     const int sub = lane % LPK, grp = lane / LPK;

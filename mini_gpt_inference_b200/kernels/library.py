@@ -34,8 +34,6 @@ _SIGNATURES = {
                                  _F, _P, _P],
     "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                 ctypes.c_longlong, _I, _I, _F, _P, _P],
-    "mg_block_tail": [_P, _P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P],
-    "mg_block_tail_max_rows": [],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],

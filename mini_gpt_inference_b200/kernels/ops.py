@@ -67,10 +67,7 @@ class CudaOps:
         self.use_skinny = True
         self.use_dependent_launch = True
         self.use_prefill_tc = True
-        self.use_block_tail = False
         self._counter_buf = None
-        self._tail_sync = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self._tail_rows = int(self.lib.mg_block_tail_max_rows())
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -118,7 +115,6 @@ class CudaOps:
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
-            self._tail_sync.zero_()        # a barrier that gave up leaves its counters behind
             raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
 
     # ---- embedding and norms --------------------------------------------------------------------
@@ -247,45 +243,6 @@ class CudaOps:
         if residual32.shape != (x.shape[0], weight.shape[0]):
             raise KernelLibraryError("linear_residual: residual has the wrong shape")
         self._linear(x, weight, bias, EPILOGUES["residual"], None, residual32)
-
-    def block_tail(self, attn, out_weight, out_bias, residual32, gain, shift, eps,
-                   fc_weight, fc_bias, activation, proj_weight, proj_bias) -> bool:
-        """For a handful of tokens, what is left of a pre-norm block after attention as one
-        resident kernel: ``x += attn.Wo^T + bo; x += act(LayerNorm(x).Wfc^T + bfc).Wproj^T + bproj``
-        on ``residual32`` in place.  Returns False, having launched nothing, when the case is not
-        one it takes (more tokens, 32-bit weights, another activation, sizes that do not fit); the
-        caller then runs the three projections one by one."""
-        m = attn.shape[0]
-        if (not self.use_block_tail or m == 0 or m > self._tail_rows or activation != "gelu_tanh"
-                or attn.dtype != torch.bfloat16
-                or any(w.dtype != torch.bfloat16 for w in (out_weight, fc_weight, proj_weight))):
-            return False
-        self._want(attn, torch.bfloat16, "block tail input", 2)
-        self._want(residual32, torch.float32, "residual", 2)
-        for name, w in (("out", out_weight), ("fc", fc_weight), ("proj", proj_weight)):
-            self._want(w, torch.bfloat16, f"block tail {name} weight", 2)
-        for name, v in (("out bias", out_bias), ("fc bias", fc_bias), ("proj bias", proj_bias),
-                        ("gain", gain), ("shift", shift)):
-            if v is not None:
-                self._want(v, torch.float32, f"block tail {name}", 1)
-        width, k1, inner = out_weight.shape[0], out_weight.shape[1], fc_weight.shape[0]
-        if (attn.shape[1] != k1 or residual32.shape != (m, width) or fc_weight.shape[1] != width
-                or proj_weight.shape != (width, inner) or gain.numel() != width
-                or (shift is not None and shift.numel() != width)
-                or (out_bias is not None and out_bias.numel() != width)
-                or (fc_bias is not None and fc_bias.numel() != inner)
-                or (proj_bias is not None and proj_bias.numel() != width)):
-            raise KernelLibraryError("block tail: shapes do not fit")
-        hidden = torch.empty((m, inner), dtype=torch.bfloat16, device=self.device)
-        code = self.lib.mg_block_tail(_ptr(attn), _ptr(residual32), _ptr(out_weight), _ptr(out_bias),
-                                      _ptr(gain), _ptr(shift), float(eps), _ptr(fc_weight),
-                                      _ptr(fc_bias), _ptr(proj_weight), _ptr(proj_bias), _ptr(hidden),
-                                      m, width, k1, inner, _ptr(self._tail_sync), _ptr(self.status),
-                                      self._stream())
-        if code == library.UNSUPPORTED:
-            return False
-        self._run(code, "block tail")
-        return True
 
     def logits(self, y, tok_emb):
         return self.linear(y, tok_emb, None, "none", torch.float32)

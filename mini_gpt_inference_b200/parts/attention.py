@@ -69,13 +69,6 @@ class CausalAttention(Mixer):
                 and type(self.position).rotate is not PositionEncoding.rotate)
 
     def forward(self, ctx, cache, y, residual32) -> None:
-        out, weight, bias = self.attend(ctx, cache, y)
-        ctx.ops.linear_residual(out, weight, bias, residual32)
-
-    def attend(self, ctx, cache, y):
-        """Everything but the output projection.  Returns ``(out, weight, bias)``: what is left
-        to do is ``residual += out . weight^T + bias``, which an arrangement may fuse with what
-        follows."""
         ops = ctx.ops
         slots = ctx.slot_mapping[cache.group]
         if not self._position_rotates() and hasattr(ops, "linear_qkv"):
@@ -90,4 +83,4 @@ class CausalAttention(Mixer):
                 ops.kv_store(qkv, self.n_head, self.n_kv_head, self.head_dim, cache, slots)
         out = ops.paged_attention(qkv, self.n_head, self.n_kv_head, self.head_dim, self.scale,
                                   cache, ctx)
-        return out, self.proj_weight, self.proj_bias
+        ops.linear_residual(out, self.proj_weight, self.proj_bias, residual32)

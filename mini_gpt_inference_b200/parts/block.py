@@ -26,17 +26,7 @@ def pre_norm(ctx, layer: Layer, cache, residual32) -> None:
     mixer, ff = layer.mixer, layer.feed_forward
     y = (layer.norm1.defer if getattr(mixer, "accepts_deferred_norm", False)
          else layer.norm1.forward)(ctx, residual32)
-    fused = getattr(ctx.ops, "block_tail", None)
-    if (fused is not None and hasattr(mixer, "attend") and hasattr(ff, "dense_form")
-            and hasattr(layer.norm2, "affine_form")):
-        # The mixer stops before its output projection; for a handful of tokens that projection,
-        # the second norm and the feed-forward run as one kernel.
-        out, weight, bias = mixer.attend(ctx, cache, y)
-        if fused(out, weight, bias, residual32, *layer.norm2.affine_form(), *ff.dense_form()):
-            return
-        ctx.ops.linear_residual(out, weight, bias, residual32)
-    else:
-        mixer.forward(ctx, cache, y, residual32)
+    mixer.forward(ctx, cache, y, residual32)
     y = (layer.norm2.defer if getattr(ff, "accepts_deferred_norm", False)
          else layer.norm2.forward)(ctx, residual32)
     ff.forward(ctx, y, residual32)

@@ -34,7 +34,3 @@ class LayerNorm(Norm):
         if not hasattr(ctx.ops, "defer_layernorm"):
             return super().defer(ctx, x32, rows)
         return ctx.ops.defer_layernorm(x32, self.weight, self.bias, self.eps, ctx.act_dtype, rows)
-
-    def affine_form(self):
-        """``(gain, shift, eps)`` for an arrangement that fuses this norm into a larger kernel."""
-        return self.weight, self.bias, self.eps

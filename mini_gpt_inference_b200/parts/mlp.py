@@ -43,8 +43,3 @@ class DenseMLP(FeedForward):
     def forward(self, ctx, y, residual32) -> None:
         h = ctx.ops.linear(y, self.fc_weight, self.fc_bias, self.activation, ctx.act_dtype)
         ctx.ops.linear_residual(h, self.proj_weight, self.proj_bias, residual32)
-
-    def dense_form(self):
-        """``(fc weight, fc bias, activation, proj weight, proj bias)`` for an arrangement that
-        fuses this feed-forward with what precedes it."""
-        return self.fc_weight, self.fc_bias, self.activation, self.proj_weight, self.proj_bias

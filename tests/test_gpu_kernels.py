@@ -134,51 +134,6 @@ def test_small_batch_projection_with_fused_norm(ops, m, n, k):
     ops.check_status()
 
 
-@pytest.mark.parametrize("m", [1, 2, 3, 5, 8])
-@pytest.mark.parametrize("width,k1,inner,bias", [(512, 512, 2048, True), (72, 48, 200, True),
-                                                 (1000, 960, 1112, False), (64, 64, 64, True)])
-def test_block_tail_in_one_kernel(ops, m, width, k1, inner, bias):
-    """Output projection, second norm and feed-forward of a block as one resident kernel: it
-    must agree with the formula and, to summation order, with the three separate kernels; and
-    it must leave its barrier counters ready for the next call (two calls in a row)."""
-    attn = randn(m, k1, dtype=torch.bfloat16, seed=41)
-    x = randn(m, width, seed=42, scale=2.0) + 0.3
-    w_o = randn(width, k1, dtype=torch.bfloat16, seed=43, scale=1 / math.sqrt(k1))
-    w_fc = randn(inner, width, dtype=torch.bfloat16, seed=44, scale=1 / math.sqrt(width))
-    w_pr = randn(width, inner, dtype=torch.bfloat16, seed=45, scale=1 / math.sqrt(inner))
-    b_o, b_fc, b_pr = (randn(n, seed=46 + i) if bias else None for i, n in enumerate((width, inner, width)))
-    gain, shift = randn(width, seed=49) + 1.0, (randn(width, seed=50) if bias else None)
-    eps = 3e-4
-
-    def dbl(t):
-        return 0.0 if t is None else t.double()
-
-    x1 = x.double() + attn.double() @ w_o.double().T + dbl(b_o)
-    y = F.layer_norm(x1, (width,), gain.double(), None if shift is None else shift.double(), eps)
-    h = plain_gpt.gelu_tanh(y @ w_fc.double().T + dbl(b_fc))
-    want = x1 + h @ w_pr.double().T + dbl(b_pr)
-
-    apart = x.clone()
-    ops.linear_residual(attn, w_o, b_o, apart)
-    hidden = ops.linear(ops.layernorm(apart, gain, shift, eps, torch.bfloat16), w_fc, b_fc, "gelu_tanh",
-                        torch.bfloat16)
-    ops.linear_residual(hidden, w_pr, b_pr, apart)
-
-    for _ in range(2):
-        got = x.clone()
-        before = ops.launches
-        assert ops.block_tail(attn, w_o, b_o, got, gain, shift, eps, w_fc, b_fc, "gelu_tanh", w_pr, b_pr)
-        assert ops.launches == before + 1
-        ops.check_status()
-        assert (got.double() - want).abs().max() <= 4e-2          # bf16 rounding of y and h
-        assert (got - apart).abs().max() <= 2e-2                   # a bf16 value may round the other way
-        assert (got - apart).abs().mean() <= 2e-4
-    # what it does not take is said, not computed wrongly
-    assert not ops.block_tail(randn(9, k1, dtype=torch.bfloat16), w_o, b_o, randn(9, width), gain, shift, eps,
-                              w_fc, b_fc, "gelu_tanh", w_pr, b_pr)
-    assert not ops.block_tail(attn, w_o, b_o, x.clone(), gain, shift, eps, w_fc, b_fc, "relu", w_pr, b_pr)
-
-
 @pytest.mark.parametrize("m", [1, 4, 8, 9, 40])
 def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m):
     n_head, n_kv, d, pt, pages, k = 6, 2, 32, 8, 12, 96
