@@ -1,29 +1,34 @@
 // Attention of single query tokens over the paged cache, split along the keys (bfloat16 cache).
 //
 // A decoding step reads every key and value of every live request once: it is bound by HBM
-// bandwidth, and a request alone gives too little parallelism (one head is one row of work).
-// So the keys of a (token, head) are cut into blocks of SPLIT positions, one CTA each.
+// bandwidth, and a request alone gives too little parallelism.  So the keys of a (token, kv head)
+// are cut into blocks of SPLIT positions, one CTA each; the query heads that share the kv head
+// (up to 16 per CTA) are the rows of one small matrix product, so grouped heads read their keys
+// once.
 //
-// A CTA first asks for everything it will read: one warp issues a bulk asynchronous copy
-// (cp.async.bulk, global -> shared, completion counted on an mbarrier) per cache page and
-// per tensor, keys on one barrier and values on another, so that tens of kilobytes are in
-// flight per CTA without holding registers, and the score pass starts as soon as the keys have
-// landed while the values are still arriving.  Then, from shared memory:
+// A CTA's four warps each own a quarter of the block's keys from load to result:
 //
-//   pass 1  scores: a key row is read by head_dim / 8 neighbouring lanes, 16 bytes each, and the
-//           dot product is finished with shuffles; the query is pre-scaled by scale * log2 e;
-//   pass 2  the block's maximum, the base-2 exponentials and their sum, all in 32-bit;
-//   pass 3  sum of p * v over the value rows, in 32-bit.
+//   load    every lane copies 16-byte pieces of its warp's key and value rows from their pages
+//           into shared memory (cp.async), swizzled so that the matrix loads below meet no bank
+//           conflict.  Positions, block tables and every cache row but the newest were written
+//           before this step began, so all of this is asked for BEFORE the wait for the kernel in
+//           front (which wrote the query and the newest row); the newest row follows after it.
+//   scores  S = Q K^T on warp-level mma (m16n8k16: the heads are the 16 rows of A, eight keys the
+//           columns of B, read with ldmatrix), scaled by scale * log2 e in 32-bit;
+//   softmax maximum, base-2 exponentials and their sum over the warp's keys, in 32-bit, inside the
+//           accumulator registers (a row lives in four lanes);
+//   values  O = P V, P rounded to bfloat16 straight from the score registers (the accumulator
+//           layout of S is the A layout of the next product), V through ldmatrix.trans.
 //
-// Each CTA writes its unnormalised output, maximum and sum to scratch memory and bumps a counter
-// of its (token, head); the CTA that arrives last merges the blocks, writes the output row and
-// resets the counter (so the counters stay zero between launches).  Block edges are absolute
-// positions (multiples of SPLIT from the first visible key), so what a token computes does not
-// depend on the batch it is in.
+// The four warps' (maximum, sum, O) are combined through shared memory into the block's partial
+// result, written to scratch; the CTA that arrives last at a counter of its (token, kv head)
+// merges the blocks, writes the output rows and resets the counter (so the counters stay zero
+// between launches).  Block edges are absolute positions (multiples of SPLIT from the first
+// visible key), so what a token computes does not depend on the batch it is in.
 //
-// Sizes: head_dim in {16, 32, 64, 128, 256} (SPLIT = 256, 256, 128, 64, 32: at most 16 KB per tile);
-// any number of heads and kv heads; any page size.  The wait for the copies is bounded: if it
-// runs out the kernel records a code in `status` and writes nothing.
+// Sizes: head_dim in {16, 32, 64, 128, 256}; any number of heads and kv heads; any page size.
+// Nothing here waits on another CTA, so no wait needs a bound; `status` is unused but kept in the
+// interface.
 #include <math.h>
 
 #include "common.cuh"
@@ -32,46 +37,45 @@ namespace {
 
 constexpr int THREADS = 128;
 constexpr int WARPS = THREADS / 32;
-constexpr uint32_t SPIN_LIMIT = 4000000u;
+constexpr int HEAD_ROWS = 16;              // query heads per CTA (rows of the A operand)
 
-// Keys per block: 16 KB per tile, so that seven CTAs share an SM and a whole decode batch of a
-// few thousand blocks is in flight at once.
-__host__ __device__ constexpr int split_keys(int head_dim) { return head_dim <= 32 ? 256 : (8192 / head_dim); }
-
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const float2 v = __bfloat1622float2(h[i]);
-        f[2 * i] = v.x;
-        f[2 * i + 1] = v.y;
-    }
+// Keys per block: 16 KB per tile (32 KB at head_dim 256), so that several CTAs share an SM and a
+// whole decode batch of a few thousand blocks is in flight at once; at least 16 keys per warp.
+__host__ __device__ constexpr int split_keys(int head_dim) {
+    return head_dim <= 32 ? 256 : (8192 / head_dim < 64 ? 64 : 8192 / head_dim);
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
-__device__ __forceinline__ void bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
 }
 
-// partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][head]
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
 template <int D>
 __global__ void __launch_bounds__(THREADS)
 attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_pages,
@@ -79,31 +83,39 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
                        const int* __restrict__ token_request, const int* __restrict__ positions,
                        bf16* __restrict__ out, float* __restrict__ part_out, float* __restrict__ part_ml,
                        int* __restrict__ counters, int n_head, int n_kv_head, int page_tokens, int max_pages,
-                       int window, int max_splits, float scale_log2e, int* __restrict__ status) {
+                       int window, int max_splits, float scale_log2e, int head_tiles) {
     constexpr int SPLIT = split_keys(D);
-    constexpr int LPK = D / 8;                 // lanes per key row (16 bytes each)
-    constexpr int KPW = 32 / LPK;              // keys per warp per round
-    extern __shared__ __align__(128) uint8_t tiles[];
-    bf16* k_tile = reinterpret_cast<bf16*>(tiles);                       // [SPLIT][D]
-    bf16* v_tile = k_tile + SPLIT * D;
-    __shared__ float scores[SPLIT];
-    __shared__ float red[WARPS];
-    __shared__ float acc_smem[WARPS][D];
-    __shared__ __align__(8) uint64_t bars[2];
+    constexpr int KW = SPLIT / WARPS;          // keys per warp
+    constexpr int CPR = D / 8;                 // 16-byte pieces per row
+    constexpr int ROWB = 2 * D;                // bytes per row
+    constexpr int RPL = CPR >= 8 ? 1 : 8 / CPR;        // rows per 128 bytes of shared memory
+    constexpr int SWZ = CPR >= 8 ? 8 : CPR;            // piece c of row r lies at piece c ^ ((r / RPL) % SWZ)
+    constexpr int OSTRIDE = D + 2;             // floats per (warp, head) partial: O, maximum, sum
+    constexpr int QSTRIDE = D + 8;             // query rows 16 bytes apart in the banks
+    static_assert(KW % 16 == 0, "a warp takes whole k steps of keys");
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* k_tile = smem;                                            // [SPLIT][D] bf16, swizzled
+    uint8_t* v_tile = smem + SPLIT * ROWB;
+    int* grow = reinterpret_cast<int*>(v_tile + SPLIT * ROWB);         // [SPLIT] cache row of each key
+    bf16* q_tiles = reinterpret_cast<bf16*>(grow + SPLIT);             // [WARPS][rows][QSTRIDE]: a copy per warp
     __shared__ int is_last;
 
-    const int token = blockIdx.x, head = blockIdx.y, split = blockIdx.z;
+    const int token = blockIdx.x, split = blockIdx.z;
+    const int kv_head = blockIdx.y / head_tiles, ht = blockIdx.y - kv_head * head_tiles;
+    const int group = n_head / n_kv_head;
+    const int h0 = kv_head * group + ht * HEAD_ROWS;                   // first query head of this CTA
+    const int nh = min(HEAD_ROWS, group - ht * HEAD_ROWS);
+    const int nh_rows = min(HEAD_ROWS, group);                         // rows the launch reserved
+    float* wpart = reinterpret_cast<float*>(q_tiles + WARPS * nh_rows * QSTRIDE);   // [WARPS][nh][OSTRIDE]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Positions, block tables and every cache row but the newest were written before this step
-    // began; only the query and the newest key/value row come from the kernel in front.  So the
-    // block asks for its old rows right away, while that kernel is still running, and for the
-    // newest row (if it holds it) after the wait.
+    const int g = lane >> 2, t = lane & 3;
     pdl_trigger();
     const int p = positions[token];
     if (p < 0) {                                                        // padding row of a fixed-size batch
         pdl_wait();                                                     // `out` may still be in use before
         if (split == 0)
-            for (int d = tid; d < D; d += THREADS) out[((size_t)token * n_head + head) * D + d] = __float2bfloat16_rn(0.f);
+            for (int i = tid; i < nh * D; i += THREADS)
+                out[((size_t)token * n_head + h0 + i / D) * D + i % D] = __float2bfloat16_rn(0.f);
         return;
     }
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
@@ -111,216 +123,235 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     if (start > p) return;                                              // this block holds no key of the token
     const int count = min(SPLIT, p + 1 - start);
     const int splits = (p - lo) / SPLIT + 1;
-    const int kv_head = head / (n_head / n_kv_head);
     const int* table = block_table + (size_t)token_request[token] * max_pages;
-
-    if (tid == 0) {
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[0])) : "memory");
-        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[1])) : "memory");
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    // ---- ask for the keys and values of the block: one bulk copy per page and tensor ----
     const bool holds_newest = start + count - 1 == p;
-    if (warp == 0) {
-        const uint32_t bytes = (uint32_t)count * D * 2;
-        if (lane == 0) {
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bars[0])), "r"(bytes) : "memory");
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&bars[1])), "r"(bytes) : "memory");
+    const int old_count = holds_newest ? count - 1 : count;            // rows [0, old_count) are old
+
+    // ---- where each key of this warp lies in the cache (a warp needs no other warp's rows) ----
+    for (int i = lane; i < KW; i += 32) {
+        const int r = warp * KW + i;
+        if (r < count) {
+            const int pos = start + r, pi = pos / page_tokens;
+            grow[r] = (table[pi] * n_kv_head + kv_head) * page_tokens + (pos - pi * page_tokens);
         }
-        __syncwarp();
-        const int old_end = holds_newest ? p : start + count;           // rows [start, old_end) are old
-        if (old_end > start) {
-            const int first_page = start / page_tokens, last_page = (old_end - 1) / page_tokens;
-            for (int which = 0; which < 2; ++which) {                   // all key copies first
-                const bf16* pages = which == 0 ? k_pages : v_pages;
-                bf16* tile = which == 0 ? k_tile : v_tile;
-                for (int pi = first_page + lane; pi <= last_page; pi += 32) {
-                    const int page = table[pi];
-                    const int r0 = max(start, pi * page_tokens), r1 = min(old_end, (pi + 1) * page_tokens);
-                    const size_t row = ((size_t)page * n_kv_head + kv_head) * page_tokens + (r0 - pi * page_tokens);
-                    bulk_copy(smem_u32(tile + (size_t)(r0 - start) * D), pages + row * D, (uint32_t)(r1 - r0) * D * 2,
-                              smem_u32(&bars[which]));
-                }
+    }
+    __syncwarp();
+    // ---- every warp asks for its own rows: all keys first, then all values ----
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+        const bf16* pages = which == 0 ? k_pages : v_pages;
+        uint8_t* tile = which == 0 ? k_tile : v_tile;
+#pragma unroll 4
+        for (int i = lane; i < KW * CPR; i += 32) {
+            const int r = warp * KW + i / CPR, c = i % CPR;
+            uint8_t* dst = tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16);
+            if (r < old_count) cp_async16(smem_u32(dst), pages + (size_t)grow[r] * D + c * 8);
+            else if (r >= count) *reinterpret_cast<uint4*>(dst) = zero4;            // keeps 0 * garbage out of O
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    pdl_wait();
+    // ---- what the kernel in front wrote: the newest row (to the warp that owns it) and the
+    // queries (a copy for every warp, so that no warp waits for another before the end) ----
+    if (holds_newest && warp == (count - 1) / KW) {
+        for (int i = lane; i < 2 * CPR; i += 32) {
+            const int which = i / CPR, c = i - which * CPR, r = count - 1;
+            const uint4 v = *reinterpret_cast<const uint4*>((which == 0 ? k_pages : v_pages) + (size_t)grow[r] * D + c * 8);
+            *reinterpret_cast<uint4*>((which == 0 ? k_tile : v_tile) + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)) = v;
+        }
+    }
+    bf16* q_tile = q_tiles + warp * (nh_rows * QSTRIDE);
+    {
+        const size_t qkv_width = (size_t)(n_head + 2 * n_kv_head) * D;
+        for (int i = lane; i < nh * CPR; i += 32) {
+            const int row = i / CPR, c = i - row * CPR;
+            *reinterpret_cast<uint4*>(q_tile + row * QSTRIDE + c * 8) =
+                *reinterpret_cast<const uint4*>(qkv + (size_t)token * qkv_width + (size_t)(h0 + row) * D + c * 8);
+        }
+    }
+    asm volatile("cp.async.wait_group 1;" ::: "memory");               // this lane's keys have landed
+    __syncwarp();                                                       // the warp's keys, its newest row, its queries
+
+    // ---- scores: S[head, key] = q . k over this warp's KW keys ----
+    float s[KW / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < KW / 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
+    {
+        // lane address pattern of ldmatrix.x4: matrix j = lane / 8 holds keys (j / 2) * 8 .., pieces j % 2
+        const int lrow = (lane & 7) + ((lane >> 4) << 3), lpiece = (lane >> 3) & 1;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            uint32_t a[4] = {0u, 0u, 0u, 0u};                           // heads past the group are zero rows
+            if (g < nh) {
+                a[0] = *reinterpret_cast<const uint32_t*>(q_tile + g * QSTRIDE + ks * 16 + 2 * t);
+                a[2] = *reinterpret_cast<const uint32_t*>(q_tile + g * QSTRIDE + ks * 16 + 8 + 2 * t);
+            }
+            if (g + 8 < nh) {
+                a[1] = *reinterpret_cast<const uint32_t*>(q_tile + (g + 8) * QSTRIDE + ks * 16 + 2 * t);
+                a[3] = *reinterpret_cast<const uint32_t*>(q_tile + (g + 8) * QSTRIDE + ks * 16 + 8 + 2 * t);
+            }
+#pragma unroll
+            for (int np = 0; np < KW / 16; ++np) {
+                const int r = warp * KW + np * 16 + lrow, c = ks * 2 + lpiece;
+                uint32_t b[4];
+                ldmatrix_x4(b, smem_u32(k_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
+                mma_bf16(s[2 * np], a, b[0], b[1]);
+                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
             }
         }
     }
-    pdl_wait();
-    if (holds_newest && tid < 2) {                                      // the row the kernel in front wrote
-        const int pi = p / page_tokens;
-        const size_t row = ((size_t)table[pi] * n_kv_head + kv_head) * page_tokens + (p - pi * page_tokens);
-        bulk_copy(smem_u32((tid == 0 ? k_tile : v_tile) + (size_t)(p - start) * D), (tid == 0 ? k_pages : v_pages) + row * D,
-                  (uint32_t)D * 2, smem_u32(&bars[tid]));
+    // ---- softmax over the warp's keys; rows g (values 0, 1) and g + 8 (values 2, 3) ----
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int nt = 0; nt < KW / 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp * KW + nt * 8 + 2 * t + (i & 1);
+            s[nt][i] = r < count ? s[nt][i] * scale_log2e : -INFINITY;
+            mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
+        }
+    float sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+    }
+    uint32_t pa[KW / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < KW / 8; ++nt) {
+        float e[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float m = mx[i >> 1];
+            e[i] = m == -INFINITY ? 0.f : exp2f(s[nt][i] - m);         // a warp past the last key holds nothing
+            sum[i >> 1] += e[i];
+        }
+        // the accumulator layout of S is the A layout of P: n-tile 2k gives a0/a1, n-tile 2k+1 a2/a3
+        pa[nt >> 1][(nt & 1) * 2] = pack_bf16(e[0], e[1]);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e[2], e[3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
+        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
     }
 
-    const int sub = lane % LPK, grp = lane / LPK;
-    // this lane's 8 dims of the query, scaled
-    float q[8];
+    // ---- values: O[head, dim] = sum of p * v, once this warp's value rows have landed ----
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    float o[D / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
     {
-        const int qkv_width = (n_head + 2 * n_kv_head) * D;
-        const uint4 raw = *reinterpret_cast<const uint4*>(qkv + (size_t)token * qkv_width + (size_t)head * D + sub * 8);
-        unpack8(raw, q);
+        // ldmatrix.x4.trans: matrix j holds keys (j % 2) * 8 .., piece j / 2 of the pair of n-tiles
+        const int lrow = (lane & 7) + (((lane >> 3) & 1) << 3), lpiece = lane >> 4;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) q[i] *= scale_log2e;
-    }
-
-    // ---- pass 1: scores, once the keys have landed ----
-    bool ok = mbar_wait(smem_u32(&bars[0]), 0);
-    for (int base = warp * KPW; base < count; base += WARPS * KPW) {
-        const int j = base + grp;
-        float dot = 0.f;
-        if (j < count) {
-            float kf[8];
-            unpack8(*reinterpret_cast<const uint4*>(k_tile + (size_t)j * D + sub * 8), kf);
+        for (int kk = 0; kk < KW / 16; ++kk) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) dot = fmaf(q[i], kf[i], dot);
-        }
-#pragma unroll
-        for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        if (sub == 0 && j < count) scores[j] = dot;
-    }
-    __syncthreads();
-
-    // ---- pass 2: maximum, exponentials, sum ----
-    float m = -INFINITY;
-    for (int j = tid; j < count; j += THREADS) m = fmaxf(m, scores[j]);
-    m = warp_max(m);
-    if (lane == 0) red[warp] = m;
-    __syncthreads();
-    m = red[0];
-#pragma unroll
-    for (int w = 1; w < WARPS; ++w) m = fmaxf(m, red[w]);
-    __syncthreads();
-    float l = 0.f;
-    for (int j = tid; j < count; j += THREADS) {
-        const float e = exp2f(scores[j] - m);
-        scores[j] = e;
-        l += e;
-    }
-    l = warp_sum(l);
-    if (lane == 0) red[warp] = l;
-    __syncthreads();
-    l = red[0];
-#pragma unroll
-    for (int w = 1; w < WARPS; ++w) l += red[w];
-
-    // ---- pass 3: sum of p * v, once the values have landed ----
-    ok = mbar_wait(smem_u32(&bars[1]), 0) && ok;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    for (int base = warp * KPW; base < count; base += WARPS * KPW) {
-        const int j = base + grp;
-        if (j < count) {
-            float vf[8];
-            unpack8(*reinterpret_cast<const uint4*>(v_tile + (size_t)j * D + sub * 8), vf);
-            const float pj = scores[j];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = fmaf(pj, vf[i], acc[i]);
+            for (int dp = 0; dp < D / 16; ++dp) {
+                const int r = warp * KW + kk * 16 + lrow, c = dp * 2 + lpiece;
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, smem_u32(v_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
+                mma_bf16(o[2 * dp], pa[kk], b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], pa[kk], b[2], b[3]);
+            }
         }
     }
-    // lanes with the same `sub` hold the same dims: add them up inside the warp, then across warps
+    // ---- the four warps' results meet in shared memory ----
 #pragma unroll
-    for (int o = LPK; o < 32; o <<= 1) {
+    for (int h = 0; h < 2; ++h) {
+        const int row = g + 8 * h;
+        if (row < nh) {
+            float* dst = wpart + ((size_t)warp * nh + row) * OSTRIDE;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
-    }
-    if (grp == 0) {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc_smem[warp][sub * 8 + i] = acc[i];
-    }
-    ok = __syncthreads_and(ok);
-    if (!ok) {
-        // the copies never arrived: report, give them a moment, leave without writing anything
-        if (tid == 0) {
-            atomicExch(status, 11);
-            for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+            for (int nt = 0; nt < D / 8; ++nt)
+                *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
+            if (t == 0) {
+                dst[D] = mx[h];
+                dst[D + 1] = sum[h];
+            }
         }
-        __syncthreads();
-        return;
     }
-    const size_t pair = (size_t)token * n_head + head;
-    const size_t slot = pair * max_splits + split;
-    if (splits == 1) {                                                  // nothing to merge
-        const float inv = 1.0f / l;
-        for (int d = tid; d < D; d += THREADS) {
-            float v = acc_smem[0][d];
+    __syncthreads();
+    const size_t pair0 = (size_t)token * n_head + h0;
+    for (int e = tid; e < nh * D; e += THREADS) {
+        const int row = e / D, d = e - row * D;
+        float m = -INFINITY;
 #pragma unroll
-            for (int w = 1; w < WARPS; ++w) v += acc_smem[w][d];
-            out[pair * D + d] = __float2bfloat16_rn(v * inv);
+        for (int w = 0; w < WARPS; ++w) m = fmaxf(m, wpart[((size_t)w * nh + row) * OSTRIDE + D]);
+        float v = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {                               // warps in order
+            const float* src = wpart + ((size_t)w * nh + row) * OSTRIDE;
+            const float f = src[D] == -INFINITY ? 0.f : exp2f(src[D] - m);
+            v = fmaf(f, src[d], v);
+            l = fmaf(f, src[D + 1], l);
         }
-        return;
+        if (splits == 1) {                                              // nothing to merge
+            out[(pair0 + row) * D + d] = __float2bfloat16_rn(v / l);
+        } else {
+            const size_t slot = (pair0 + row) * max_splits + split;
+            part_out[slot * D + d] = v;
+            if (d == 0) {
+                part_ml[slot * 2] = m;
+                part_ml[slot * 2 + 1] = l;
+            }
+        }
     }
-    for (int d = tid; d < D; d += THREADS) {
-        float v = acc_smem[0][d];
-#pragma unroll
-        for (int w = 1; w < WARPS; ++w) v += acc_smem[w][d];
-        part_out[slot * D + d] = v;
-    }
-    if (tid == 0) {
-        part_ml[slot * 2] = m;
-        part_ml[slot * 2 + 1] = l;
-    }
-    // ---- the CTA that finishes last merges the blocks of this (token, head) ----
+    if (splits == 1) return;
+    // ---- the CTA that finishes last merges the blocks of this (token, kv head) ----
     // The barrier orders every thread's partial writes before thread 0's release on the counter;
     // the CTA that reads the final count acquires, so it sees the partial rows of all blocks.
     __syncthreads();
+    int* counter = counters + (size_t)token * (n_kv_head * head_tiles) + blockIdx.y;
     if (tid == 0) {
         int done;
-        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(done) : "l"(counters + pair) : "memory");
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(done) : "l"(counter) : "memory");
         is_last = (done == splits - 1);
-        if (is_last) counters[pair] = 0;                                // ready for the next launch
+        if (is_last) *counter = 0;                                      // ready for the next launch
     }
     __syncthreads();
     if (!is_last) return;
-    // Merge with all loads in flight at once: one thread per block fetches its maximum and sum,
-    // then each thread adds up its share of the partial rows, eight loads at a time.
-    const size_t base = pair * max_splits;
-    float* ml = scores;                                                 // reuse: [splits] weights
-    float M = -INFINITY;
-    for (int s0 = 0; s0 < splits; s0 += THREADS) {
-        const int s = s0 + tid;
-        if (s < splits) M = fmaxf(M, __ldcg(&part_ml[(base + s) * 2]));
-    }
-    M = warp_max(M);
-    if (lane == 0) red[warp] = M;
-    __syncthreads();
-    M = red[0];
-#pragma unroll
-    for (int w = 1; w < WARPS; ++w) M = fmaxf(M, red[w]);
-    __syncthreads();
-    float denom = 0.f;
-    for (int s0 = 0; s0 < splits; s0 += THREADS) {
-        const int s = s0 + tid;
-        if (s < splits) {
-            const float w = exp2f(__ldcg(&part_ml[(base + s) * 2]) - M);
-            if (s < SPLIT) ml[s] = w;
-            denom += w * __ldcg(&part_ml[(base + s) * 2 + 1]);
+    // A warp per head: weights of the blocks into shared memory (the key tile is free now), then
+    // each lane adds up its dims over the blocks in order, eight loads in flight.
+    constexpr int WCAP = KW * ROWB / 4;
+    float* weights = reinterpret_cast<float*>(k_tile) + warp * WCAP;
+    for (int row = warp; row < nh; row += WARPS) {
+        const size_t base = (pair0 + row) * max_splits;
+        float M = -INFINITY;
+        for (int sidx = lane; sidx < splits; sidx += 32) M = fmaxf(M, __ldcg(&part_ml[(base + sidx) * 2]));
+        M = warp_max(M);
+        float denom = 0.f;
+        for (int sidx = lane; sidx < splits; sidx += 32) {
+            const float w = exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
+            if (sidx < WCAP) weights[sidx] = w;
+            denom += w * __ldcg(&part_ml[(base + sidx) * 2 + 1]);
         }
-    }
-    denom = warp_sum(denom);
-    if (lane == 0) red[warp] = denom;
-    __syncthreads();
-    denom = red[0];
+        denom = warp_sum(denom);
+        __syncwarp();
+        const float inv = 1.0f / denom;
+        for (int d = lane; d < D; d += 32) {
+            float v = 0.f;
+            for (int s0 = 0; s0 < splits; s0 += 8) {
+                float x[8];
 #pragma unroll
-    for (int w = 1; w < WARPS; ++w) denom += red[w];
-    const float inv = 1.0f / denom;
-    for (int d = tid; d < D; d += THREADS) {
-        float v = 0.f;
-        for (int s0 = 0; s0 < splits; s0 += 8) {                        // blocks in order, 8 loads in flight
-            float x[8];
+                for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
-#pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (s0 + u < splits) {
-                    const int s = s0 + u;
-                    const float w = s < SPLIT ? ml[s] : exp2f(__ldcg(&part_ml[(base + s) * 2]) - M);
-                    v = fmaf(w, x[u], v);
-                }
+                for (int u = 0; u < 8; ++u)
+                    if (s0 + u < splits) {
+                        const int sidx = s0 + u;
+                        const float w = sidx < WCAP ? weights[sidx] : exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
+                        v = fmaf(w, x[u], v);
+                    }
+            }
+            out[(pair0 + row) * D + d] = __float2bfloat16_rn(v * inv);
         }
-        out[pair * D + d] = __float2bfloat16_rn(v * inv);
+        __syncwarp();
     }
 }
 
@@ -328,19 +359,23 @@ template <int D>
 int launch(const void* qkv, const void* k_pages, const void* v_pages, const int* block_table,
            const int* token_request, const int* positions, void* out, float* part_out, float* part_ml,
            int* counters, int n_tokens, int n_head, int n_kv_head, int page_tokens, int max_pages, int window,
-           int max_splits, float scale, int* status, cudaStream_t s) {
-    constexpr size_t smem = (size_t)2 * split_keys(D) * D * sizeof(bf16);
+           int max_splits, float scale, cudaStream_t s) {
+    const int group = n_head / n_kv_head;
+    const int head_tiles = (group + HEAD_ROWS - 1) / HEAD_ROWS;
+    const int nh_max = group < HEAD_ROWS ? group : HEAD_ROWS;
+    const size_t smem = (size_t)2 * split_keys(D) * D * sizeof(bf16) + (size_t)WARPS * nh_max * (D + 8) * sizeof(bf16) +
+                        (size_t)split_keys(D) * sizeof(int) + (size_t)WARPS * nh_max * (D + 2) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention (split): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
-    dim3 grid(n_tokens, n_head, max_splits);
+    dim3 grid(n_tokens, n_kv_head * head_tiles, max_splits);
     cudaError_t le = mg_launch(attention_split_kernel<D>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
                                (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
                                (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                               window, max_splits, scale * 1.4426950408889634f, status);
+                               window, max_splits, scale * 1.4426950408889634f, head_tiles);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     return MG_OK;
@@ -365,19 +400,20 @@ MG_API long long mg_attention_split_scratch_floats(int n_tokens, int n_head, int
 // qkv / pages / out as mg_paged_attention_generic, bfloat16 only.  `scratch` holds
 // mg_attention_split_scratch_floats() floats and need not be initialised; `counters` holds
 // n_tokens * n_head ints that are ZERO before the first launch (the kernel leaves them zero);
-// `max_splits` = mg_attention_split_count() of the longest context; `status` receives a
-// non-zero code if a wait ran out.  Launches that share scratch or counters must not overlap.
+// `max_splits` = mg_attention_split_count() of the longest context; `status` is not written
+// (the kernel has no bounded wait).  Launches that share scratch or counters must not overlap.
 MG_API int mg_paged_attention_split(const void* qkv, const void* k_pages, const void* v_pages,
                                     const int* block_table, const int* token_request, const int* positions,
                                     void* out, float* scratch, int* counters, int n_tokens, int n_head,
                                     int n_kv_head, int head_dim, int page_tokens, int max_pages, int window,
                                     int max_splits, float scale, int* status, void* stream) {
+    (void)status;
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && max_splits > 0,
                "attention (split): bad sizes");
     MG_REQUIRE(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
     MG_REQUIRE(n_head <= 65535 && max_splits <= 65535, "attention (split): too many heads or key blocks");
-    MG_REQUIRE(scratch != nullptr && counters != nullptr && status != nullptr, "attention (split): missing scratch");
+    MG_REQUIRE(scratch != nullptr && counters != nullptr, "attention (split): missing scratch");
     cudaStream_t s = (cudaStream_t)stream;
     float* part_out = scratch;
     float* part_ml = scratch + (size_t)n_tokens * n_head * max_splits * head_dim;
@@ -385,7 +421,7 @@ MG_API int mg_paged_attention_split(const void* qkv, const void* k_pages, const 
     case DIM:                                                                                                     \
         return launch<DIM>(qkv, k_pages, v_pages, block_table, token_request, positions, out, part_out, part_ml, \
                            counters, n_tokens, n_head, n_kv_head, page_tokens, max_pages, window, max_splits,    \
-                           scale, status, s)
+                           scale, s)
     switch (head_dim) {
         MG_SPLIT_CASE(16);
         MG_SPLIT_CASE(32);

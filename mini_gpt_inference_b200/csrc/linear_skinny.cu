@@ -24,11 +24,7 @@
 // Every output element sums its K terms in a fixed order (k blocks in order inside a slice,
 // slices in order), independent of M and of the other rows.  K must be a multiple of 8 and the
 // activations must fit the shared memory; other sizes are refused (the tensor-core GEMM takes them).
-#include "common.cuh"
-
-#define EPI_STORE 0
-#define EPI_GELU 1
-#define EPI_RESIDUAL 2
+#include "linear_epilogue.cuh"
 
 namespace {
 
@@ -47,30 +43,15 @@ struct SkinnyArgs {
     const float* shift;              // may be null
     float eps;
     const bf16* w;                   // [N, K]
-    const float* bias;               // may be null
-    void* out;                       // [M, N]
-    float* residual;                 // [M, N] for EPI_RESIDUAL
-    int M, N, K, epilogue, out_bf16;
+    LinearEpilogue ep;
+    int M, N, K;
     int k_splits;                    // warps that share one tile of 8 rows (1, 2, 4 or 8)
     int tiles_per_cta;
-    // key/value sink of the QKV projection (k_pages null: none)
-    bf16* k_pages;
-    bf16* v_pages;
-    const int* slots;                // [M] flat cache row of each token, < 0: skip
-    int q_width, n_kv_head, head_dim, page_tokens;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
 template <int MT>   // token rows of the A operand: 8 (rows 8..15 are zero) or 16; a.M <= MT
@@ -110,7 +91,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     {
         const int ti = tid / (MT * TILE_N), r = tid % TILE_N;
         const int n = (first_tile + ti) * TILE_N + r;
-        if (a.bias && ti < tiles_per_round && ti < a.tiles_per_cta && n < a.N) first_bias = a.bias[n];
+        if (a.ep.bias && ti < tiles_per_round && ti < a.tiles_per_cta && n < a.N) first_bias = a.ep.bias[n];
     }
     // Weights and bias do not depend on the kernel before this one; everything below does.
     pdl_trigger();
@@ -190,8 +171,8 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         const int e_ti = tid / (MT * TILE_N), e_rem = tid - e_ti * (MT * TILE_N);
         const int e_m = e_rem / TILE_N, e_n = (first_tile + t0 + e_ti) * TILE_N + (e_rem - e_m * TILE_N);
         float e_res = 0.f;
-        if (a.epilogue == EPI_RESIDUAL && e_ti < tiles_per_round && t0 + e_ti < a.tiles_per_cta && e_n < a.N && e_m < a.M)
-            e_res = a.residual[(size_t)e_m * a.N + e_n];
+        if (a.ep.epilogue == EPI_RESIDUAL && e_ti < tiles_per_round && t0 + e_ti < a.tiles_per_cta && e_n < a.N && e_m < a.M)
+            e_res = a.ep.residual[(size_t)e_m * a.N + e_n];
         float c[4] = {0.f, 0.f, 0.f, 0.f};
         if (active) {
             const bf16* wrow = a.w + (size_t)min(tile * TILE_N + g, a.N - 1) * K;
@@ -236,29 +217,8 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             if ((t0 + ti) >= a.tiles_per_cta || n >= a.N || m >= a.M) continue;
             float v = 0.f;
             for (int s = 0; s < ks; ++s) v += partial[((size_t)(ti * ks + s) * MT + m) * TILE_N + r];   // slices in order
-            if (a.bias) v += (e == tid && t0 == 0) ? first_bias : a.bias[n];
-            if (a.epilogue == EPI_GELU) v = gelu_tanh(v);
-            const size_t idx = (size_t)m * a.N + n;
-            if (a.epilogue == EPI_RESIDUAL) {
-                a.residual[idx] = (e == tid ? e_res : a.residual[idx]) + v;
-            } else if (a.out_bf16) {
-                const bf16 hv = __float2bfloat16_rn(v);
-                reinterpret_cast<bf16*>(a.out)[idx] = hv;
-                if (a.k_pages != nullptr && n >= a.q_width) {
-                    const int slot = a.slots[m];
-                    if (slot >= 0) {
-                        const int kv_width = a.n_kv_head * a.head_dim;
-                        const int f = n - a.q_width;
-                        const int which = f / kv_width, fi = f - which * kv_width;
-                        const int h = fi / a.head_dim, d = fi - h * a.head_dim;
-                        const int page = slot / a.page_tokens, off = slot - page * a.page_tokens;
-                        const size_t dst = (((size_t)page * a.n_kv_head + h) * a.page_tokens + off) * a.head_dim + d;
-                        (which == 0 ? a.k_pages : a.v_pages)[dst] = hv;
-                    }
-                }
-            } else {
-                reinterpret_cast<float*>(a.out)[idx] = v;
-            }
+            if (a.ep.bias) v += (e == tid && t0 == 0) ? first_bias : a.ep.bias[n];
+            linear_finish(a.ep, m, n, v, e == tid, e_res);
         }
         __syncthreads();
     }
@@ -297,10 +257,11 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
                "linear: bad key/value sink");
     SkinnyArgs a;
     a.x = (const bf16*)x; a.x32 = x ? nullptr : x32; a.row_index = row_index; a.gain = gain; a.shift = shift; a.eps = eps;
-    a.w = (const bf16*)w; a.bias = bias; a.out = out; a.residual = residual;
-    a.M = M; a.N = N; a.K = K; a.epilogue = epilogue; a.out_bf16 = out_bf16;
-    a.k_pages = (bf16*)k_pages; a.v_pages = (bf16*)v_pages; a.slots = slots;
-    a.q_width = q_width; a.n_kv_head = n_kv_head; a.head_dim = head_dim; a.page_tokens = page_tokens;
+    a.w = (const bf16*)w; a.M = M; a.N = N; a.K = K;
+    a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
+    a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
+    a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
     // Cut the work so that every SM gets some and a lane holds all its weights at once: tiles of
     // 8 rows, each shared by k_splits warps with at least two k blocks (of 32) per warp.
     const int tiles = (N + TILE_N - 1) / TILE_N;

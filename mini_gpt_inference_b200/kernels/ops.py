@@ -16,6 +16,7 @@ from .library import KernelLibraryError, check
 
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
+CLUSTER_ROWS = 64        # most tokens the mid-batch (K split over a cluster) projection kernel takes
 
 
 class DeferredNorm:
@@ -65,6 +66,7 @@ class CudaOps:
         self.use_tensor_cores = True
         self.use_split_attention = True
         self.use_skinny = True
+        self.use_cluster = True
         self.use_dependent_launch = True
         self.use_prefill_tc = True
         self._counter_buf = None
@@ -206,6 +208,17 @@ class CudaOps:
         if deferred is not None:
             x = deferred.materialize()
         self._want(x, weight.dtype, "linear input", 2)
+        if x.dtype == torch.bfloat16 and self.use_cluster and 0 < m <= CLUSTER_ROWS and k % 8 == 0:
+            sink = [None, None, None, 0, 0, 0, 0]
+            if kv_sink is not None:
+                cache, slots, n_head, n_kv_head, head_dim = kv_sink
+                sink = [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim,
+                        n_kv_head, head_dim, cache.page_tokens]
+            code = self.lib.mg_linear_cluster(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                              m, n, k, epilogue, out_bf16, *sink, self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "linear (mid batch)")
+                return kv_sink is not None
         if x.dtype == torch.bfloat16 and self.use_tensor_cores:
             code = self.lib.mg_linear_tc(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                          m, n, k, epilogue, out_bf16, _ptr(self.status),

@@ -134,6 +134,34 @@ def test_small_batch_projection_with_fused_norm(ops, m, n, k):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m", [17, 24, 32, 33, 50, 64])
+@pytest.mark.parametrize("n,k", [(1536, 512), (512, 2048), (509, 96), (200, 200), (77, 40), (2048, 4096)])
+def test_mid_batch_projection_over_a_cluster(ops, m, n, k):
+    """17 to 64 tokens: K cut over the CTAs of a cluster, partial sums met through distributed
+    shared memory; every epilogue, against the formula and against the tensor-core kernel."""
+    x = randn(m, k, dtype=torch.bfloat16, seed=31)
+    w = randn(n, k, dtype=torch.bfloat16, seed=32, scale=1 / math.sqrt(k))
+    b = randn(n, seed=33)
+    want = x.double() @ w.double().T + b.double()
+    before = ops.launches
+    got = ops.linear(x, w, b, "none", torch.float32)
+    assert ops.launches == before + 1
+    assert (got.double() - want).abs().max() <= 2e-4
+    ops.use_cluster = False
+    try:
+        other = ops.linear(x, w, b, "none", torch.float32)
+    finally:
+        ops.use_cluster = True
+    assert (got - other).abs().max() <= 1e-4                  # same bf16 inputs, 32-bit sums
+    res = randn(m, n, seed=34)
+    keep = res.clone()
+    ops.linear_residual(x, w, b, res)
+    assert (res.double() - (keep.double() + want)).abs().max() <= 2e-4
+    gl = ops.linear(x, w, None, "gelu_tanh", torch.bfloat16)
+    assert (gl.double() - plain_gpt.gelu_tanh(want - b.double())).abs().max() <= 3e-2
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [1, 4, 8, 9, 40])
 def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m):
     n_head, n_kv, d, pt, pages, k = 6, 2, 32, 8, 12, 96
