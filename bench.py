@@ -9,7 +9,9 @@ run has the layer sizes of the 50M configuration (8 layers, width 512, 8 heads o
 bfloat16, a batch of 8 and contexts that end at 2048 tokens.  One JSON line is printed:
 
 * ``value``: decoded tokens per second from the device time of K decode steps (CUDA events
-  around each step's work on the stream; L2 is flushed between steps, outside the events);
+  around each step's work on the stream; L2 is flushed between steps, outside the events; a
+  step takes the tokens that the step before sampled on the device, as the engine does in
+  steady decoding, so the host prepares the next step while the device runs this one);
 * ``e2e``: the same through ``LLMEngine.step()`` with host token ids in and out, wall clock;
 * ``prefill``: one 2,048-token prompt; ``roofline``: bytes a decode step must read / its time;
 * ``points``: decode at batch 1 and 64.
@@ -193,7 +195,7 @@ def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None)
     last = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
     greedy = [SamplingParams(temperature=0.0)] * batch
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
-    times = []
+    events, ids, feed = [], None, list(range(batch))
     launches_before = getattr(runner.ops, "launches", 0)
     torch.cuda.synchronize()
     for step in range(steps + warmup):
@@ -205,13 +207,19 @@ def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None)
             if clock_sampler is not None:
                 clock_sampler.start()                   # clocks of the timed steps only
         start.record()
-        logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
+        if ids is None:
+            logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
+        else:
+            # the tokens sampled by the step before are taken on the device, as the engine does
+            # in steady decoding: the host prepares this step while the device runs the last one
+            logits = runner.step([StepEntry(rid, [0], [0]) for rid in rids], copy=False,
+                                 token_sources=feed, previous_ids=ids)
         ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch)
         end.record()
-        last = ids.tolist()                            # device -> host: the step's result
-        if step >= warmup:
-            times.append(start.elapsed_time(end))
+        events.append((start, end))
     torch.cuda.synchronize()
+    last = ids.tolist()                                # device -> host: the last step's result
+    times = [a.elapsed_time(b) for a, b in events[warmup:]]
     clocks = clock_sampler.stop() if clock_sampler is not None else None
     launches = getattr(runner.ops, "launches", 0) - launches_before
     for rid in rids:
