@@ -169,6 +169,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     const uint32_t tmem_base = sync->tmem_base;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+    // The work list, positions and block tables are inputs of the step; queries, keys and values
+    // come from the kernels in front, and nothing is read or written of them before this wait.
+    pdl_trigger();
+    pdl_wait();
 
     // Issue the tile loads of one key block (thread 0 only): keys into a stage of the ring,
     // values into the single value tile.
@@ -380,6 +384,8 @@ attention_prefill_merge_kernel(const int* __restrict__ work, const float* __rest
     const int item = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
     const int row0 = work[5 * item + 1], n_rows = work[5 * item + 2];
     const int chunk = work[5 * item + 3], n_chunks = work[5 * item + 4];
+    pdl_trigger();
+    pdl_wait();                                                       // the partial rows come from the kernel in front
     if (chunk != 0 || n_chunks == 1 || tid >= n_rows) return;
     const size_t stride = (size_t)n_head * (D + 2) * BQ;              // between items
     const float* base = partial + ((size_t)item * n_head + head) * (D + 2) * BQ + tid;
@@ -492,12 +498,15 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
         configured = true;
     }
     dim3 grid(n_items, n_head);
-    attention_prefill_tc_kernel<<<grid, THREADS, smem, (cudaStream_t)stream>>>(
-        map_q, map_k, map_v, work, block_table, positions, (bf16*)out, partial, n_head, n_kv_head, page_tokens,
-        box_rows, max_pages, window, scale * 1.4426950408889634f, status);
+    cudaError_t le = mg_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, true, map_q,
+                               map_k, map_v, work, block_table, positions, (bf16*)out, partial, n_head, n_kv_head,
+                               page_tokens, box_rows, max_pages, window, scale * 1.4426950408889634f, status);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_prefill_tc: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_prefill_tc");
     if (merge) {
-        attention_prefill_merge_kernel<<<grid, THREADS, 0, (cudaStream_t)stream>>>(work, partial, (bf16*)out, n_head);
+        le = mg_launch(attention_prefill_merge_kernel, grid, dim3(THREADS), 0, (cudaStream_t)stream, true, work,
+                       (const float*)partial, (bf16*)out, n_head);
+        if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_prefill_merge: %s", cudaGetErrorString(le));
         MG_CHECK_LAUNCH("attention_prefill_merge");
     }
     return MG_OK;

@@ -46,6 +46,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
                                  int rows, int width, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    pdl_trigger();
+    pdl_wait();                                        // x comes from the kernel in front
     if (row >= rows) return;
     const float* xr = x + (size_t)row * width;
     float sum = 0.f;
@@ -72,10 +74,9 @@ MG_API int mg_layernorm(const float* x, const float* gain, const float* shift, v
     cudaStream_t s = (cudaStream_t)stream;
     const int warps = 4;
     dim3 grid(ceil_div(rows, warps)), block(32 * warps);
-    if (out_bf16)
-        layernorm_kernel<bf16><<<grid, block, 0, s>>>(x, gain, shift, (bf16*)y, rows, width, eps);
-    else
-        layernorm_kernel<float><<<grid, block, 0, s>>>(x, gain, shift, (float*)y, rows, width, eps);
+    const cudaError_t le = out_bf16 ? mg_launch(layernorm_kernel<bf16>, grid, block, 0, s, true, x, gain, shift, (bf16*)y, rows, width, eps)
+                                    : mg_launch(layernorm_kernel<float>, grid, block, 0, s, true, x, gain, shift, (float*)y, rows, width, eps);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "layernorm: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("layernorm");
     return MG_OK;
 }
@@ -106,6 +107,8 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, const int* __restrict
                                 int q_width, int n_kv_head, int head_dim, int page_tokens) {
     const int n = blockIdx.x;
     const int slot = slots[n];
+    pdl_trigger();
+    pdl_wait();                                        // qkv comes from the kernel in front
     if (slot < 0) return;
     const int page = slot / page_tokens, off = slot - page * page_tokens;
     const int kv_width = n_kv_head * head_dim;
@@ -127,12 +130,12 @@ MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v
                "kv_store: bad sizes");
     cudaStream_t s = (cudaStream_t)stream;
     const int q_width = n_head * head_dim, qkv_width = (n_head + 2 * n_kv_head) * head_dim;
-    if (is_bf16)
-        kv_store_kernel<bf16><<<n_tokens, 128, 0, s>>>((const bf16*)qkv, slots, (bf16*)k_pages, (bf16*)v_pages,
-                                                     qkv_width, q_width, n_kv_head, head_dim, page_tokens);
-    else
-        kv_store_kernel<float><<<n_tokens, 128, 0, s>>>((const float*)qkv, slots, (float*)k_pages, (float*)v_pages,
-                                                      qkv_width, q_width, n_kv_head, head_dim, page_tokens);
+    const cudaError_t le =
+        is_bf16 ? mg_launch(kv_store_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, true, (const bf16*)qkv, slots, (bf16*)k_pages,
+                            (bf16*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens)
+                : mg_launch(kv_store_kernel<float>, dim3(n_tokens), dim3(128), 0, s, true, (const float*)qkv, slots,
+                            (float*)k_pages, (float*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "kv_store: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("kv_store");
     return MG_OK;
 }

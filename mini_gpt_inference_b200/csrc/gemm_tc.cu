@@ -199,6 +199,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
+    // Barriers, tensor memory and the bias are set up while the kernel in front drains; its
+    // results (the activations, the residual stream) are touched only from here on.
+    pdl_trigger();
+    pdl_wait();
 
     if (tid == 0) {
         // ---- producer: TMA loads into the ring of stages ----
@@ -441,8 +445,9 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
         configured = true;
     }
     dim3 grid(ceil_div(rows_p, TILE_P), ceil_div(rows_q, BN));
-    gemm_tc_kernel<BN, SWAP><<<grid, 128, smem, s>>>(map_p, map_q, bias, out, residual, rows_p, rows_q, K, ld_out,
-                                                    epilogue, out_bf16, stages, status);
+    const cudaError_t le = mg_launch(gemm_tc_kernel<BN, SWAP>, grid, dim3(128), smem, s, true, map_p, map_q, bias, out,
+                                     residual, rows_p, rows_q, K, ld_out, epilogue, out_bf16, stages, status);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("gemm_tc");
     return MG_OK;
 }

@@ -23,7 +23,7 @@ import torch
 
 from ..cache.manager import NO_PAGE, CacheFullError, CacheManager
 from ..cache.storage import CacheStorage
-from ..parts.context import StepContext, query_tiles
+from ..parts.context import KEY_CHUNK, StepContext, query_tiles
 from ..parts.model import DecoderModel
 
 
@@ -52,8 +52,34 @@ class _DecodeGraph:
     kernels: int = 0              # kernel launches inside the graph
 
 
+@dataclass
+class _Packed:
+    """The integers of one step, packed on the host, and what the host itself needs of them."""
+
+    buf: np.ndarray
+    offsets: np.ndarray
+    total: int
+    work_items: int
+    q_len: list
+    ctx_before: list
+    state_slot: list
+    wanted: int
+
+
+@dataclass
+class _ShapeGraph:
+    """A captured step of one shape (tokens per request, attention work items, wanted rows)."""
+
+    meta: torch.Tensor
+    staging: torch.Tensor
+    graph: object
+    logits: torch.Tensor | None
+    kernels: int
+
+
 class ModelRunner:
     GRAPH_ROWS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    SHAPE_GRAPHS = 16              # most captured prompt-step shapes kept at a time
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
                  ops, act_dtype: torch.dtype, device, max_context: int | None = None,
@@ -83,6 +109,12 @@ class ModelRunner:
         self._graph_pool = None
         self._copy_done = None
         self.graph_replays = 0
+        # Steps with prompt portions: a shape that comes a second time (full portions of a long
+        # prompt, a benchmark's repeated prompt) is captured too; the host then issues one launch
+        # instead of sixty, which is what bounds such a step on a fast GPU.
+        self._shape_seen: dict[tuple, int] = {}
+        self._shape_graphs: dict[tuple, _ShapeGraph] = {}
+        self.shape_graph_replays = 0
 
     # ---- requests ---------------------------------------------------------------------
     def length_of(self, request_id: str) -> int:
@@ -103,10 +135,15 @@ class ModelRunner:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
-            for t in e.tokens:
-                if not (0 <= int(t) < self.vocab_size):
-                    raise StepError(f"token id {t} of request {e.request_id!r} is outside "
-                                    f"the vocabulary (0..{self.vocab_size - 1})")
+            if n > 16:                                   # a prompt portion: one pass in numpy
+                ids = np.asarray(e.tokens)
+                low, high = int(ids.min()), int(ids.max())
+                bad = low if low < 0 else high if high >= self.vocab_size else None
+            else:
+                bad = next((t for t in e.tokens if not (0 <= int(t) < self.vocab_size)), None)
+            if bad is not None:
+                raise StepError(f"token id {bad} of request {e.request_id!r} is outside "
+                                f"the vocabulary (0..{self.vocab_size - 1})")
             for w in e.want:
                 if not (0 <= int(w) < n):
                     raise StepError(f"request {e.request_id!r} wants logits at {w}, "
@@ -139,17 +176,18 @@ class ModelRunner:
             ok = m.reserve(e.request_id, m.get(e.request_id).length + len(e.tokens))
             assert ok, "pages were counted a moment ago"
 
-    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
-        """Pack the step's integers, copy them to the device once, and describe the batch."""
+    def _pack(self, entries: Sequence[StepEntry]) -> _Packed:
+        """Pack the step's integers into one int32 buffer on the host."""
         m = self.manager
         n_groups = len(m.groups)
         R = len(entries)
         N = sum(len(e.tokens) for e in entries)
         W = sum(len(e.want) for e in entries)
         P = self.max_pages
+        host_q_len = [len(e.tokens) for e in entries]
+        host_ctx = [m.get(e.request_id).length for e in entries]
         # work items of the tiled attention kernels (runs of queries x chunks of keys)
-        work = query_tiles([len(e.tokens) for e in entries],
-                           [m.get(e.request_id).length for e in entries])
+        work = query_tiles(host_q_len, host_ctx)
         # layout of the packed int32 buffer
         sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [5 * len(work)]
         offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
@@ -188,25 +226,35 @@ class ModelRunner:
             row += n
 
         seg(8 + 2 * n_groups)[:] = np.asarray(work, dtype=np.int32).reshape(-1)
-        dev = self._to_device(buf, total)
+        return _Packed(buf, offsets, total, len(work), host_q_len, host_ctx,
+                       [m.get(e.request_id).state_slot for e in entries], W)
+
+    def _context(self, dev: torch.Tensor, packed: _Packed) -> StepContext:
+        """Describe the batch whose packed integers lie in ``dev``."""
+        offsets, n_groups = packed.offsets, len(self.manager.groups)
+        R, P = len(packed.q_len), self.max_pages
 
         def dseg(i):
             return dev[int(offsets[i]): int(offsets[i + 1])]
 
-        host_q_len = [len(e.tokens) for e in entries]
-        host_ctx = [m.get(e.request_id).length for e in entries]
         return StepContext(
-            ops=self.ops, act_dtype=self.act_dtype, num_tokens=N, num_requests=R,
+            ops=self.ops, act_dtype=self.act_dtype, num_tokens=sum(packed.q_len), num_requests=R,
             token_ids=dseg(0), positions=dseg(1), token_request=dseg(2),
             req_q_start=dseg(3), req_q_len=dseg(4), req_ctx_before=dseg(5),
             req_state_slot=dseg(6), logit_rows=dseg(7),
             block_tables=[dseg(8 + g).view(R, P) for g in range(n_groups)],
             slot_mapping=[dseg(8 + n_groups + g) for g in range(n_groups)],
-            attn_work=dseg(8 + 2 * n_groups).view(len(work), 5),
-            host_q_len=host_q_len, host_ctx_before=host_ctx,
-            host_state_slot=[m.get(e.request_id).state_slot for e in entries],
-            max_q_len=max(host_q_len), max_ctx_after=max(a + b for a, b in zip(host_q_len, host_ctx)),
-            decode_only=all(n == 1 for n in host_q_len), storage=self.storage)
+            attn_work=dseg(8 + 2 * n_groups).view(packed.work_items, 5),
+            host_q_len=packed.q_len, host_ctx_before=packed.ctx_before,
+            host_state_slot=packed.state_slot,
+            max_q_len=max(packed.q_len),
+            max_ctx_after=max(a + b for a, b in zip(packed.q_len, packed.ctx_before)),
+            decode_only=all(n == 1 for n in packed.q_len), storage=self.storage)
+
+    def build_context(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Pack the step's integers, copy them to the device once, and describe the batch."""
+        packed = self._pack(entries)
+        return self._context(self._to_device(packed.buf, packed.total), packed)
 
     def _to_device(self, buf: np.ndarray, total: int) -> torch.Tensor:
         self.last_h2d_bytes = 4 * total
@@ -341,6 +389,78 @@ class ModelRunner:
             copy = False
         return logits.clone() if copy else logits
 
+    # ---- steps with prompt portions: eager, or replayed once their shape has come twice --------
+    def _prompt_step(self, entries: Sequence[StepEntry], copy: bool):
+        packed = self._pack(entries)
+        decode_only = all(n == 1 for n in packed.q_len)
+        if not self.use_cuda_graphs or decode_only:
+            return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
+        # what the launches of a step depend on besides the device-side integers
+        merge = max(a + b for a, b in zip(packed.q_len, packed.ctx_before)) > KEY_CHUNK
+        key = (tuple(packed.q_len), packed.work_items, packed.wanted, merge)
+        state = self._shape_graphs.get(key)
+        if state is None:
+            seen = self._shape_seen.get(key, 0) + 1
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            self._shape_seen[key] = seen
+            if seen < 2:
+                return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
+            return self._capture_shape(key, packed)
+        self._shape_graphs[key] = self._shape_graphs.pop(key)         # most recently used last
+        self._stage(state, packed)
+        state.graph.replay()
+        self.shape_graph_replays += 1
+        if hasattr(self.ops, "launches"):
+            self.ops.launches += state.kernels
+        if state.logits is None:
+            return None
+        return state.logits.clone() if copy else state.logits
+
+    def _stage(self, state: _ShapeGraph, packed: _Packed) -> None:
+        if self._copy_done is not None:
+            self._copy_done.synchronize()                 # the staging buffer is free again
+        state.staging.numpy()[: packed.total] = packed.buf[: packed.total]
+        state.meta.copy_(state.staging, non_blocking=True)
+        if self._copy_done is None:
+            self._copy_done = torch.cuda.Event()
+        self._copy_done.record()
+        self.last_h2d_bytes = 4 * packed.total
+
+    def _capture_shape(self, key: tuple, packed: _Packed):
+        """Run the step eagerly from persistent inputs (its result is returned), then capture
+        the same launches for the next step of this shape."""
+        size = max(packed.total, 1)
+        state = _ShapeGraph(torch.zeros(size, dtype=torch.int32, device=self.device),
+                            torch.zeros(size, dtype=torch.int32, pin_memory=True), None, None, 0)
+        self._stage(state, packed)
+        ctx = self._context(state.meta, packed)
+        result = self.model.forward(ctx)
+        if result is not None:
+            result = result.clone()                        # the capture below reuses the memory
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        launches = getattr(self.ops, "launches", 0)
+        dependent = getattr(self.ops, "set_dependent_launch", None)
+        if dependent is not None:
+            dependent(True)
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                state.logits = self.model.forward(ctx)
+        finally:
+            if dependent is not None:
+                dependent(False)
+        state.kernels = getattr(self.ops, "launches", 0) - launches
+        if hasattr(self.ops, "launches"):
+            self.ops.launches = launches                   # captured, not run
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        state.graph = graph
+        while len(self._shape_graphs) >= self.SHAPE_GRAPHS:
+            self._shape_graphs.pop(next(iter(self._shape_graphs)))     # least recently used
+        self._shape_graphs[key] = state
+        return result
+
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether a step of ``n_entries`` single tokens may take its tokens from the ids that the
         previous step sampled, without the host seeing them first (``token_sources``)."""
@@ -367,8 +487,7 @@ class ModelRunner:
                 and all(len(e.tokens) == 1 for e in entries)):
             logits = self._graph_step(entries, copy, token_sources, previous_ids)
         else:
-            ctx = self.build_context(entries)
-            logits = self.model.forward(ctx)
+            logits = self._prompt_step(entries, copy)
         for e in entries:
             self.manager.advance(e.request_id, self.manager.get(e.request_id).length + len(e.tokens))
         return logits

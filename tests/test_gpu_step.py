@@ -116,6 +116,49 @@ def test_mixed_requests_with_page_reuse(which, dtype, sharp):
         assert_close(torch.cat(got[rid]), want[rid], tol, f"mixed batch, request {rid}")
 
 
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "bfloat16"), ("A", "bfloat16")])
+def test_prompt_steps_of_a_repeated_shape_are_replayed(which, dtype):
+    """A step shape that comes a second time is captured and replayed from then on (different
+    tokens, other pages, a request beside it): the logits stay those of the plain
+    implementation, and equal those of a runner that never captures."""
+    cfg, tensors, runner, tol = _setup(which, dtype, False)
+    _, _, eager, _ = _setup(which, dtype, False)
+    eager.use_cuda_graphs = False
+    n = min(23, cfg.n_positions - 6)
+    outs = []
+    for rep in range(5):
+        a, b = tokens_for(cfg, n + 5, 40 + rep), tokens_for(cfg, 6, 60 + rep)
+        want_a, want_b = plain_logits(cfg, tensors, a), plain_logits(cfg, tensors, b)
+        for r in (runner, eager):
+            r.step([StepEntry("a", a[:5], [])])                      # another shape in between
+            got = r.step([StepEntry("a", a[5:], list(range(n))), StepEntry("b", b, [5, 0])])
+            assert_close(got[:n], want_a[5:], tol, f"repeat {rep}, request a")
+            assert_close(got[n:], want_b[[5, 0]], tol, f"repeat {rep}, request b")
+            outs.append(got)
+            r.finish("a")
+            if rep % 2 == 0:
+                r.finish("b")                                      # b's pages change every other time
+            else:
+                r.step([StepEntry("b", [1], [])])
+                r.finish("b")
+    assert runner.shape_graph_replays >= 3 and eager.shape_graph_replays == 0
+    for mine, theirs in zip(outs[0::2], outs[1::2]):
+        assert torch.equal(mine, theirs), "a replayed step differs from the same launches run eagerly"
+    runner.manager.check()
+
+
+def test_captured_shapes_are_bounded():
+    cfg, tensors, runner, tol = _setup("A", "bfloat16", False)
+    runner.SHAPE_GRAPHS = 3
+    for n in (2, 3, 4, 5, 6, 7):
+        for rep in range(3):
+            tokens = tokens_for(cfg, n, 80 + n)
+            got = runner.step([StepEntry("r", tokens, [n - 1])])
+            assert_close(got, plain_logits(cfg, tensors, tokens)[-1:], tol, f"{n} tokens, repeat {rep}")
+            runner.finish("r")
+    assert len(runner._shape_graphs) == 3 and runner.shape_graph_replays == 6
+
+
 @pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "float32")])
 def test_cuttings_agree_bitwise_in_32bit(which, dtype):
     """In 32-bit every (token, head) and every output element is computed by the same
