@@ -214,7 +214,8 @@ def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None)
             # in steady decoding: the host prepares this step while the device runs the last one
             logits = runner.step([StepEntry(rid, [0], [0]) for rid in rids], copy=False,
                                  token_sources=feed, previous_ids=ids)
-        ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch)
+        ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch,
+                             greedy_ids=runner.greedy_ids(batch), out=runner.sampled_ids[:batch])
         end.record()
         events.append((start, end))
     torch.cuda.synchronize()

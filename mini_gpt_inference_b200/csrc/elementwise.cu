@@ -155,3 +155,20 @@ MG_API int mg_gather_tokens(int* token_ids, const int* source, const int* previo
     MG_CHECK_LAUNCH("gather_tokens");
     return MG_OK;
 }
+
+// ---- a step's integers from pinned host memory ------------------------------------------------------
+// dst[i] = src[i], src being page-locked host memory that the device reads over the bus.  A few
+// kilobytes travel in a couple of microseconds, and unlike a copy on the DMA engine the kernel
+// puts no engine switch between itself and the kernels that follow on the stream.
+__global__ void copy_ints_kernel(int* __restrict__ dst, const int* __restrict__ src, int n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+MG_API int mg_copy_ints(int* dst, const int* src, int n, void* stream) {
+    if (n == 0) return MG_OK;
+    MG_REQUIRE(n > 0 && dst && src, "copy_ints: bad arguments");
+    const int blocks = ceil_div(n, 256) < 64 ? ceil_div(n, 256) : 64;
+    copy_ints_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(dst, src, n);
+    MG_CHECK_LAUNCH("copy_ints");
+    return MG_OK;
+}

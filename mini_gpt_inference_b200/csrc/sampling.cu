@@ -48,6 +48,8 @@ argmax_part_kernel(const float* __restrict__ logits, float* __restrict__ part_v,
                    int vocab, int limit, int parts, int slice) {
     __shared__ float best_v[ARGMAX_THREADS / 32];
     __shared__ int best_i[ARGMAX_THREADS / 32];
+    pdl_trigger();
+    pdl_wait();                                        // the logits come from the kernel in front
     const float* row = logits + (size_t)blockIdx.x * vocab;
     const int begin = blockIdx.y * slice, end = min(limit, begin + slice);
     float v = -INFINITY;
@@ -86,6 +88,8 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int*
                                     int* __restrict__ out, int parts) {
     float v = -INFINITY;
     int idx = 0x7fffffff;
+    pdl_trigger();
+    pdl_wait();
     for (int k = threadIdx.x; k < parts; k += 32) {
         const float x = part_v[(size_t)blockIdx.x * parts + k];
         const int i = part_i[(size_t)blockIdx.x * parts + k];
@@ -128,10 +132,13 @@ MG_API int mg_argmax_wide(const float* logits, int* out, float* scratch_v, int* 
     const int parts = mg_argmax_parts(vocab);
     MG_REQUIRE(parts <= 65535, "argmax: vocabulary too wide");
     cudaStream_t s = (cudaStream_t)stream;
-    argmax_part_kernel<<<dim3(rows, parts), ARGMAX_THREADS, 0, s>>>(logits, scratch_v, scratch_i, vocab, limit, parts,
-                                                                  ARGMAX_SLICE);
+    cudaError_t le = mg_launch(argmax_part_kernel, dim3(rows, parts), dim3(ARGMAX_THREADS), 0, s, true, logits, scratch_v,
+                               scratch_i, vocab, limit, parts, ARGMAX_SLICE);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "argmax (parts): %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("argmax (parts)");
-    argmax_merge_kernel<<<rows, 32, 0, s>>>(scratch_v, scratch_i, out, parts);
+    le = mg_launch(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, true, (const float*)scratch_v, (const int*)scratch_i, out,
+                   parts);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "argmax (merge): %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("argmax (merge)");
     return MG_OK;
 }

@@ -55,6 +55,7 @@ class LLMEngine:
                                    self.engine_cfg.max_num_batched_tokens,
                                    self.engine_cfg.prefill_chunk)
         self.sampler = Sampler(ops, loaded.device, vocab_limit, seed)
+        self.runner.greedy_vocab_limit = vocab_limit     # before the first decode step is captured
         self.max_context = self.runner.max_context
         self._sequences: dict[str, SequenceState] = {}
         # Steady decoding overlaps the host with the device: a step is launched with the tokens
@@ -147,9 +148,11 @@ class LLMEngine:
         self.num_steps += 1
         self.num_overlapped_steps += 1
         self.num_tokens_run += len(rows)
+        # ids go where the next step's graph looks for its tokens; greedy rows are there already
         ids = self.sampler.sample(
             logits, [s.request.sampling_params for s in rows], [s.seed for s in rows],
-            [s.num_generated for s in rows])
+            [s.num_generated for s in rows], greedy_ids=self.runner.greedy_ids(len(rows)),
+            out=self.runner.sampled_ids[: len(rows)])
         slot = self.num_steps % 2
         if self._pinned_ids[slot] is None or self._pinned_ids[slot].numel() < len(rows):
             self._pinned_ids[slot] = torch.empty(max(len(rows), self.engine_cfg.max_batch_size),

@@ -112,6 +112,13 @@ class ModelRunner:
         # Steps with prompt portions: a shape that comes a second time (full portions of a long
         # prompt, a benchmark's repeated prompt) is captured too; the host then issues one launch
         # instead of sixty, which is what bounds such a step on a fast GPU.
+        # Ids sampled by a step, where the next step finds its tokens (``token_sources``).  A
+        # replayed decode step reads them at its start and leaves the argmax of its own logits
+        # there at its end, so steady greedy decoding launches nothing but the graph.
+        self.sampled_ids = (torch.zeros(self.GRAPH_ROWS[-1], dtype=torch.int32, device=self.device)
+                            if self.use_cuda_graphs else None)
+        self.greedy_vocab_limit: int | None = None      # ids at or above it are never chosen
+        self._greedy_rows = 0                            # rows of sampled_ids the last step filled
         self._shape_seen: dict[tuple, int] = {}
         self._shape_graphs: dict[tuple, _ShapeGraph] = {}
         self.shape_graph_replays = 0
@@ -269,6 +276,13 @@ class ModelRunner:
         self._pinned[:total].numpy()[:] = buf[:total]
         return self._pinned[:total].to(self.device, non_blocking=True)
 
+    def _upload(self, meta: torch.Tensor, staging: torch.Tensor) -> None:
+        upload = getattr(self.ops, "upload_ints", None)
+        if upload is not None and meta.numel() <= 4096:   # larger ones go faster on the copy engine
+            upload(meta, staging)
+        else:
+            meta.copy_(staging, non_blocking=True)
+
     # ---- decode steps as CUDA graphs ---------------------------------------------------------
     def _graph_layout(self, rows: int):
         g, pages = len(self.manager.groups), self.max_pages
@@ -307,9 +321,14 @@ class ModelRunner:
         dependent = getattr(self.ops, "set_dependent_launch", None)
         if dependent is not None:
             dependent(True)
+        sources = meta[offsets[8 + 2 * g]: offsets[9 + 2 * g]]
         try:
             with torch.cuda.graph(graph, pool=self._graph_pool):
+                # tokens that the step before sampled are fetched on the device (source >= 0)
+                self.ops.gather_tokens(ctx.token_ids, sources, self.sampled_ids)
                 state.logits = self.model.forward(ctx)
+                # and this step's greedy choice is left where the next step looks for it
+                self.ops.argmax(state.logits, self.greedy_vocab_limit, out=self.sampled_ids[:rows])
         finally:
             if dependent is not None:
                 dependent(False)
@@ -365,21 +384,21 @@ class ModelRunner:
         if self._copy_done is not None:
             self._copy_done.synchronize()                 # the staging buffer is free again
         self._fill_graph_inputs(state, entries, token_sources)
-        state.meta.copy_(state.staging, non_blocking=True)
+        self._upload(state.meta, state.staging)
         if self._copy_done is None:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()
         self.last_h2d_bytes = 4 * state.offsets[-1]
-        if token_sources is not None and previous_ids is not None:
-            off = state.offsets
-            g = len(self.manager.groups)
-            self.ops.gather_tokens(state.meta[off[0]: off[1]], state.meta[off[8 + 2 * g]: off[9 + 2 * g]],
-                                   previous_ids)
+        if token_sources is not None and previous_ids is not None and (
+                previous_ids.data_ptr() != self.sampled_ids.data_ptr()):
+            # ids that were sampled into a tensor of the caller's: bring them where the graph looks
+            self.sampled_ids[: previous_ids.numel()].copy_(previous_ids)
         state.graph.replay()
         self.graph_replays += 1
         if hasattr(self.ops, "launches"):
             self.ops.launches += state.kernels
         wanted = [r for r, e in enumerate(entries) if len(e.want)]
+        self._greedy_rows = len(entries) if len(wanted) == len(entries) else 0
         if not wanted:
             return None
         if len(wanted) == len(entries):
@@ -421,7 +440,7 @@ class ModelRunner:
         if self._copy_done is not None:
             self._copy_done.synchronize()                 # the staging buffer is free again
         state.staging.numpy()[: packed.total] = packed.buf[: packed.total]
-        state.meta.copy_(state.staging, non_blocking=True)
+        self._upload(state.meta, state.staging)
         if self._copy_done is None:
             self._copy_done = torch.cuda.Event()
         self._copy_done.record()
@@ -461,6 +480,13 @@ class ModelRunner:
         self._shape_graphs[key] = state
         return result
 
+    def greedy_ids(self, rows: int):
+        """The argmax of each of the last step's ``rows`` logit rows, if that step took it on its
+        way (a replayed decode step whose every entry wanted its logits); else None."""
+        if rows and self._greedy_rows == rows:
+            return self.sampled_ids[:rows]
+        return None
+
     def can_feed_tokens_on_device(self, n_entries: int) -> bool:
         """Whether a step of ``n_entries`` single tokens may take its tokens from the ids that the
         previous step sampled, without the host seeing them first (``token_sources``)."""
@@ -476,6 +502,7 @@ class ModelRunner:
         >= 0 the entry's token is taken on the device from ``previous_ids[token_sources[i]]``
         (int32 ids sampled by the step before) and the entry's own token is a placeholder."""
         entries = list(entries)
+        self._greedy_rows = 0
         if not entries:
             return None
         self._validate(entries)

@@ -35,6 +35,7 @@ _SIGNATURES = {
                                  _F, _P, _P],
     "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                 ctypes.c_longlong, _I, _I, _F, _P, _P],
+    "mg_copy_ints": [_P, _P, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],

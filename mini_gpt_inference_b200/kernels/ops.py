@@ -171,6 +171,15 @@ class CudaOps:
         self._run(self.lib.mg_gather_tokens(_ptr(token_ids), _ptr(source), _ptr(previous),
                                             token_ids.numel(), self._stream()), "gather_tokens")
 
+    def upload_ints(self, dst, pinned) -> None:
+        """dst[:] = pinned[:] where ``pinned`` is page-locked host memory: the device reads it
+        itself, so nothing switches engines between this and the kernels that follow."""
+        self._want(dst, torch.int32, "upload destination", 1)
+        if (pinned.dtype != torch.int32 or pinned.device.type != "cpu" or not pinned.is_pinned()
+                or pinned.numel() != dst.numel() or not pinned.is_contiguous()):
+            raise KernelLibraryError("upload_ints: the source must be pinned int32 host memory of the same size")
+        self._run(self.lib.mg_copy_ints(_ptr(dst), _ptr(pinned), dst.numel(), self._stream()), "upload_ints")
+
     # ---- projections ----------------------------------------------------------------------------
     def defer_layernorm(self, x32, gain, shift, eps, out_dtype, rows=None):
         """A LayerNorm to be fused into the projection that consumes it, where that pays."""
@@ -330,10 +339,18 @@ class CudaOps:
         return out
 
     # ---- sampling -------------------------------------------------------------------------------
-    def argmax(self, logits, vocab_limit=None):
+    def _ids_out(self, out, rows):
+        if out is None:
+            return torch.empty((rows,), dtype=torch.int32, device=self.device)
+        self._want(out, torch.int32, "ids", 1)
+        if out.numel() != rows:
+            raise KernelLibraryError(f"ids: room for {out.numel()} rows, {rows} wanted")
+        return out
+
+    def argmax(self, logits, vocab_limit=None, out=None):
         self._want(logits, torch.float32, "logits", 2)
         rows, vocab = logits.shape
-        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        out = self._ids_out(out, rows)
         if vocab >= 8192 and rows <= 512:
             # few rows of a wide vocabulary: many blocks per row, then a merge
             parts = self.lib.mg_argmax_parts(vocab)
@@ -348,7 +365,8 @@ class CudaOps:
                                  int(vocab_limit or 0), self._stream()), "argmax")
         return out
 
-    def sample(self, logits, temperature, top_k, top_p, seed_lo, seed_hi, counter, vocab_limit=None):
+    def sample(self, logits, temperature, top_k, top_p, seed_lo, seed_hi, counter, vocab_limit=None,
+               out=None):
         """One draw per row.  temperature float32 [rows]; top_k int32 [rows] or None (<= 0: off);
         top_p float32 [rows] or None (>= 1: off); seed_lo, seed_hi, counter: int32 [rows] holding
         the 32-bit words of each row's seed and the number of its draw."""
@@ -364,7 +382,7 @@ class CudaOps:
         for t in (temperature, top_k, top_p, seed_lo, seed_hi, counter):
             if t is not None and t.numel() != rows:
                 raise KernelLibraryError("sample: per-row parameters do not match the rows")
-        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        out = self._ids_out(out, rows)
         self._run(self.lib.mg_sample(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p),
                                  _ptr(seed_lo), _ptr(seed_hi), _ptr(counter), _ptr(out), rows,
                                  logits.shape[1], int(vocab_limit or 0), self._stream()), "sample")

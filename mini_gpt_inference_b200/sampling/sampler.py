@@ -32,12 +32,21 @@ class Sampler:
         """A seed for a request that gave none."""
         return int(self._rng.integers(0, 2**63 - 1))
 
-    def sample(self, logits: torch.Tensor, params, seeds, draw_numbers) -> torch.Tensor:
-        """``params[i]`` has temperature/top_k/top_p; returns int32 ids ``[rows]`` on the device."""
+    def sample(self, logits: torch.Tensor, params, seeds, draw_numbers, greedy_ids=None,
+               out=None) -> torch.Tensor:
+        """``params[i]`` has temperature/top_k/top_p; returns int32 ids ``[rows]`` on the device.
+
+        ``greedy_ids``: the argmax of every row if the step that made the logits took it already
+        (a replayed decode step does); it is returned as it is when every row is greedy.
+        ``out``: where to write the ids instead of a new tensor."""
         rows = logits.shape[0]
         if rows == 0:
             return torch.empty((0,), dtype=torch.int32, device=logits.device)
         if all(p.temperature <= 0 for p in params):
+            if greedy_ids is not None:
+                return greedy_ids
+            if out is not None:
+                return self.ops.argmax(logits, self.vocab_limit, out=out)
             return self.ops.argmax(logits, self.vocab_limit)
         vocab = logits.shape[1]
         packed = np.zeros((6, rows), dtype=np.int32)
@@ -51,6 +60,7 @@ class Sampler:
         dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
         use_k = any(p.top_k is not None and p.top_k < vocab for p in params)
         use_p = any(p.top_p is not None and p.top_p < 1.0 for p in params)
+        extra = {} if out is None else {"out": out}
         return self.ops.sample(logits, dev[0].view(torch.float32), dev[1] if use_k else None,
                                dev[2].view(torch.float32) if use_p else None,
-                               dev[3], dev[4], dev[5], self.vocab_limit)
+                               dev[3], dev[4], dev[5], self.vocab_limit, **extra)

@@ -80,6 +80,10 @@ class TorchOps:
     def logits(self, y, tok_emb):
         return y.float() @ tok_emb.float().T
 
-    def argmax(self, logits, vocab_limit=None):
+    def argmax(self, logits, vocab_limit=None, out=None):
         v = logits if vocab_limit is None else logits[:, :vocab_limit]
-        return v.argmax(-1).to(torch.int32)
+        ids = v.argmax(-1).to(torch.int32)
+        if out is None:
+            return ids
+        out.copy_(ids)
+        return out
