@@ -1,7 +1,7 @@
 """Each part alone against its plain formula, at sizes of its own; and the framework's
-generality: a toy mixer with per-request state of its own, a toy position encoding and a toy
-architecture, all defined here, are registered, built and stepped without touching the
-framework's files."""
+generality: a toy mixer with per-request state of its own, a toy feed-forward that routes each
+token to one of several experts, a toy position encoding and a toy architecture, all defined
+here, are registered, built and stepped without touching the framework's files."""
 
 from __future__ import annotations
 
@@ -22,7 +22,8 @@ from mini_gpt_inference_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, LayerCa
                                            Mixer, ModelSpec, PartSpec, PositionEncoding,
                                            StepContext, TensorSpec, register_mixer,
                                            register_position_encoding)
-from mini_gpt_inference_b200.parts.base import EMBEDDINGS, HEADS, POSITION_ENCODINGS
+from mini_gpt_inference_b200.parts.base import (EMBEDDINGS, HEADS, POSITION_ENCODINGS, FeedForward,
+                                                register_feed_forward)
 from mini_gpt_inference_b200.weights import random_tensors
 
 pytestmark = pytest.mark.gpu
@@ -193,6 +194,35 @@ class RunningMeanMixer(Mixer):
             start += n
 
 
+@register_feed_forward("toy_top1_experts")
+class Top1Experts(FeedForward):
+    """Every token goes to the one expert whose router logit is largest (logits in 32-bit, ties
+    to the lower index); an expert is ``proj(gelu(fc(y)))`` without biases."""
+
+    def __init__(self, prefix, width, inner, experts):
+        super().__init__(prefix)
+        self.width, self.inner, self.experts = width, inner, experts
+
+    def tensor_specs(self):
+        specs = {self.prefix + "router.weight": TensorSpec((self.experts, self.width), "matrix")}
+        for e in range(self.experts):
+            specs[self.prefix + f"e{e}.fc.weight"] = TensorSpec((self.inner, self.width), "matrix")
+            specs[self.prefix + f"e{e}.proj.weight"] = TensorSpec((self.width, self.inner), "matrix",
+                                                                   "residual_proj")
+        return specs
+
+    def forward(self, ctx, y, residual32):
+        choice = (y.float() @ self.router_weight.float().T).argmax(-1)
+        for e in range(self.experts):
+            rows = (choice == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            h = ctx.ops.linear(y[rows].contiguous(), getattr(self, f"e{e}_fc_weight"), None, "gelu_tanh",
+                               ctx.act_dtype)
+            residual32[rows] += ctx.ops.linear(h, getattr(self, f"e{e}_proj_weight"), None, "none",
+                                               torch.float32)
+
+
 @register_position_encoding("toy_sign_flip")
 class SignFlipPositions(PositionEncoding):
     """No table; flips the sign of q and k at odd positions (a stand-in for a rotation)."""
@@ -225,7 +255,9 @@ def describe_toy(cfg: ToyConfig) -> ModelSpec:
                                          "head_dim": 16, "bias": False, "window": 6}, "attn")
     layers = (LayerSpec("l0.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"), ff, norm, norm2),
               LayerSpec("l1.", attn, ff, norm, norm2),
-              LayerSpec("l2.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"), ff, norm, norm2))
+              LayerSpec("l2.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"),
+                        PartSpec("toy_top1_experts", {"width": cfg.width, "inner": 24, "experts": 3}, "moe"),
+                        norm, norm2))
     return ModelSpec(
         architecture="ToyStateLM", width=cfg.width, vocab_size=cfg.vocab_size,
         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": cfg.width}, "emb"),
@@ -250,6 +282,27 @@ def test_toy_mixer_alone_matches_its_formula(ops):
     want = torch.cat([2 * y[:5].cumsum(0) / torch.arange(1, 6, device=DEV)[:, None],
                       2 * y[5:].cumsum(0) / torch.arange(1, 4, device=DEV)[:, None]])
     assert torch.allclose(residual, want, atol=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_routed_feed_forward_alone_matches_its_formula(ops, dtype):
+    part = FEED_FORWARDS.build(PartSpec("toy_top1_experts", {"width": 40, "inner": 56, "experts": 4}, "moe"), "")
+    w = bind_random(part, dtype, 17)
+    ctx = make_ctx(ops, dtype, [9, 14])
+    y = (torch.randn(23, 40, generator=torch.Generator().manual_seed(18)) * 2).to(dtype).to(DEV)
+    residual = torch.zeros(23, 40, device=DEV)
+    part.forward(ctx, y, residual)
+    yd = y.double().cpu()
+    choice = (y.float() @ part.router_weight.float().T).argmax(-1).cpu()     # as the part computes it
+    assert len(set(choice.tolist())) >= 3, "the inputs were meant to reach several experts"
+    want = torch.zeros(23, 40, dtype=torch.float64)
+    for t in range(23):
+        e = int(choice[t])
+        h = plain_gpt.gelu_tanh(yd[t] @ w[f"moe.e{e}.fc.weight"].double().T)
+        if dtype == torch.bfloat16:
+            h = h.to(torch.bfloat16).double()
+        want[t] = h @ w[f"moe.e{e}.proj.weight"].double().T
+    assert rel_err(residual.cpu(), want) <= (1e-5 if dtype == torch.float32 else 2e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
