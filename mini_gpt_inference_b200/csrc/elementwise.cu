@@ -40,16 +40,68 @@ MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void*
 // ---- LayerNorm -----------------------------------------------------------------------------
 // One warp per row.  Mean, then the biased variance of the centred values, then the affine
 // map; all in 32-bit.  y = (x - mean) * rsqrt(var + eps) * gain (+ shift).
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename TOut>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                  const float* __restrict__ shift, TOut* __restrict__ y,
                                  int rows, int width, float eps) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    // widths of up to 1024 in steps of 128: the row lives in registers, one trip to memory
+    const bool fast = width % 128 == 0 && width <= 1024 &&
+                      (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)shift | (uintptr_t)y) & 15) == 0;
+    float4 gn[8], sh[8];
+    if (fast) {                                        // gain and shift are weights: fetched before the wait
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < width / 128) {
+                gn[i] = *reinterpret_cast<const float4*>(gain + (lane + 32 * i) * 4);
+                sh[i] = shift ? *reinterpret_cast<const float4*>(shift + (lane + 32 * i) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+    }
     pdl_trigger();
     pdl_wait();                                        // x comes from the kernel in front
     if (row >= rows) return;
     const float* xr = x + (size_t)row * width;
+    TOut* yr = y + (size_t)row * width;
+    if (fast) {
+        float4 v[8];
+        const int n4 = width / 128;
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < n4) {
+                v[i] = *reinterpret_cast<const float4*>(xr + (lane + 32 * i) * 4);
+                sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            }
+        const float mean = warp_sum(sum) / (float)width;
+        float sq = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < n4) {
+                const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+                sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+            }
+        const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            if (i < n4) {
+                const int c = (lane + 32 * i) * 4;
+                store4(yr + c, (v[i].x - mean) * rstd * gn[i].x + sh[i].x, (v[i].y - mean) * rstd * gn[i].y + sh[i].y,
+                       (v[i].z - mean) * rstd * gn[i].z + sh[i].z, (v[i].w - mean) * rstd * gn[i].w + sh[i].w);
+            }
+        return;
+    }
     float sum = 0.f;
     for (int c = lane; c < width; c += 32) sum += xr[c];
     const float mean = warp_sum(sum) / (float)width;
@@ -59,7 +111,6 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
         sq += d * d;
     }
     const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
-    TOut* yr = y + (size_t)row * width;
     for (int c = lane; c < width; c += 32) {
         float v = (xr[c] - mean) * rstd * gain[c];
         if (shift) v += shift[c];
