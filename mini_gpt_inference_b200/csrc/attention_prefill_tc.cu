@@ -204,23 +204,34 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     float run_max = -INFINITY, run_sum = 0.f;
     bool good = true;
 
+    // S = Q K^T of one key block (thread 0 only): waits for the block's keys, issues, commits.
+    auto issue_scores = [&](int it) {
+        const int stage = it & 1;
+        bool ok = true;
+        if (it == 0) ok = mbar_wait(smem_u32(&sync->q_full), 0);
+        ok = ok && mbar_wait(smem_u32(&sync->k_full[stage]), (it >> 1) & 1);
+        if (!ok) { atomicExch(status, 21); sync->failed = 1; }
+        tc_fence_after();
+        constexpr uint32_t idesc_s = instr_desc(BQ, BK, false);
+        const uint64_t dq = smem_desc_sw128(smem_u32(q_tile));
+        const uint64_t dk = smem_desc_sw128(smem_u32(k_tiles + stage * KV_BYTES));
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+            umma_bf16(tmem_base, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
+        umma_commit(smem_u32(&sync->s_done));
+    };
+    if (tid == 0 && first_blk <= last_blk) {
+        if (first_blk + 1 <= last_blk) load_tiles(first_blk + 1, false, 1);   // keys one block ahead
+        issue_scores(0);
+    }
+
     for (int blk = first_blk, it = 0; blk <= last_blk; ++blk, ++it) {
         const int stage = it & 1;
-        if (tid == 0) {
+        // The scores of this block were asked for together with the product of the block before
+        // (below), so the tensor core computes them while the threads finish that block.
+        if (tid == 0 && it > 0) {
             if (blk + 1 <= last_blk) load_tiles(blk + 1, false, stage ^ 1);   // keys one block ahead
-            if (it > 0) load_tiles(blk, true, 0);           // values: the tile is free since the last product
-            bool ok = true;
-            if (it == 0) ok = mbar_wait(smem_u32(&sync->q_full), 0);
-            ok = ok && mbar_wait(smem_u32(&sync->k_full[stage]), (it >> 1) & 1);
-            if (!ok) { atomicExch(status, 21); sync->failed = 1; }
-            tc_fence_after();
-            constexpr uint32_t idesc_s = instr_desc(BQ, BK, false);
-            const uint64_t dq = smem_desc_sw128(smem_u32(q_tile));
-            const uint64_t dk = smem_desc_sw128(smem_u32(k_tiles + stage * KV_BYTES));
-#pragma unroll
-            for (int k = 0; k < D / 16; ++k)
-                umma_bf16(tmem_base, dq + (uint64_t)(k * 2), dk + (uint64_t)(k * 2), idesc_s, k ? 1u : 0u);
-            umma_commit(smem_u32(&sync->s_done));
+            load_tiles(blk, true, 0);                       // values: the tile is free since the last product
         }
         __syncwarp();
         if (!mbar_wait(smem_u32(&sync->s_done), it & 1)) { good = false; atomicExch(status, 22); }
@@ -233,8 +244,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // Blocks that lie wholly before the first query of the tile (and inside every window)
         // need no mask: the common case takes the short path.
         const bool unmasked = (key0 + BK - 1 <= pos0) && (window <= 0 || key0 >= pos0 + BQ - window);
-        float blk_max = -INFINITY;
-        // first pass over the row of S: the block's maximum
+        // first pass over the row of S: the block's maximum (four chains, so that a maximum does
+        // not wait for the one before it)
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int c = 0; c < BK / 32; ++c) {
             uint32_t r[32];
@@ -242,22 +254,23 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             tmem_wait_ld();
             if (unmasked) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) blk_max = fmaxf(blk_max, __uint_as_float(r[j]));
+                for (int j = 0; j < 32; ++j) mx[j & 3] = fmaxf(mx[j & 3], __uint_as_float(r[j]));
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int col = c * 32 + j;
                     const bool visible = col <= hi && col >= lo_col;
-                    blk_max = fmaxf(blk_max, visible ? __uint_as_float(r[j]) : -INFINITY);
+                    mx[j & 3] = fmaxf(mx[j & 3], visible ? __uint_as_float(r[j]) : -INFINITY);
                 }
             }
         }
+        float blk_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
         blk_max *= scale_log2e;                                            // scale > 0: max commutes
         const float new_max = fmaxf(run_max, blk_max);
         const bool none = new_max == -INFINITY;                            // no visible key so far
         const float corr = none ? 1.f : exp2f(run_max - new_max);
         const float shift = none ? 0.f : new_max;
-        float blk_sum = 0.f;
+        float part_sum[4] = {0.f, 0.f, 0.f, 0.f};                          // one per 16-byte chunk of a load
         uint8_t* p_row = p_tile + (tid >> 3) * 1024 + (tid & 7) * 128;
         // second pass: P = 2^(s - max) as bfloat16 into the swizzled tile, 8 keys per 16-byte chunk
 #pragma unroll
@@ -283,7 +296,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const float p0 = pv[g * 8 + 2 * j], p1 = pv[g * 8 + 2 * j + 1];
-                    blk_sum += p0 + p1;                                    // the sum stays in 32-bit
+                    part_sum[j] += p0 + p1;                                // the sum stays in 32-bit
                     const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&h);
                 }
@@ -293,6 +306,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
         }
+        const float blk_sum = (part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]);
         run_sum = run_sum * corr + blk_sum;
         run_max = new_max;
         // Rows of the value tile past the last key of this work item hold whatever the page held
@@ -323,6 +337,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 umma_bf16(tmem_base + O_COL, dp, dv, idesc_pv, k ? 1u : 0u);
             }
             umma_commit(smem_u32(&sync->pv_done));
+            // everybody has read S (the barrier above): the next block's scores may overwrite it
+            if (blk + 1 <= last_blk) issue_scores(it + 1);
         }
         __syncwarp();
         if (!mbar_wait(smem_u32(&sync->pv_done), it & 1)) { good = false; atomicExch(status, 24); }

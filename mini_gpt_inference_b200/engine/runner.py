@@ -97,6 +97,12 @@ class ModelRunner:
         if self.max_context is None:
             self.max_context = manager.num_pages * manager.page_tokens
         self.max_pages = manager.max_pages_per_request(self.max_context)
+        # work items of the tiled attention kernel that run at once, per head (two CTAs per SM)
+        heads = max((getattr(layer.mixer, "n_head", 0) for layer in getattr(model, "layers", [])), default=0)
+        self._attention_slots = None
+        if self.device.type == "cuda" and heads:
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            self._attention_slots = max(1, 2 * sms // heads)
         self._pinned = None
         self._pinned_size = 0
         self.last_h2d_bytes = 0          # bytes of the last step's one host-to-device copy
@@ -194,7 +200,7 @@ class ModelRunner:
         host_q_len = [len(e.tokens) for e in entries]
         host_ctx = [m.get(e.request_id).length for e in entries]
         # work items of the tiled attention kernels (runs of queries x chunks of keys)
-        work = query_tiles(host_q_len, host_ctx)
+        work = query_tiles(host_q_len, host_ctx, self._attention_slots)
         # layout of the packed int32 buffer
         sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [5 * len(work)]
         offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)

@@ -51,21 +51,37 @@ QUERY_TILE = 128       # most consecutive tokens of one request in a tile
 KEY_CHUNK = 512        # most key positions one work item walks over
 
 
-def query_tiles(q_lens, ctx_befores):
+def query_tiles(q_lens, ctx_befores, slots=None):
     """Cut a ragged batch into work items ``(request, first row, rows, chunk, chunks)``.
 
     The tokens of each request are cut into runs of at most QUERY_TILE rows.  The keys a run
     may see (positions 0 .. its last token) are cut into ``chunks`` parts of at most KEY_CHUNK
     positions, one work item each, so that a long context is spread over several CTAs; their
-    partial results are merged afterwards.  Items of one run are consecutive, chunk 0 first."""
-    items = []
-    row = 0
-    for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
-        for b in range(0, n, QUERY_TILE):
-            rows = min(QUERY_TILE, n - b)
-            keys = before + b + rows
-            chunks = max(1, -(-keys // KEY_CHUNK))
-            for c in range(chunks):
-                items.append((r, row + b, rows, c, chunks))
-        row += n
+    partial results are merged afterwards.  Items of one run are consecutive, chunk 0 first; the
+    runs come longest item first, so that when the grid does not fit the GPU at once, the CTAs
+    that start last are the short ones.
+
+    ``slots``: how many work items the GPU runs at once (per head).  If the items exceed it by
+    less than half, longer parts (up to twice KEY_CHUNK) are tried, so that a second round of a
+    few CTAs is not added to the first."""
+
+    def cut(limit):
+        runs = []
+        row = 0
+        for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
+            for b in range(0, n, QUERY_TILE):
+                rows = min(QUERY_TILE, n - b)
+                keys = before + b + rows
+                chunks = max(1, -(-keys // limit))
+                runs.append((-(keys / chunks), len(runs), r, row + b, rows, chunks))
+            row += n
+        runs.sort()
+        return [(r, row0, rows, c, chunks) for _, _, r, row0, rows, chunks in runs for c in range(chunks)]
+
+    items = cut(KEY_CHUNK)
+    if slots and slots < len(items) <= slots + slots // 2:
+        for limit in range(KEY_CHUNK + QUERY_TILE, 2 * KEY_CHUNK + 1, QUERY_TILE):
+            longer = cut(limit)
+            if len(longer) <= slots:
+                return longer
     return items
