@@ -3,7 +3,7 @@
 // A decoding step reads every key and value of every live request once: it is bound by HBM
 // bandwidth, and a request alone gives too little parallelism.  So the keys of a (token, kv head)
 // are cut into blocks of SPLIT positions, one CTA each; the query heads that share the kv head
-// (up to 16 per CTA) are the rows of one small matrix product, so grouped heads read their keys
+// (up to 16 per CTA) are the columns of one small matrix product, so grouped heads read their keys
 // once.
 //
 // A CTA's four warps each own a quarter of the block's keys from load to result:
@@ -13,12 +13,14 @@
 //           conflict.  Positions, block tables and every cache row but the newest were written
 //           before this step began, so all of this is asked for BEFORE the wait for the kernel in
 //           front (which wrote the query and the newest row); the newest row follows after it.
-//   scores  S = Q K^T on warp-level mma (m16n8k16: the heads are the 16 rows of A, eight keys the
-//           columns of B, read with ldmatrix), scaled by scale * log2 e in 32-bit;
-//   softmax maximum, base-2 exponentials and their sum over the warp's keys, in 32-bit, inside the
-//           accumulator registers (a row lives in four lanes);
-//   values  O = P V, P rounded to bfloat16 straight from the score registers (the accumulator
-//           layout of S is the A layout of the next product), V through ldmatrix.trans.
+//   scores  S[key, head] = K q^T on warp-level mma (m16n8k16: sixteen keys are the rows of A, read
+//           with ldmatrix; up to eight heads the columns of B), scaled by scale * log2 e in 32-bit;
+//   softmax maximum, base-2 exponentials and their sum over the warp's keys, per head, in 32-bit,
+//           inside the accumulator registers (a head's keys live in the eight lanes with equal t);
+//   values  O[dim, head] = V^T P: V through ldmatrix.trans as the A operand, P rounded to bfloat16
+//           and brought from the accumulator layout to the B layout by movmatrix (an 8x8 transpose
+//           inside the warp).  With keys and dims as rows no row of a product is padding, whatever
+//           the number of heads.
 //
 // The four warps' (maximum, sum, O) are combined through shared memory into the block's partial
 // result, written to scratch; the CTA that arrives last at a counter of its (token, kv head)
@@ -70,13 +72,20 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Transpose of an 8x8 block of 16-bit values held one row per group of four lanes.
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
 // partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
-template <int D>
+template <int D, int NT>   // NT: tiles of 8 query heads per CTA (1 or 2)
 __global__ void __launch_bounds__(THREADS)
 attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_pages,
                        const bf16* __restrict__ v_pages, const int* __restrict__ block_table,
@@ -173,110 +182,121 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     asm volatile("cp.async.wait_group 1;" ::: "memory");               // this lane's keys have landed
     __syncwarp();                                                       // the warp's keys, its newest row, its queries
 
-    // ---- scores: S[head, key] = q . k over this warp's KW keys ----
-    float s[KW / 8][4];
+    // ---- scores, keys as rows: S[key, head] = k . q over this warp's KW keys ----
+    // B operand: the queries, head nt * 8 + g in column g (heads past the group are zero columns)
+    uint32_t qb[NT][D / 16][2];
 #pragma unroll
-    for (int nt = 0; nt < KW / 8; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) s[nt][i] = 0.f;
-    {
-        // lane address pattern of ldmatrix.x4: matrix j = lane / 8 holds keys (j / 2) * 8 .., pieces j % 2
-        const int lrow = (lane & 7) + ((lane >> 4) << 3), lpiece = (lane >> 3) & 1;
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-            uint32_t a[4] = {0u, 0u, 0u, 0u};                           // heads past the group are zero rows
-            if (g < nh) {
-                a[0] = *reinterpret_cast<const uint32_t*>(q_tile + g * QSTRIDE + ks * 16 + 2 * t);
-                a[2] = *reinterpret_cast<const uint32_t*>(q_tile + g * QSTRIDE + ks * 16 + 8 + 2 * t);
-            }
-            if (g + 8 < nh) {
-                a[1] = *reinterpret_cast<const uint32_t*>(q_tile + (g + 8) * QSTRIDE + ks * 16 + 2 * t);
-                a[3] = *reinterpret_cast<const uint32_t*>(q_tile + (g + 8) * QSTRIDE + ks * 16 + 8 + 2 * t);
-            }
-#pragma unroll
-            for (int np = 0; np < KW / 16; ++np) {
-                const int r = warp * KW + np * 16 + lrow, c = ks * 2 + lpiece;
-                uint32_t b[4];
-                ldmatrix_x4(b, smem_u32(k_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
-                mma_bf16(s[2 * np], a, b[0], b[1]);
-                mma_bf16(s[2 * np + 1], a, b[2], b[3]);
-            }
+            const int h = nt * 8 + g;
+            qb[nt][ks][0] = h < nh ? *reinterpret_cast<const uint32_t*>(q_tile + h * QSTRIDE + ks * 16 + 2 * t) : 0u;
+            qb[nt][ks][1] = h < nh ? *reinterpret_cast<const uint32_t*>(q_tile + h * QSTRIDE + ks * 16 + 8 + 2 * t) : 0u;
         }
-    }
-    // ---- softmax over the warp's keys; rows g (values 0, 1) and g + 8 (values 2, 3) ----
-    float mx[2] = {-INFINITY, -INFINITY};
+    float s[NT][KW / 16][4];
 #pragma unroll
-    for (int nt = 0; nt < KW / 8; ++nt)
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = warp * KW + nt * 8 + 2 * t + (i & 1);
-            s[nt][i] = r < count ? s[nt][i] * scale_log2e : -INFINITY;
-            mx[i >> 1] = fmaxf(mx[i >> 1], s[nt][i]);
-        }
-    float sum[2] = {0.f, 0.f};
+        for (int mt = 0; mt < KW / 16; ++mt)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-    }
-    uint32_t pa[KW / 16][4];
-#pragma unroll
-    for (int nt = 0; nt < KW / 8; ++nt) {
-        float e[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float m = mx[i >> 1];
-            e[i] = m == -INFINITY ? 0.f : exp2f(s[nt][i] - m);         // a warp past the last key holds nothing
-            sum[i >> 1] += e[i];
-        }
-        // the accumulator layout of S is the A layout of P: n-tile 2k gives a0/a1, n-tile 2k+1 a2/a3
-        pa[nt >> 1][(nt & 1) * 2] = pack_bf16(e[0], e[1]);
-        pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16(e[2], e[3]);
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 1);
-        sum[h] += __shfl_xor_sync(0xffffffffu, sum[h], 2);
-    }
-
-    // ---- values: O[head, dim] = sum of p * v, once this warp's value rows have landed ----
-    asm volatile("cp.async.wait_group 0;" ::: "memory");
-    __syncwarp();
-    float o[D / 8][4];
-#pragma unroll
-    for (int nt = 0; nt < D / 8; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+            for (int i = 0; i < 4; ++i) s[nt][mt][i] = 0.f;
     {
-        // ldmatrix.x4.trans: matrix j holds keys (j % 2) * 8 .., piece j / 2 of the pair of n-tiles
+        // A operand by ldmatrix.x4: matrix j = lane / 8 holds keys (j % 2) * 8 .., piece j / 2
         const int lrow = (lane & 7) + (((lane >> 3) & 1) << 3), lpiece = lane >> 4;
 #pragma unroll
-        for (int kk = 0; kk < KW / 16; ++kk) {
+        for (int mt = 0; mt < KW / 16; ++mt)
 #pragma unroll
-            for (int dp = 0; dp < D / 16; ++dp) {
-                const int r = warp * KW + kk * 16 + lrow, c = dp * 2 + lpiece;
-                uint32_t b[4];
-                ldmatrix_x4_trans(b, smem_u32(v_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
-                mma_bf16(o[2 * dp], pa[kk], b[0], b[1]);
-                mma_bf16(o[2 * dp + 1], pa[kk], b[2], b[3]);
+            for (int ks = 0; ks < D / 16; ++ks) {
+                const int r = warp * KW + mt * 16 + lrow, c = ks * 2 + lpiece;
+                uint32_t a[4];
+                ldmatrix_x4(a, smem_u32(k_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_bf16(s[nt][mt], a, qb[nt][ks][0], qb[nt][ks][1]);
             }
+    }
+    // ---- softmax over the warp's keys, per head: a lane holds heads 2t, 2t+1 (values 0, 1 and
+    // 2, 3) of keys g and g + 8 of every 16; the other keys of a head are in the lanes with the same t
+    float mx[NT][2], sum[NT][2];
+    uint32_t pb[NT][KW / 16][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+        mx[nt][0] = mx[nt][1] = -INFINITY;
+#pragma unroll
+        for (int mt = 0; mt < KW / 16; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = warp * KW + mt * 16 + g + ((i >> 1) << 3);
+                s[nt][mt][i] = r < count ? s[nt][mt][i] * scale_log2e : -INFINITY;
+                mx[nt][i & 1] = fmaxf(mx[nt][i & 1], s[nt][mt][i]);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) mx[nt][i] = fmaxf(mx[nt][i], __shfl_xor_sync(0xffffffffu, mx[nt][i], o));
+        sum[nt][0] = sum[nt][1] = 0.f;
+#pragma unroll
+        for (int mt = 0; mt < KW / 16; ++mt) {
+            float e[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float m = mx[nt][i & 1];
+                e[i] = m == -INFINITY ? 0.f : exp2f(s[nt][mt][i] - m);  // a warp past the last key holds nothing
+                sum[nt][i & 1] += e[i];
+            }
+            // P[key, head] as the B operand of the next product needs keys along k: the 8x8 blocks
+            // (keys g, heads 2t..) are transposed inside the warp
+            pb[nt][mt][0] = movmatrix_trans(pack_bf16(e[0], e[1]));
+            pb[nt][mt][1] = movmatrix_trans(pack_bf16(e[2], e[3]));
         }
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) sum[nt][i] += __shfl_xor_sync(0xffffffffu, sum[nt][i], o);
+    }
+
+    // ---- values, dims as rows: O[dim, head] = sum over keys of v[key, dim] * p[key, head] ----
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncwarp();
+    float o[NT][D / 16][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int dm = 0; dm < D / 16; ++dm)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[nt][dm][i] = 0.f;
+    {
+        // A operand by ldmatrix.x4.trans: matrix j holds keys (j / 2) * 8 .., piece j % 2
+        const int lrow = (lane & 7) + (((lane >> 4) & 1) << 3), lpiece = (lane >> 3) & 1;
+#pragma unroll
+        for (int kk = 0; kk < KW / 16; ++kk)
+#pragma unroll
+            for (int dm = 0; dm < D / 16; ++dm) {
+                const int r = warp * KW + kk * 16 + lrow, c = dm * 2 + lpiece;
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, smem_u32(v_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][dm], a, pb[nt][kk][0], pb[nt][kk][1]);
+            }
     }
     // ---- the four warps' results meet in shared memory ----
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int row = g + 8 * h;
-        if (row < nh) {
-            float* dst = wpart + ((size_t)warp * nh + row) * OSTRIDE;
+    for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int nt = 0; nt < D / 8; ++nt)
-                *reinterpret_cast<float2*>(dst + nt * 8 + 2 * t) = make_float2(o[nt][2 * h], o[nt][2 * h + 1]);
-            if (t == 0) {
-                dst[D] = mx[h];
-                dst[D + 1] = sum[h];
+        for (int i = 0; i < 2; ++i) {
+            const int row = nt * 8 + 2 * t + i;
+            if (row < nh) {
+                float* dst = wpart + ((size_t)warp * nh + row) * OSTRIDE;
+#pragma unroll
+                for (int dm = 0; dm < D / 16; ++dm) {
+                    dst[dm * 16 + g] = o[nt][dm][i];
+                    dst[dm * 16 + g + 8] = o[nt][dm][i + 2];
+                }
+                if (g == 0) {
+                    dst[D] = mx[nt][i];
+                    dst[D + 1] = sum[nt][i];
+                }
             }
         }
-    }
     __syncthreads();
     const size_t pair0 = (size_t)token * n_head + h0;
     for (int e = tid; e < nh * D; e += THREADS) {
@@ -367,15 +387,22 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
                         (size_t)split_keys(D) * sizeof(int) + (size_t)WARPS * nh_max * (D + 2) * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(attention_split_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention (split): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     dim3 grid(n_tokens, n_kv_head * head_tiles, max_splits);
-    cudaError_t le = mg_launch(attention_split_kernel<D>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
-                               (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-                               (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                               window, max_splits, scale * 1.4426950408889634f, head_tiles);
+    const cudaError_t le =
+        nh_max <= 8 ? mg_launch(attention_split_kernel<D, 1>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
+                                (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
+                                (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
+                                window, max_splits, scale * 1.4426950408889634f, head_tiles)
+                    : mg_launch(attention_split_kernel<D, 2>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
+                                (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
+                                (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
+                                window, max_splits, scale * 1.4426950408889634f, head_tiles);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     return MG_OK;
