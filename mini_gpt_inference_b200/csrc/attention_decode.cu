@@ -84,6 +84,66 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
+// One warp merges the key blocks of one (token, head): the weights of the blocks go to `weights`
+// (shared memory, room for `cap` of them; blocks beyond are weighed again when used), then each
+// lane adds up its dims over the blocks in order, eight loads in flight.
+template <int D>
+__device__ __forceinline__ void merge_row(const float* __restrict__ part_out, const float* __restrict__ part_ml,
+                                          size_t base, int splits, float* weights, int cap, bf16* __restrict__ out_row,
+                                          int lane) {
+    float M = -INFINITY;
+    for (int sidx = lane; sidx < splits; sidx += 32) M = fmaxf(M, __ldcg(&part_ml[(base + sidx) * 2]));
+    M = warp_max(M);
+    float denom = 0.f;
+    for (int sidx = lane; sidx < splits; sidx += 32) {
+        const float w = exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
+        if (sidx < cap) weights[sidx] = w;
+        denom += w * __ldcg(&part_ml[(base + sidx) * 2 + 1]);
+    }
+    denom = warp_sum(denom);
+    __syncwarp();
+    const float inv = 1.0f / denom;
+    for (int d = lane; d < D; d += 32) {
+        float v = 0.f;
+        for (int s0 = 0; s0 < splits; s0 += 8) {
+            float x[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; ++u)
+                if (s0 + u < splits) {
+                    const int sidx = s0 + u;
+                    const float w = sidx < cap ? weights[sidx] : exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
+                    v = fmaf(w, x[u], v);
+                }
+        }
+        out_row[d] = __float2bfloat16_rn(v * inv);
+    }
+    __syncwarp();
+}
+
+// The merge as a kernel of its own, for grids of many waves: the attention CTAs then leave as soon
+// as their partial rows are written, instead of each waiting for the old value of a counter.
+template <int D>
+__global__ void __launch_bounds__(THREADS)
+attention_merge_kernel(const int* __restrict__ positions, const float* __restrict__ part_out,
+                       const float* __restrict__ part_ml, bf16* __restrict__ out, int n_head, int window,
+                       int max_splits) {
+    constexpr int SPLIT = split_keys(D);
+    __shared__ float weights[WARPS][256];
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * WARPS + warp;
+    const int p = positions[token];
+    pdl_trigger();
+    pdl_wait();                                                        // the partial rows come from the kernel in front
+    if (p < 0 || head >= n_head) return;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int splits = (p - lo) / SPLIT + 1;
+    if (splits == 1) return;                                            // the attention kernel wrote the row itself
+    const size_t pair = (size_t)token * n_head + head;
+    merge_row<D>(part_out, part_ml, pair * max_splits, splits, weights[warp], 256, out + pair * D, lane);
+}
+
 // partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
 template <int D, int NT>   // NT: tiles of 8 query heads per CTA (1 or 2)
 __global__ void __launch_bounds__(THREADS)
@@ -92,7 +152,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
                        const int* __restrict__ token_request, const int* __restrict__ positions,
                        bf16* __restrict__ out, float* __restrict__ part_out, float* __restrict__ part_ml,
                        int* __restrict__ counters, int n_head, int n_kv_head, int page_tokens, int max_pages,
-                       int window, int max_splits, float scale_log2e, int head_tiles) {
+                       int window, int max_splits, float scale_log2e, int head_tiles, int merge_inside) {
     constexpr int SPLIT = split_keys(D);
     constexpr int KW = SPLIT / WARPS;          // keys per warp
     constexpr int CPR = D / 8;                 // 16-byte pieces per row
@@ -119,7 +179,8 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     pdl_trigger();
-    const int p = positions[token];
+    const int request = token_request[token];                          // asked for together with the position:
+    const int p = positions[token];                                    // one trip to memory, not two
     if (p < 0) {                                                        // padding row of a fixed-size batch
         pdl_wait();                                                     // `out` may still be in use before
         if (split == 0)
@@ -132,7 +193,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     if (start > p) return;                                              // this block holds no key of the token
     const int count = min(SPLIT, p + 1 - start);
     const int splits = (p - lo) / SPLIT + 1;
-    const int* table = block_table + (size_t)token_request[token] * max_pages;
+    const int* table = block_table + (size_t)request * max_pages;
     const bool holds_newest = start + count - 1 == p;
     const int old_count = holds_newest ? count - 1 : count;            // rows [0, old_count) are old
 
@@ -323,7 +384,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
             }
         }
     }
-    if (splits == 1) return;
+    if (splits == 1 || !merge_inside) return;
     // ---- the CTA that finishes last merges the blocks of this (token, kv head) ----
     // The barrier orders every thread's partial writes before thread 0's release on the counter;
     // the CTA that reads the final count acquires, so it sees the partial rows of all blocks.
@@ -337,42 +398,11 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     }
     __syncthreads();
     if (!is_last) return;
-    // A warp per head: weights of the blocks into shared memory (the key tile is free now), then
-    // each lane adds up its dims over the blocks in order, eight loads in flight.
+    // A warp per head; the weights of the blocks go to shared memory (the key tile is free now).
     constexpr int WCAP = KW * ROWB / 4;
     float* weights = reinterpret_cast<float*>(k_tile) + warp * WCAP;
-    for (int row = warp; row < nh; row += WARPS) {
-        const size_t base = (pair0 + row) * max_splits;
-        float M = -INFINITY;
-        for (int sidx = lane; sidx < splits; sidx += 32) M = fmaxf(M, __ldcg(&part_ml[(base + sidx) * 2]));
-        M = warp_max(M);
-        float denom = 0.f;
-        for (int sidx = lane; sidx < splits; sidx += 32) {
-            const float w = exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
-            if (sidx < WCAP) weights[sidx] = w;
-            denom += w * __ldcg(&part_ml[(base + sidx) * 2 + 1]);
-        }
-        denom = warp_sum(denom);
-        __syncwarp();
-        const float inv = 1.0f / denom;
-        for (int d = lane; d < D; d += 32) {
-            float v = 0.f;
-            for (int s0 = 0; s0 < splits; s0 += 8) {
-                float x[8];
-#pragma unroll
-                for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
-#pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    if (s0 + u < splits) {
-                        const int sidx = s0 + u;
-                        const float w = sidx < WCAP ? weights[sidx] : exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
-                        v = fmaf(w, x[u], v);
-                    }
-            }
-            out[(pair0 + row) * D + d] = __float2bfloat16_rn(v * inv);
-        }
-        __syncwarp();
-    }
+    for (int row = warp; row < nh; row += WARPS)
+        merge_row<D>(part_out, part_ml, (pair0 + row) * max_splits, splits, weights, WCAP, out + (pair0 + row) * D, lane);
 }
 
 template <int D>
@@ -394,17 +424,28 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
         configured = true;
     }
     dim3 grid(n_tokens, n_kv_head * head_tiles, max_splits);
-    const cudaError_t le =
+    // A grid of several waves (six CTAs fit an SM) merges in a second kernel, so that its CTAs do
+    // not hold their shared memory while a counter answers; a small grid merges inside, which
+    // saves a launch.
+    const long long ctas = (long long)n_tokens * n_kv_head * head_tiles * max_splits;
+    const int merge_inside = (max_splits == 1 || ctas <= 1536) ? 1 : 0;
+    cudaError_t le =
         nh_max <= 8 ? mg_launch(attention_split_kernel<D, 1>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
                                 (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
                                 (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                                window, max_splits, scale * 1.4426950408889634f, head_tiles)
+                                window, max_splits, scale * 1.4426950408889634f, head_tiles, merge_inside)
                     : mg_launch(attention_split_kernel<D, 2>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
                                 (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
                                 (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                                window, max_splits, scale * 1.4426950408889634f, head_tiles);
+                                window, max_splits, scale * 1.4426950408889634f, head_tiles, merge_inside);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
+    if (!merge_inside) {
+        le = mg_launch(attention_merge_kernel<D>, dim3(n_tokens, (n_head + WARPS - 1) / WARPS), dim3(THREADS), 0, s, true,
+                       positions, (const float*)part_out, (const float*)part_ml, (bf16*)out, n_head, window, max_splits);
+        if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_merge: %s", cudaGetErrorString(le));
+        MG_CHECK_LAUNCH("attention_merge");
+    }
     return MG_OK;
 }
 

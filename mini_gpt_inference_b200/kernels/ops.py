@@ -310,6 +310,9 @@ class CudaOps:
                 _ptr(self._counters(n * n_head)), n, n_head, n_kv_head, head_dim, cache.page_tokens,
                 table.shape[1], window, splits, float(scale), _ptr(self.status), self._stream()),
                 "paged_attention (split)")
+            group = n_head // n_kv_head
+            if splits > 1 and n * n_kv_head * ((group + 15) // 16) * splits > 1536:
+                self.launches += 1         # a grid of several waves merges in a kernel of its own
             return out
         work = getattr(ctx, "attn_work", None)
         if (qkv.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0
