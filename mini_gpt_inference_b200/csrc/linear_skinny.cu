@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     const int xstride = K * 2 + XPAD;                                         // bytes per token row
     uint8_t* xs = smem_raw;                                                   // [MT][K] bf16, padded rows
     float* partial = reinterpret_cast<float*>(smem_raw + (size_t)MT * xstride);   // [WARPS][MT][8]
+    float* gain_s = partial + WARPS * MT * TILE_N;                                // [K] and [K]: LayerNorm gain and shift
+    float* shift_s = gain_s + K;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -93,9 +95,20 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         const int n = (first_tile + ti) * TILE_N + r;
         if (a.ep.bias && ti < tiles_per_round && ti < a.tiles_per_cta && n < a.N) first_bias = a.ep.bias[n];
     }
+    // Gain and shift of the LayerNorm prologue are weights too: they go to shared memory now, so
+    // that the normalisation does not wait for them after the statistics.
+    const bool ln_fast = a.x32 != nullptr && K % 128 == 0 && K <= 1024;
+    if (ln_fast) {
+        for (int i = tid; i < K / 4; i += THREADS) {
+            reinterpret_cast<float4*>(gain_s)[i] = reinterpret_cast<const float4*>(a.gain)[i];
+            reinterpret_cast<float4*>(shift_s)[i] =
+                a.shift ? reinterpret_cast<const float4*>(a.shift)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     // Weights and bias do not depend on the kernel before this one; everything below does.
     pdl_trigger();
     pdl_wait();
+    if (ln_fast) __syncthreads();
 
     // ---- stage the activations (with the LayerNorm prologue if asked) as bfloat16 ----
     // Rows at and past M stay as they are: a token's results depend on its own row only.
@@ -103,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         for (int m = warp; m < a.M; m += WARPS) {
             uint8_t* dst = xs + (size_t)m * xstride;
             const float* src = a.x32 + (size_t)(a.row_index ? a.row_index[m] : m) * K;
-            if (K % 128 == 0 && K <= 1024) {
+            if (ln_fast) {
                 // the row lives in registers between the passes: 16-byte loads, one trip to memory
                 float4 v[8];
                 const int n4 = K / 128;
@@ -127,9 +140,8 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
                 for (int i = 0; i < 8; ++i)
                     if (i < n4) {
                         const int c = (lane + 32 * i) * 4;
-                        const float4 gn = *reinterpret_cast<const float4*>(a.gain + c);
-                        float4 sh = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (a.shift) sh = *reinterpret_cast<const float4*>(a.shift + c);
+                        const float4 gn = *reinterpret_cast<const float4*>(gain_s + c);
+                        const float4 sh = *reinterpret_cast<const float4*>(shift_s + c);
                         uint2 y;
                         y.x = pack_bf16((v[i].x - mean) * rstd * gn.x + sh.x, (v[i].y - mean) * rstd * gn.y + sh.y);
                         y.y = pack_bf16((v[i].z - mean) * rstd * gn.z + sh.z, (v[i].w - mean) * rstd * gn.w + sh.w);
@@ -231,7 +243,7 @@ MG_API int mg_linear_skinny_max_rows() { return MAX_M; }
 
 // Shared memory the kernel needs for M tokens of width K (the caller checks it against the limit).
 static size_t skinny_smem(int mt, int K) {
-    return (size_t)mt * ((size_t)K * 2 + XPAD) + (size_t)WARPS * mt * TILE_N * sizeof(float);
+    return (size_t)mt * ((size_t)K * 2 + XPAD) + (size_t)WARPS * mt * TILE_N * sizeof(float) + (size_t)2 * K * sizeof(float);
 }
 
 // x: [M, K] bf16 (or null when x32 is given: then rows row_index[m] (or m) of x32 [*, K] are

@@ -188,7 +188,7 @@ class CudaOps:
 
     def _skinny_ok(self, m, k, dtype) -> bool:
         return (self.use_skinny and dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0
-                and SKINNY_ROWS * (2 * k + 64) + 8 * SKINNY_ROWS * 8 * 4 <= 200 * 1024)
+                and SKINNY_ROWS * (2 * k + 64) + 8 * SKINNY_ROWS * 8 * 4 + 8 * k <= 200 * 1024)
 
     def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None):
         """x: a tensor [M, K] or a DeferredNorm.  kv_sink: (cache view, slots, n_head, n_kv_head,
