@@ -91,6 +91,36 @@ template <int D>
 __device__ __forceinline__ void merge_row(const float* __restrict__ part_out, const float* __restrict__ part_ml,
                                           size_t base, int splits, float* weights, int cap, bf16* __restrict__ out_row,
                                           int lane) {
+    if constexpr (D >= 32 && D <= 128) {
+        if (splits <= 16) {
+            // Few blocks: maxima, sums and every partial value this lane needs are asked for at
+            // once (one trip to memory instead of two); lane s holds the weight of block s.
+            constexpr int DPL = D / 32;
+            const float2 ml = lane < splits ? __ldcg(reinterpret_cast<const float2*>(part_ml) + base + lane)
+                                            : make_float2(-INFINITY, 0.f);
+            float x[16][DPL];
+#pragma unroll
+            for (int sidx = 0; sidx < 16; ++sidx)
+#pragma unroll
+                for (int j = 0; j < DPL; ++j)
+                    x[sidx][j] = sidx < splits ? __ldcg(&part_out[(base + sidx) * D + lane + 32 * j]) : 0.f;
+            const float M = warp_max(ml.x);
+            const float w = lane < splits ? exp2f(ml.x - M) : 0.f;
+            const float inv = 1.0f / warp_sum(w * ml.y);
+            float v[DPL];
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) v[j] = 0.f;
+#pragma unroll
+            for (int sidx = 0; sidx < 16; ++sidx) {                       // blocks in order
+                const float ws = __shfl_sync(0xffffffffu, w, sidx);
+#pragma unroll
+                for (int j = 0; j < DPL; ++j) v[j] = fmaf(ws, x[sidx][j], v[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) out_row[lane + 32 * j] = __float2bfloat16_rn(v[j] * inv);
+            return;
+        }
+    }
     float M = -INFINITY;
     for (int sidx = lane; sidx < splits; sidx += 32) M = fmaxf(M, __ldcg(&part_ml[(base + sidx) * 2]));
     M = warp_max(M);

@@ -4,17 +4,25 @@
 // ---- embedding + learned position add ---------------------------------------------------
 // x[n, :] = tok_emb[id[n], :] + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
 // A row with a negative position is padding of a fixed-size batch: it becomes zeros.
+// With `source` given, a row whose source[n] >= 0 takes its id from previous[source[n]] (the token
+// the step before sampled, still on the device) instead of ids[n].
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ tok, const TW* __restrict__ ptab,
-                             float* __restrict__ out, int width) {
+                             float* __restrict__ out, int width, const int* __restrict__ source,
+                             const int* __restrict__ previous) {
     const int n = blockIdx.x;
     float* orow = out + (size_t)n * width;
     if (pos[n] < 0) {
         for (int c = threadIdx.x; c < width; c += blockDim.x) orow[c] = 0.f;
         return;
     }
-    const TW* trow = tok + (size_t)ids[n] * width;
+    int id = ids[n];
+    if (source != nullptr) {
+        const int src = source[n];
+        if (src >= 0) id = previous[src];
+    }
+    const TW* trow = tok + (size_t)id * width;
     const TW* prow = ptab ? ptab + (size_t)pos[n] * width : nullptr;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = to_float(trow[c]);
@@ -24,15 +32,18 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
 }
 
 MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void* ptab, float* out,
-                    int n_tokens, int width, int weights_bf16, void* stream) {
+                    int n_tokens, int width, int weights_bf16, const int* source, const int* previous, void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && width > 0, "embed: bad sizes");
+    MG_REQUIRE(source == nullptr || previous != nullptr, "embed: token sources without the ids they point to");
     cudaStream_t s = (cudaStream_t)stream;
     int threads = width >= 256 ? 256 : 128;
     if (weights_bf16)
-        embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, pos, (const bf16*)tok, (const bf16*)ptab, out, width);
+        embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, pos, (const bf16*)tok, (const bf16*)ptab, out, width, source,
+                                                       previous);
     else
-        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)tok, (const float*)ptab, out, width);
+        embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)tok, (const float*)ptab, out, width,
+                                                        source, previous);
     MG_CHECK_LAUNCH("embed");
     return MG_OK;
 }

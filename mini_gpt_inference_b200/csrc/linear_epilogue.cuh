@@ -21,8 +21,10 @@ struct LinearEpilogue {
     int q_width, n_kv_head, head_dim, page_tokens;
 };
 
-// v: the sum with its bias.  `res` is the residual value if the caller fetched it already.
-__device__ __forceinline__ void linear_finish(const LinearEpilogue& e, int m, int n, float v, bool have_res, float res) {
+// v: the sum with its bias.  `res` is the residual value if the caller fetched it already, `slot`
+// the token's cache row if it did (pass have_slot = false to have it read here).
+__device__ __forceinline__ void linear_finish(const LinearEpilogue& e, int m, int n, float v, bool have_res, float res,
+                                              bool have_slot = false, int slot_in = -1) {
     if (e.epilogue == EPI_GELU) v = gelu_tanh(v);
     const size_t idx = (size_t)m * e.N + n;
     if (e.epilogue == EPI_RESIDUAL) {
@@ -31,7 +33,7 @@ __device__ __forceinline__ void linear_finish(const LinearEpilogue& e, int m, in
         const bf16 hv = __float2bfloat16_rn(v);
         reinterpret_cast<bf16*>(e.out)[idx] = hv;
         if (e.k_pages != nullptr && n >= e.q_width) {
-            const int slot = e.slots[m];
+            const int slot = have_slot ? slot_in : e.slots[m];
             if (slot >= 0) {
                 const int kv_width = e.n_kv_head * e.head_dim;
                 const int f = n - e.q_width;

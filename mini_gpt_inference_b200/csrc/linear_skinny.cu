@@ -88,13 +88,20 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             first_w[i] = (live && b_begin + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow + k) : zero4;
         }
     }
-    // The bias of the first result of this thread as well, so that the epilogue does not wait for it.
+    // The bias of the first result of this thread as well, so that the epilogue does not wait for it;
+    // and, for the QKV projection, the cache row of its token (an input of the step, not a result).
     float first_bias = 0.f;
+    int first_slot = -1;
     {
         const int ti = tid / (MT * TILE_N), r = tid % TILE_N;
         const int n = (first_tile + ti) * TILE_N + r;
         if (a.ep.bias && ti < tiles_per_round && ti < a.tiles_per_cta && n < a.N) first_bias = a.ep.bias[n];
+        const int m = (tid % (MT * TILE_N)) / TILE_N;
+        if (a.ep.k_pages != nullptr && m < a.M) first_slot = a.ep.slots[m];
     }
+    // Which rows to normalise is an input of the step as well.
+    int first_row = warp;
+    if (a.x32 != nullptr && a.row_index != nullptr && warp < a.M) first_row = a.row_index[warp];
     // Gain and shift of the LayerNorm prologue are weights too: they go to shared memory now, so
     // that the normalisation does not wait for them after the statistics.
     const bool ln_fast = a.x32 != nullptr && K % 128 == 0 && K <= 1024;
@@ -115,7 +122,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     if (a.x32 != nullptr) {
         for (int m = warp; m < a.M; m += WARPS) {
             uint8_t* dst = xs + (size_t)m * xstride;
-            const float* src = a.x32 + (size_t)(a.row_index ? a.row_index[m] : m) * K;
+            const float* src = a.x32 + (size_t)(a.row_index ? (m == warp ? first_row : a.row_index[m]) : m) * K;
             if (ln_fast) {
                 // the row lives in registers between the passes: 16-byte loads, one trip to memory
                 float4 v[8];
@@ -230,7 +237,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             float v = 0.f;
             for (int s = 0; s < ks; ++s) v += partial[((size_t)(ti * ks + s) * MT + m) * TILE_N + r];   // slices in order
             if (a.ep.bias) v += (e == tid && t0 == 0) ? first_bias : a.ep.bias[n];
-            linear_finish(a.ep, m, n, v, e == tid, e_res);
+            linear_finish(a.ep, m, n, v, e == tid, e_res, e == tid, first_slot);
         }
         __syncthreads();
     }

@@ -315,6 +315,12 @@ class ModelRunner:
             slot_mapping=[seg(8 + g + i) for i in range(g)],
             host_q_len=[1] * rows, host_ctx_before=[0] * rows, host_state_slot=[0] * rows,
             max_q_len=1, max_ctx_after=self.max_context, decode_only=True, storage=self.storage)
+        # Tokens that the step before sampled are fetched on the device (source >= 0): by the
+        # embedding itself if it can, else by a kernel in front of it.
+        sources = meta[offsets[8 + 2 * g]: offsets[9 + 2 * g]]
+        fused_fetch = getattr(self.model.embedding, "takes_token_source", False)
+        if fused_fetch:
+            ctx.token_source, ctx.fed_ids = sources, self.sampled_ids
         state = _DecodeGraph(rows, offsets, meta, staging, ctx)
         self._fill_graph_inputs(state, [])                # all rows are padding: nothing is written
         meta.copy_(staging)
@@ -327,11 +333,10 @@ class ModelRunner:
         dependent = getattr(self.ops, "set_dependent_launch", None)
         if dependent is not None:
             dependent(True)
-        sources = meta[offsets[8 + 2 * g]: offsets[9 + 2 * g]]
         try:
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                # tokens that the step before sampled are fetched on the device (source >= 0)
-                self.ops.gather_tokens(ctx.token_ids, sources, self.sampled_ids)
+                if not fused_fetch:
+                    self.ops.gather_tokens(ctx.token_ids, sources, self.sampled_ids)
                 state.logits = self.model.forward(ctx)
                 # and this step's greedy choice is left where the next step looks for it
                 self.ops.argmax(state.logits, self.greedy_vocab_limit, out=self.sampled_ids[:rows])

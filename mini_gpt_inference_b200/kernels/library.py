@@ -20,7 +20,7 @@ _SIGNATURES = {
     "mg_device_arch": [_I],
     "mg_set_device": [_I],
     "mg_set_dependent_launch": [_I],
-    "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
     "mg_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
     "mg_gather_rows": [_P, _P, _P, _I, _I, _P],
     "mg_gather_tokens": [_P, _P, _P, _I, _P],

@@ -127,9 +127,16 @@ class CudaOps:
             raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
 
     # ---- embedding and norms --------------------------------------------------------------------
-    def embed(self, token_ids, positions, tok_emb, pos_table):
+    def embed(self, token_ids, positions, tok_emb, pos_table, source=None, previous=None):
+        """Rows of the embedding (plus rows of the position table).  With ``source``: a row whose
+        source is >= 0 takes its id from ``previous[source]`` instead of ``token_ids``."""
         self._want(token_ids, torch.int32, "token_ids", 1)
         self._want(positions, torch.int32, "positions", 1)
+        if source is not None:
+            self._want(source, torch.int32, "token sources", 1)
+            self._want(previous, torch.int32, "previous ids", 1)
+            if source.numel() != token_ids.numel():
+                raise KernelLibraryError("embed: one source per token")
         self._want(tok_emb, None, "tok_emb", 2)
         if pos_table is not None:
             self._want(pos_table, tok_emb.dtype, "pos_table", 2)
@@ -138,7 +145,8 @@ class CudaOps:
         n, width = token_ids.numel(), tok_emb.shape[1]
         out = torch.empty((n, width), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
-                                _ptr(out), n, width, self._is_bf16(tok_emb), self._stream()),
+                                _ptr(out), n, width, self._is_bf16(tok_emb), _ptr(source), _ptr(previous),
+                                self._stream()),
               "embed")
         return out
 

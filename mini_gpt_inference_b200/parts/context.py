@@ -34,6 +34,10 @@ class StepContext:
     logit_rows: torch.Tensor              # [W] rows whose logits are wanted
     # work list of kernels that take tiles of queries: see query_tiles(); None if not built
     attn_work: torch.Tensor | None = None
+    # Optional: where token_source[i] >= 0, token i is fed_ids[token_source[i]] (a token the step
+    # before sampled, still on the device) instead of token_ids[i].
+    token_source: torch.Tensor | None = None
+    fed_ids: torch.Tensor | None = None
     # host mirrors for parts that plan on the host
     host_q_len: list[int] = field(default_factory=list)
     host_ctx_before: list[int] = field(default_factory=list)

@@ -15,6 +15,9 @@ from .spec import TensorSpec
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
     graph_safe = True      # launches kernels only; nothing is decided on the host per step
+    # forward() honours ctx.token_source / ctx.fed_ids (tokens taken from the ids that the step
+    # before sampled); an embedding without this flag gets its tokens gathered by a kernel in front.
+    takes_token_source = True
 
     def __init__(self, prefix: str, vocab_size: int, width: int) -> None:
         super().__init__(prefix)
@@ -26,6 +29,10 @@ class TokenEmbedding(Part):
 
     def forward(self, ctx, position):
         table = position.table() if position is not None else None
+        if getattr(ctx, "token_source", None) is not None:
+            # some tokens are still on the device where the step before sampled them
+            return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table,
+                                 source=ctx.token_source, previous=ctx.fed_ids)
         return ctx.ops.embed(ctx.token_ids, ctx.positions, self.weight, table)
 
 
