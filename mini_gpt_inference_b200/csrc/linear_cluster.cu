@@ -69,6 +69,13 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
     const int e_m = tid / TILE_N, e_n = (cluster_id * WARPS + rank) * TILE_N + tid % TILE_N;
     const bool e_live = rank < WARPS && e_m < M && e_n < N;
     float e_bias = (e_live && a.ep.bias) ? a.ep.bias[e_n] : 0.f;
+    // for the QKV projection, the cache rows of the tokens this thread finishes (inputs of the step)
+    int e_slot[MT * TILE_N / THREADS];
+#pragma unroll
+    for (int j = 0; j < MT * TILE_N / THREADS; ++j) {
+        const int m = e_m + j * (THREADS / TILE_N);
+        e_slot[j] = (a.ep.k_pages != nullptr && m < M) ? a.ep.slots[m] : -1;
+    }
     pdl_trigger();
     pdl_wait();
     float e_res = 0.f;
@@ -134,7 +141,9 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
     for (int tl = rank; tl < WARPS; tl += ranks) {
         const int out_tile = cluster_id * WARPS + tl;
         if (out_tile >= total_tiles) break;
-        for (int e = tid; e < MT * TILE_N; e += THREADS) {
+#pragma unroll
+        for (int j = 0; j < MT * TILE_N / THREADS; ++j) {
+            const int e = tid + j * THREADS;
             const int m = e / TILE_N, r = e - m * TILE_N;
             const int n = out_tile * TILE_N + r;
             if (m >= M || n >= N) continue;
@@ -145,7 +154,7 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
             }
             const bool first = tl == rank && e == tid;
             if (a.ep.bias) v += first ? e_bias : a.ep.bias[n];
-            linear_finish(a.ep, m, n, v, first, e_res);
+            linear_finish(a.ep, m, n, v, first, e_res, true, e_slot[j]);
         }
     }
     cluster.sync();                                    // nobody leaves while its sums may still be read
