@@ -8,8 +8,9 @@
 // its weights (16 bytes per row and k block) before it waits for the kernel in front.  The sums
 // run on warp-level mma (m16n8k16, tokens as the 16 rows of A, weight rows as the 8 columns of
 // B; see linear_skinny.cu for how one 16-byte load feeds two mma's).  The partial sums of the K
-// slices meet through distributed shared memory: after a cluster barrier the CTA of rank r adds
-// up tile r from the shared memory of all ranks, in rank order, and applies the epilogue.
+// slices meet through distributed shared memory: every warp stores its tile's partial sums into
+// the shared memory of the CTA that finishes that tile; after one cluster barrier that CTA adds
+// them up in rank order from its own memory and applies the epilogue.
 //
 // Every output element sums its K terms in a fixed order (k blocks in order inside a slice,
 // slices in rank order), independent of M and of the other rows.  K must be a multiple of 8.
@@ -127,18 +128,22 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
             }
         }
     }
-    // c0, c1: token 16 mg + g, rows 2t and 2t+1 of the tile; c2, c3: token 16 mg + g + 8
+    // c0, c1: token 16 mg + g, rows 2t and 2t+1 of the tile; c2, c3: token 16 mg + g + 8.
+    // The partial sums of tile `warp` go straight into the shared memory of the CTA that finishes
+    // that tile (rank warp % ranks), into the row of this rank: [slot][source rank][MT][8].
     {
-        float* mine = part + (size_t)warp * MT * TILE_N;
+        float* theirs = cluster.map_shared_rank(part, warp % ranks) +
+                        ((size_t)(warp / ranks) * ranks + rank) * MT * TILE_N;
 #pragma unroll
         for (int mg = 0; mg < MG; ++mg) {
-            *reinterpret_cast<float2*>(mine + (mg * 16 + g) * TILE_N + 2 * t) = make_float2(c[mg][0], c[mg][1]);
-            *reinterpret_cast<float2*>(mine + (mg * 16 + g + 8) * TILE_N + 2 * t) = make_float2(c[mg][2], c[mg][3]);
+            *reinterpret_cast<float2*>(theirs + (mg * 16 + g) * TILE_N + 2 * t) = make_float2(c[mg][0], c[mg][1]);
+            *reinterpret_cast<float2*>(theirs + (mg * 16 + g + 8) * TILE_N + 2 * t) = make_float2(c[mg][2], c[mg][3]);
         }
     }
-    cluster.sync();
+    cluster.sync();                                    // all partial sums have arrived; nothing remote is touched after this
     // ---- the CTA of rank r finishes tiles r, r + ranks, ...: slices added in rank order ----
-    for (int tl = rank; tl < WARPS; tl += ranks) {
+    for (int slot = 0; slot * ranks + rank < WARPS; ++slot) {
+        const int tl = slot * ranks + rank;
         const int out_tile = cluster_id * WARPS + tl;
         if (out_tile >= total_tiles) break;
 #pragma unroll
@@ -148,16 +153,12 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
             const int n = out_tile * TILE_N + r;
             if (m >= M || n >= N) continue;
             float v = 0.f;
-            for (int s = 0; s < ranks; ++s) {
-                const float* theirs = cluster.map_shared_rank(part, s);
-                v += theirs[((size_t)tl * MT + m) * TILE_N + r];
-            }
-            const bool first = tl == rank && e == tid;
+            for (int s = 0; s < ranks; ++s) v += part[((size_t)(slot * ranks + s) * MT + m) * TILE_N + r];
+            const bool first = slot == 0 && j == 0;
             if (a.ep.bias) v += first ? e_bias : a.ep.bias[n];
             linear_finish(a.ep, m, n, v, first, e_res, true, e_slot[j]);
         }
     }
-    cluster.sync();                                    // nobody leaves while its sums may still be read
 }
 
 }  // namespace
