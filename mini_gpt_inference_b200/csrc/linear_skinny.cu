@@ -47,6 +47,11 @@ struct SkinnyArgs {
     int M, N, K;
     int k_splits;                    // warps that share one tile of 8 rows (1, 2, 4 or 8)
     int tiles_per_cta;
+    // greedy choice on the way (AMAX kernels): the largest output of each token over this CTA's
+    // rows goes to amax_v / amax_i [token][CTA]; rows at and past amax_limit are never chosen
+    float* amax_v;
+    int* amax_i;
+    int amax_limit;
 };
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
@@ -54,7 +59,10 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int MT>   // token rows of the A operand: 8 (rows 8..15 are zero) or 16; a.M <= MT
+// MT: token rows of the A operand: 8 (rows 8..15 are zero) or 16; a.M <= MT.  AMAX: also leave,
+// per token, the largest output of this CTA's rows and its index (the first stage of an argmax
+// over the rows, for the head's logits), lowest index first among equals.
+template <int MT, bool AMAX>
 __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs a) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     const int K = a.K;
@@ -63,6 +71,10 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     float* partial = reinterpret_cast<float*>(smem_raw + (size_t)MT * xstride);   // [WARPS][MT][8]
     float* gain_s = partial + WARPS * MT * TILE_N;                                // [K] and [K]: LayerNorm gain and shift
     float* shift_s = gain_s + K;
+    float* cand_v = shift_s + K;                                                  // [WARPS][MT] and the same of ints (AMAX)
+    int* cand_i = reinterpret_cast<int*>(cand_v + WARPS * MT);
+    float best_v = -INFINITY;                                                     // thread m: token m's best so far
+    int best_i = 0x7fffffff;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
 
@@ -233,13 +245,45 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             const int ti = e / (MT * TILE_N), rem = e - ti * (MT * TILE_N);
             const int m = rem / TILE_N, r = rem - m * TILE_N;
             const int n = (first_tile + t0 + ti) * TILE_N + r;
-            if ((t0 + ti) >= a.tiles_per_cta || n >= a.N || m >= a.M) continue;
+            const bool live = (t0 + ti) < a.tiles_per_cta && n < a.N && m < a.M;
             float v = 0.f;
-            for (int s = 0; s < ks; ++s) v += partial[((size_t)(ti * ks + s) * MT + m) * TILE_N + r];   // slices in order
-            if (a.ep.bias) v += (e == tid && t0 == 0) ? first_bias : a.ep.bias[n];
-            linear_finish(a.ep, m, n, v, e == tid, e_res, e == tid, first_slot);
+            if (live) {
+                for (int s = 0; s < ks; ++s) v += partial[((size_t)(ti * ks + s) * MT + m) * TILE_N + r];   // slices in order
+                if (a.ep.bias) v += (e == tid && t0 == 0) ? first_bias : a.ep.bias[n];
+                linear_finish(a.ep, m, n, v, e == tid, e_res, e == tid, first_slot);
+            }
+            if constexpr (AMAX) {
+                // the eight rows of a (tile, token) sit in eight neighbouring lanes
+                float cv = (live && n < a.amax_limit) ? v : -INFINITY;
+                int ci = (live && n < a.amax_limit) ? n : 0x7fffffff;
+#pragma unroll
+                for (int o = 1; o < TILE_N; o <<= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, cv, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, ci, o);
+                    if (ov > cv || (ov == cv && oi < ci)) { cv = ov; ci = oi; }
+                }
+                if (r == 0) {
+                    cand_v[ti * MT + m] = cv;
+                    cand_i[ti * MT + m] = ci;
+                }
+            }
         }
         __syncthreads();
+        if constexpr (AMAX) {
+            if (tid < MT) {
+                for (int ti = 0; ti < tiles_per_round; ++ti) {                   // tiles in order
+                    const float cv = cand_v[ti * MT + tid];
+                    const int ci = cand_i[ti * MT + tid];
+                    if (cv > best_v || (cv == best_v && ci < best_i)) { best_v = cv; best_i = ci; }
+                }
+            }
+        }
+    }
+    if constexpr (AMAX) {
+        if (tid < a.M) {
+            a.amax_v[(size_t)tid * gridDim.x + blockIdx.x] = best_v;
+            a.amax_i[(size_t)tid * gridDim.x + blockIdx.x] = best_i;
+        }
     }
 }
 
@@ -248,9 +292,32 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
 // Largest M this kernel takes.
 MG_API int mg_linear_skinny_max_rows() { return MAX_M; }
 
+// How the work of an [N, K] matrix is cut: tiles of 8 rows, each shared by `ks` warps with at least
+// two k blocks (of 32) per warp, so that every SM gets some and a lane holds all its weights at
+// once; `tpc` tiles per CTA.  Returns the number of CTAs.
+static int skinny_split(int N, int K, int* ks_out, int* tpc_out) {
+    const int tiles = (N + TILE_N - 1) / TILE_N, kblocks = (K + 31) / 32;
+    int ks = 1;
+    while (ks < WARPS && kblocks / (ks * 2) >= 2 && (long long)tiles * (ks * 2) / WARPS <= 200) ks *= 2;
+    const int per_round = WARPS / ks;
+    int tpc = per_round;                                   // one round per CTA by default
+    while ((tiles + tpc - 1) / tpc > 8 * 148) tpc += per_round;
+    *ks_out = ks;
+    *tpc_out = tpc;
+    return (tiles + tpc - 1) / tpc;
+}
+
+// CTAs mg_linear_skinny launches for an [N, K] matrix: with the greedy choice on the way, its
+// scratch holds M * that many floats and as many ints.
+MG_API int mg_linear_skinny_ctas(int N, int K) {
+    int ks, tpc;
+    return skinny_split(N, K, &ks, &tpc);
+}
+
 // Shared memory the kernel needs for M tokens of width K (the caller checks it against the limit).
 static size_t skinny_smem(int mt, int K) {
-    return (size_t)mt * ((size_t)K * 2 + XPAD) + (size_t)WARPS * mt * TILE_N * sizeof(float) + (size_t)2 * K * sizeof(float);
+    return (size_t)mt * ((size_t)K * 2 + XPAD) + (size_t)WARPS * mt * TILE_N * sizeof(float) + (size_t)2 * K * sizeof(float) +
+           (size_t)2 * WARPS * mt * sizeof(float);
 }
 
 // x: [M, K] bf16 (or null when x32 is given: then rows row_index[m] (or m) of x32 [*, K] are
@@ -261,7 +328,7 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
                             const float* shift, float eps, const void* w, const float* bias, void* out,
                             float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
                             void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
-                            int page_tokens, void* stream) {
+                            int page_tokens, float* amax_v, int* amax_i, int amax_limit, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
@@ -281,28 +348,26 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
     a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
-    // Cut the work so that every SM gets some and a lane holds all its weights at once: tiles of
-    // 8 rows, each shared by k_splits warps with at least two k blocks (of 32) per warp.
-    const int tiles = (N + TILE_N - 1) / TILE_N;
-    const int kblocks = (K + 31) / 32;
-    int ks = 1;
-    while (ks < WARPS && kblocks / (ks * 2) >= 2 && (long long)tiles * (ks * 2) / WARPS <= 200) ks *= 2;
-    a.k_splits = ks;
-    const int per_round = WARPS / ks;
-    int tpc = per_round;                                   // one round per CTA by default
-    while ((tiles + tpc - 1) / tpc > 8 * 148) tpc += per_round;
-    a.tiles_per_cta = tpc;
-    const int grid = (tiles + tpc - 1) / tpc;
+    MG_REQUIRE(amax_v == nullptr || (amax_i != nullptr && epilogue == EPI_STORE && !out_bf16),
+               "linear: the greedy choice goes with 32-bit stored outputs");
+    a.amax_v = amax_v; a.amax_i = amax_i; a.amax_limit = (amax_limit <= 0 || amax_limit > N) ? N : amax_limit;
+    const int grid = skinny_split(N, K, &a.k_splits, &a.tiles_per_cta);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_skinny_kernel<16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear (skinny): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     cudaStream_t s = (cudaStream_t)stream;
-    const cudaError_t le = mt == 8 ? mg_launch(linear_skinny_kernel<8>, dim3(grid), dim3(THREADS), smem, s, true, a)
-                                   : mg_launch(linear_skinny_kernel<16>, dim3(grid), dim3(THREADS), smem, s, true, a);
+    const bool amax = amax_v != nullptr;
+    const cudaError_t le =
+        mt == 8 ? (amax ? mg_launch(linear_skinny_kernel<8, true>, dim3(grid), dim3(THREADS), smem, s, true, a)
+                        : mg_launch(linear_skinny_kernel<8, false>, dim3(grid), dim3(THREADS), smem, s, true, a))
+                : (amax ? mg_launch(linear_skinny_kernel<16, true>, dim3(grid), dim3(THREADS), smem, s, true, a)
+                        : mg_launch(linear_skinny_kernel<16, false>, dim3(grid), dim3(THREADS), smem, s, true, a));
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear_skinny: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("linear_skinny");
     return MG_OK;

@@ -104,6 +104,43 @@ __global__ void argmax_merge_kernel(const float* __restrict__ part_v, const int*
     if (threadIdx.x == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
 }
 
+// Stage 2 for many parts (hundreds, as the head projection leaves them): a block per row.
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_merge_block_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out,
+                          int parts) {
+    __shared__ float best_v[ARGMAX_THREADS / 32];
+    __shared__ int best_i[ARGMAX_THREADS / 32];
+    float v = -INFINITY;
+    int idx = 0x7fffffff;
+    pdl_trigger();
+    pdl_wait();
+    for (int k = threadIdx.x; k < parts; k += ARGMAX_THREADS) {
+        const float x = part_v[(size_t)blockIdx.x * parts + k];
+        const int i = part_i[(size_t)blockIdx.x * parts + k];
+        if (x > v || (x == v && i < idx)) { v = x; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { best_v[warp] = v; best_i[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < ARGMAX_THREADS / 32 ? best_v[lane] : -INFINITY;
+        idx = lane < ARGMAX_THREADS / 32 ? best_i[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+
 constexpr int ARGMAX_SLICE = 2048;
 
 }  // namespace
@@ -138,6 +175,21 @@ MG_API int mg_argmax_wide(const float* logits, int* out, float* scratch_v, int* 
     MG_CHECK_LAUNCH("argmax (parts)");
     le = mg_launch(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, true, (const float*)scratch_v, (const int*)scratch_i, out,
                    parts);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "argmax (merge): %s", cudaGetErrorString(le));
+    MG_CHECK_LAUNCH("argmax (merge)");
+    return MG_OK;
+}
+
+// The second stage alone: part_v / part_i hold `parts` candidates per row (value and index, as
+// the head projection leaves them when it takes the greedy choice on its way).
+MG_API int mg_argmax_merge(const float* part_v, const int* part_i, int* out, int rows, int parts, void* stream) {
+    if (rows == 0) return MG_OK;
+    MG_REQUIRE(rows > 0 && parts > 0 && part_v && part_i && out, "argmax (merge): bad arguments");
+    const cudaError_t le =
+        parts > 64 ? mg_launch(argmax_merge_block_kernel, dim3(rows), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, true,
+                               part_v, part_i, out, parts)
+                   : mg_launch(argmax_merge_kernel, dim3(rows), dim3(32), 0, (cudaStream_t)stream, true, part_v, part_i, out,
+                               parts);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "argmax (merge): %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("argmax (merge)");
     return MG_OK;

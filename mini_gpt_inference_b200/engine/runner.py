@@ -337,9 +337,13 @@ class ModelRunner:
             with torch.cuda.graph(graph, pool=self._graph_pool):
                 if not fused_fetch:
                     self.ops.gather_tokens(ctx.token_ids, sources, self.sampled_ids)
+                # this step's greedy choice is left where the next step looks for it: by the head
+                # on its way if it can, else by the argmax kernels
+                ctx.greedy_out, ctx.greedy_vocab_limit = self.sampled_ids[:rows], self.greedy_vocab_limit
+                ctx.greedy_taken = False
                 state.logits = self.model.forward(ctx)
-                # and this step's greedy choice is left where the next step looks for it
-                self.ops.argmax(state.logits, self.greedy_vocab_limit, out=self.sampled_ids[:rows])
+                if not ctx.greedy_taken:
+                    self.ops.argmax(state.logits, self.greedy_vocab_limit, out=self.sampled_ids[:rows])
         finally:
             if dependent is not None:
                 dependent(False)

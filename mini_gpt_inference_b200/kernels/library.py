@@ -27,7 +27,9 @@ _SIGNATURES = {
     "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_skinny": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
-                         _I, _I, _I, _I, _P],
+                         _I, _I, _I, _I, _P, _P, _I, _P],
+    "mg_linear_skinny_ctas": [_I, _I],
+    "mg_argmax_merge": [_P, _P, _P, _I, _I, _P],
     "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],

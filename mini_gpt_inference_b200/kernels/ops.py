@@ -70,6 +70,7 @@ class CudaOps:
         self.use_split_attention = True
         self.use_skinny = True
         self.use_cluster = True
+        self.greedy_taken = False
         self.use_dependent_launch = True
         self.use_prefill_tc = True
         self._counter_buf = None
@@ -198,7 +199,7 @@ class CudaOps:
         return (self.use_skinny and dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0
                 and SKINNY_ROWS * (2 * k + 64) + 8 * SKINNY_ROWS * 8 * 4 + 8 * k <= 200 * 1024)
 
-    def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None):
+    def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None, greedy=None):
         """x: a tensor [M, K] or a DeferredNorm.  kv_sink: (cache view, slots, n_head, n_kv_head,
         head_dim) to also write key/value features to the cache.  Returns True if the sink was
         served inside the projection kernel."""
@@ -224,10 +225,22 @@ class CudaOps:
             else:
                 self._want(x, weight.dtype, "linear input", 2)
                 args = [_ptr(x), None, None, None, None, 0.0]
+            amax = [None, None, 0]
+            if greedy is not None:
+                # first stage of the argmax over the rows, on the projection's way
+                ids_out, limit = greedy
+                parts = self.lib.mg_linear_skinny_ctas(n, k)
+                part_v = torch.empty((m * parts,), dtype=torch.float32, device=self.device)
+                part_i = torch.empty((m * parts,), dtype=torch.int32, device=self.device)
+                amax = [_ptr(part_v), _ptr(part_i), int(limit or 0)]
             code = self.lib.mg_linear_skinny(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
-                                             m, n, k, epilogue, out_bf16, *sink, self._stream())
+                                             m, n, k, epilogue, out_bf16, *sink, *amax, self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "linear (small batch)")
+                if greedy is not None:
+                    self._run(self.lib.mg_argmax_merge(_ptr(part_v), _ptr(part_i), _ptr(ids_out), m, parts,
+                                                       self._stream()), "argmax (merge)")
+                    self.greedy_taken = True
                 return kv_sink is not None
         if deferred is not None:
             x = deferred.materialize()
@@ -281,8 +294,17 @@ class CudaOps:
             raise KernelLibraryError("linear_residual: residual has the wrong shape")
         self._linear(x, weight, bias, EPILOGUES["residual"], None, residual32)
 
-    def logits(self, y, tok_emb):
-        return self.linear(y, tok_emb, None, "none", torch.float32)
+    def logits(self, y, tok_emb, greedy_out=None, vocab_limit=None):
+        """Logits in 32-bit.  With ``greedy_out`` (int32 ``[rows]``): the argmax of every row (ids at
+        or above ``vocab_limit`` excluded) is left there as well; returns ``(logits, taken)`` then,
+        ``taken`` False if the projection that ran cannot take it on its way."""
+        if greedy_out is None:
+            return self.linear(y, tok_emb, None, "none", torch.float32)
+        self._ids_out(greedy_out, y.shape[0])
+        out = torch.empty((y.shape[0], tok_emb.shape[0]), dtype=torch.float32, device=self.device)
+        self.greedy_taken = False
+        self._linear(y, tok_emb, None, EPILOGUES["none"], out, None, greedy=(greedy_out, vocab_limit))
+        return out, self.greedy_taken
 
     # ---- attention ------------------------------------------------------------------------------
     def kv_store(self, qkv, n_head, n_kv_head, head_dim, cache, slot_mapping):

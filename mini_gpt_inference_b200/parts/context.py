@@ -38,6 +38,11 @@ class StepContext:
     # before sampled, still on the device) instead of token_ids[i].
     token_source: torch.Tensor | None = None
     fed_ids: torch.Tensor | None = None
+    # Optional: where the head may leave the argmax of every logits row (ids at or above
+    # greedy_vocab_limit excluded); it sets greedy_taken if it did.
+    greedy_out: torch.Tensor | None = None
+    greedy_vocab_limit: int | None = None
+    greedy_taken: bool = False
     # host mirrors for parts that plan on the host
     host_q_len: list[int] = field(default_factory=list)
     host_ctx_before: list[int] = field(default_factory=list)

@@ -59,4 +59,10 @@ class TiedHead(Part):
         return None
 
     def forward(self, ctx, y):
+        greedy_out = getattr(ctx, "greedy_out", None)
+        if greedy_out is not None:
+            # the step also wants each row's greedy choice: the projection may take it on its way
+            logits, ctx.greedy_taken = ctx.ops.logits(y, self.embedding.weight, greedy_out,
+                                                      getattr(ctx, "greedy_vocab_limit", None))
+            return logits
         return ctx.ops.logits(y, self.embedding.weight)

@@ -162,6 +162,36 @@ def test_mid_batch_projection_over_a_cluster(ops, m, n, k):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 16, 24])
+@pytest.mark.parametrize("vocab,k,limit", [(50304, 512, None), (50304, 512, 50257), (509, 96, 300), (77, 40, None)])
+def test_greedy_choice_on_the_way_of_the_head_projection(ops, m, vocab, k, limit):
+    """The head's projection may leave the argmax of every row while it writes the logits: it
+    must be the argmax of exactly those logits (lowest index among equals, ids at or above the
+    limit never), whichever kernel runs."""
+    x32 = randn(m + 2, k, seed=61, scale=1.5)
+    rows = torch.tensor([(3 * i + 1) % (m + 2) for i in range(m)], dtype=torch.int32).cuda()
+    gain, shift = randn(k, seed=62) + 1.0, randn(k, seed=63)
+    w = randn(vocab, k, dtype=torch.bfloat16, seed=64, scale=1 / math.sqrt(k))
+    w[vocab // 2] = w[3]                                        # equal logits: the lower index must win
+    w[vocab - 1] = w[3]
+    ids = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+    y = ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16, rows)
+    logits, taken = ops.logits(y, w, ids, limit)
+    if not taken:
+        ids = ops.argmax(logits, limit)
+    assert taken == (m <= 16), "up to 16 rows the small-batch projection takes the choice on its way"
+    masked = logits.clone()
+    if limit is not None:
+        masked[:, limit:] = -float("inf")
+    want = masked.argmax(-1)
+    best = masked.max(-1).values
+    first = (masked == best[:, None]).float().argmax(-1)      # lowest index among equal maxima
+    assert torch.equal(ids.long(), first), (ids, want)
+    plain = ops.logits(y, w)
+    assert torch.equal(plain, logits), "the logits themselves must not change"
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [1, 4, 8, 9, 40])
 def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m):
     n_head, n_kv, d, pt, pages, k = 6, 2, 32, 8, 12, 96
