@@ -199,10 +199,21 @@ class CudaOps:
         return (self.use_skinny and dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0
                 and SKINNY_ROWS * (2 * k + 64) + 8 * SKINNY_ROWS * 8 * 4 + 8 * k <= 200 * 1024)
 
+    @staticmethod
+    def _sink_args(kv_sink):
+        """The key/value sink of a QKV projection as the C functions take it."""
+        if kv_sink is None:
+            return [None, None, None, 0, 0, 0, 0]
+        cache, slots, n_head, n_kv_head, head_dim = kv_sink
+        return [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim, n_kv_head,
+                head_dim, cache.page_tokens]
+
     def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None, greedy=None):
         """x: a tensor [M, K] or a DeferredNorm.  kv_sink: (cache view, slots, n_head, n_kv_head,
-        head_dim) to also write key/value features to the cache.  Returns True if the sink was
-        served inside the projection kernel."""
+        head_dim) to also write key/value features to the cache.  greedy: (ids out, vocabulary
+        limit) to also leave each row's argmax where the kernel that runs can take it on its way
+        (``self.greedy_taken`` says whether it did).  Returns True if the sink was served inside
+        the projection kernel."""
         deferred = x if isinstance(x, DeferredNorm) else None
         m, k = x.shape
         n = weight.shape[0]
@@ -214,11 +225,7 @@ class CudaOps:
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
         if self._skinny_ok(m, k, weight.dtype):
-            sink = [None, None, None, 0, 0, 0, 0]
-            if kv_sink is not None:
-                cache, slots, n_head, n_kv_head, head_dim = kv_sink
-                sink = [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim,
-                        n_kv_head, head_dim, cache.page_tokens]
+            sink = self._sink_args(kv_sink)
             if deferred is not None:
                 args = [None, _ptr(deferred.x32), _ptr(deferred.rows), _ptr(deferred.gain),
                         _ptr(deferred.shift), deferred.eps]
@@ -246,11 +253,7 @@ class CudaOps:
             x = deferred.materialize()
         self._want(x, weight.dtype, "linear input", 2)
         if x.dtype == torch.bfloat16 and self.use_cluster and 0 < m <= CLUSTER_ROWS and k % 8 == 0:
-            sink = [None, None, None, 0, 0, 0, 0]
-            if kv_sink is not None:
-                cache, slots, n_head, n_kv_head, head_dim = kv_sink
-                sink = [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim,
-                        n_kv_head, head_dim, cache.page_tokens]
+            sink = self._sink_args(kv_sink)
             code = self.lib.mg_linear_cluster(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                               m, n, k, epilogue, out_bf16, *sink, self._stream())
             if code != library.UNSUPPORTED:
