@@ -17,6 +17,8 @@ from .library import KernelLibraryError, check
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
 CLUSTER_ROWS = 64        # most tokens the mid-batch (K split over a cluster) projection kernel takes
+STREAM_MIN_ROWS = 8192   # a matrix this tall (the head) goes through the streaming kernel ...
+STREAM_ROWS = 16         # ... for up to this many tokens (it takes 64; beyond 16 the tensor-core GEMM measured faster)
 
 
 class DeferredNorm:
@@ -70,6 +72,7 @@ class CudaOps:
         self.use_split_attention = True
         self.use_skinny = True
         self.use_cluster = True
+        self.use_stream = True
         self.greedy_taken = False
         self.use_dependent_launch = True
         self.use_prefill_tc = True
@@ -224,6 +227,35 @@ class CudaOps:
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
+        if (self.use_stream and kv_sink is None and n >= STREAM_MIN_ROWS and weight.dtype == torch.bfloat16
+                and 0 < m <= STREAM_ROWS and k % 8 == 0):
+            # a wide matrix (the head): one CTA per SM streams it through shared memory
+            if deferred is not None and m > SKINNY_ROWS:
+                # more rows than a CTA normalises quickly: the norm runs as a kernel of its own
+                x, deferred = deferred.materialize(), None
+            if deferred is not None:
+                args = [None, _ptr(deferred.x32), _ptr(deferred.rows), _ptr(deferred.gain),
+                        _ptr(deferred.shift), deferred.eps]
+            else:
+                self._want(x, weight.dtype, "linear input", 2)
+                args = [_ptr(x), None, None, None, None, 0.0]
+            amax = [None, None, 0]
+            if greedy is not None:
+                ids_out, limit = greedy
+                parts = self.lib.mg_linear_stream_parts(n)
+                part_v = torch.empty((m * parts,), dtype=torch.float32, device=self.device)
+                part_i = torch.empty((m * parts,), dtype=torch.int32, device=self.device)
+                amax = [_ptr(part_v), _ptr(part_i), int(limit or 0)]
+            code = self.lib.mg_linear_stream(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                             m, n, k, epilogue, out_bf16, *amax, _ptr(self.status),
+                                             self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "linear (wide matrix)")
+                if greedy is not None:
+                    self._run(self.lib.mg_argmax_merge(_ptr(part_v), _ptr(part_i), _ptr(ids_out), m, parts,
+                                                       self._stream()), "argmax (merge)")
+                    self.greedy_taken = True
+                return False
         if self._skinny_ok(m, k, weight.dtype):
             sink = self._sink_args(kv_sink)
             if deferred is not None:
@@ -252,7 +284,10 @@ class CudaOps:
         if deferred is not None:
             x = deferred.materialize()
         self._want(x, weight.dtype, "linear input", 2)
-        if x.dtype == torch.bfloat16 and self.use_cluster and 0 < m <= CLUSTER_ROWS and k % 8 == 0:
+        # (a matrix of thousands of 8-row tiles, the head, is left to the tensor-core GEMM: every one
+        # of its clusters would stage the activations and meet at a barrier for a few KB of weights)
+        if (x.dtype == torch.bfloat16 and self.use_cluster and 0 < m <= CLUSTER_ROWS and k % 8 == 0
+                and n <= 8192):
             sink = self._sink_args(kv_sink)
             code = self.lib.mg_linear_cluster(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                               m, n, k, epilogue, out_bf16, *sink, self._stream())

@@ -162,8 +162,9 @@ def test_mid_batch_projection_over_a_cluster(ops, m, n, k):
     ops.check_status()
 
 
-@pytest.mark.parametrize("m", [1, 5, 8, 16, 24])
-@pytest.mark.parametrize("vocab,k,limit", [(50304, 512, None), (50304, 512, 50257), (509, 96, 300), (77, 40, None)])
+@pytest.mark.parametrize("m", [1, 5, 8, 16, 24, 33, 64])
+@pytest.mark.parametrize("vocab,k,limit", [(50304, 512, None), (50304, 512, 50257), (509, 96, 300), (77, 40, None),
+                                           (9001, 200, 9000)])
 def test_greedy_choice_on_the_way_of_the_head_projection(ops, m, vocab, k, limit):
     """The head's projection may leave the argmax of every row while it writes the logits: it
     must be the argmax of exactly those logits (lowest index among equals, ids at or above the
@@ -179,7 +180,7 @@ def test_greedy_choice_on_the_way_of_the_head_projection(ops, m, vocab, k, limit
     logits, taken = ops.logits(y, w, ids, limit)
     if not taken:
         ids = ops.argmax(logits, limit)
-    assert taken == (m <= 16), "up to 16 rows the small-batch projection takes the choice on its way"
+    assert taken == (m <= 16), "up to 16 rows the projection takes the choice on its way"
     masked = logits.clone()
     if limit is not None:
         masked[:, limit:] = -float("inf")
@@ -189,6 +190,33 @@ def test_greedy_choice_on_the_way_of_the_head_projection(ops, m, vocab, k, limit
     assert torch.equal(ids.long(), first), (ids, want)
     plain = ops.logits(y, w)
     assert torch.equal(plain, logits), "the logits themselves must not change"
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m", [3, 16, 24, 64])
+def test_streaming_projection_of_a_wide_matrix_takes_up_to_64_rows(ops, m):
+    """The kernel that streams a wide matrix through shared memory is used for up to 16 rows; it
+    takes 64, checked here by raising the limit."""
+    from mini_gpt_inference_b200.kernels import ops as ops_module
+
+    n, k = 9001, 200
+    x = randn(m, k, dtype=torch.bfloat16, seed=71)
+    w = randn(n, k, dtype=torch.bfloat16, seed=72, scale=1 / math.sqrt(k))
+    b = randn(n, seed=73)
+    want = x.double() @ w.double().T + b.double()
+    was = ops_module.STREAM_ROWS
+    ops_module.STREAM_ROWS = 64
+    try:
+        ids = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+        got = ops.linear(x, w, b, "none", torch.float32)
+        logits, taken = ops.logits(x, w, ids, 9000)
+    finally:
+        ops_module.STREAM_ROWS = was
+    assert taken
+    assert (got.double() - want).abs().max() <= 2e-4
+    masked = logits.clone()
+    masked[:, 9000:] = -float("inf")
+    assert torch.equal(ids.long(), masked.argmax(-1))
     ops.check_status()
 
 
