@@ -92,23 +92,28 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
     // this warp takes tiles tile_begin + warp, + WARPS, ...
     const int n_mine = tile_begin + warp < tile_end ? (tile_end - tile_begin - warp + WARPS - 1) / WARPS : 0;
 
-    // ask for tile j of this warp (lane 0): one bulk copy per weight row that exists
+    // Ask for tile j of this warp (the whole warp calls): lane 0 announces the bytes, then lane r
+    // asks for weight row r with a bulk copy of its own: one instruction for the eight copies
+    // (issued one after the other by a single lane they cost the warp a microsecond a tile).
     auto issue = [&](int j) {
         const int tile = tile_begin + warp + j * WARPS, s = j % stages;
         const int rows = min(TILE_N, a.N - tile * TILE_N);
         const uint32_t bar = smem_u32(&bars[warp][s]);
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)rows * K * 2) : "memory");
-        for (int r = 0; r < rows; ++r)
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)rows * K * 2) : "memory");
+        __syncwarp();
+        if (lane < rows)
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_u32(my_ring + (size_t)s * tile_bytes + (size_t)r * xstride)),
-                           "l"(a.w + ((size_t)tile * TILE_N + r) * K), "r"((uint32_t)K * 2), "r"(bar)
+                         ::"r"(smem_u32(my_ring + (size_t)s * tile_bytes + (size_t)lane * xstride)),
+                           "l"(a.w + ((size_t)tile * TILE_N + lane) * K), "r"((uint32_t)K * 2), "r"(bar)
                          : "memory");
     };
     if (lane == 0) {
         for (int s = 0; s < stages; ++s) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&bars[warp][s])) : "memory");
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int j = 0; j < stages && j < n_mine; ++j) issue(j);       // weights depend on no kernel before
     }
+    __syncwarp();
+    for (int j = 0; j < stages && j < n_mine; ++j) issue(j);           // weights depend on no kernel before
     // Which rows to normalise, and gain and shift, are inputs and weights as well.
     int first_row = warp;
     if (a.x32 != nullptr && a.row_index != nullptr && warp < a.M) first_row = a.row_index[warp];
@@ -226,7 +231,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
             }
         }
         __syncwarp();                                                   // every lane has read the stage
-        if (lane == 0 && j + stages < n_mine) {
+        if (j + stages < n_mine) {                                      // uniform in the warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(j + stages);
         }
