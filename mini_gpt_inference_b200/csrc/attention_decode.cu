@@ -331,7 +331,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float m = mx[nt][i & 1];
-                e[i] = m == -INFINITY ? 0.f : exp2f(s[nt][mt][i] - m);  // a warp past the last key holds nothing
+                e[i] = m == -INFINITY ? 0.f : exp2_approx(s[nt][mt][i] - m);  // a warp past the last key holds nothing
                 sum[nt][i & 1] += e[i];
             }
             // P[key, head] as the B operand of the next product needs keys along k: the 8x8 blocks

@@ -281,13 +281,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             float pv[32];
             if (unmasked) {
 #pragma unroll
-                for (int j = 0; j < 32; ++j) pv[j] = exp2f(fmaf(__uint_as_float(r[j]), scale_log2e, -shift));
+                for (int j = 0; j < 32; ++j) pv[j] = exp2_approx(fmaf(__uint_as_float(r[j]), scale_log2e, -shift));
             } else {
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
                     const int col = c * 32 + j;
                     const bool visible = !none && col <= hi && col >= lo_col;
-                    pv[j] = visible ? exp2f(fmaf(__uint_as_float(r[j]), scale_log2e, -shift)) : 0.f;
+                    pv[j] = visible ? exp2_approx(fmaf(__uint_as_float(r[j]), scale_log2e, -shift)) : 0.f;
                 }
             }
 #pragma unroll

@@ -57,6 +57,15 @@ __device__ __forceinline__ float gelu_tanh(float u) {
     return 0.5f * u * (1.0f + tanhf(k * (u + 0.044715f * u * u * u)));
 }
 
+// 2^x as one instruction of the special-function unit (two units in the last place; results
+// below the smallest normal number become zero).  For softmax weights, whose argument is <= 0 and
+// whose result is rounded to bfloat16 or summed in 32-bit right away.
+__device__ __forceinline__ float exp2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
 // ---- programmatic dependent launch ---------------------------------------------------------
