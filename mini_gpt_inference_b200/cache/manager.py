@@ -40,6 +40,10 @@ class RequestCache:
     state_slot: int
     length: int = 0                                   # tokens in the cache
     tables: list[list[int]] = field(default_factory=list)   # per group: page id per page index
+    # (serial, version) names one state of the tables: serial is unique per admission, version
+    # counts their changes, so a copy of the tables kept elsewhere knows when it is stale
+    serial: int = 0
+    version: int = 0
 
 
 class CacheManager:
@@ -99,7 +103,8 @@ class CacheManager:
             raise PoolError(f"request {request_id!r} is already admitted")
         if self.slots.num_free == 0:
             raise CacheFullError("no state slot free")
-        req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups])
+        self._serial = getattr(self, "_serial", 0) + 1
+        req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups], self._serial)
         self.requests[request_id] = req
         return req
 
@@ -141,7 +146,9 @@ class CacheManager:
         if any(n > group.pool.num_free for n, group in zip(need, self.groups)):
             return False
         for g, (n, group) in enumerate(zip(need, self.groups)):
-            req.tables[g].extend(group.pool.take(n))
+            if n:
+                req.tables[g].extend(group.pool.take(n))
+                req.version += 1
         return True
 
     def advance(self, request_id: str, new_length: int) -> None:
@@ -161,6 +168,7 @@ class CacheManager:
                 group.pool.give_back(passed)
                 for i in range(min(first, len(table))):
                     table[i] = NO_PAGE
+                req.version += 1
 
     def release(self, request_id: str) -> None:
         req = self.get(request_id)

@@ -50,6 +50,8 @@ class _DecodeGraph:
     graph: object = None
     logits: torch.Tensor | None = None
     kernels: int = 0              # kernel launches inside the graph
+    # per row: which state of which request's tables the staging buffer holds (None: no pages)
+    row_tables: list = field(default_factory=list)
 
 
 @dataclass
@@ -355,40 +357,61 @@ class ModelRunner:
 
     def _fill_graph_inputs(self, state: _DecodeGraph, entries: Sequence[StepEntry],
                            token_sources=None) -> None:
+        """The step's integers into the pinned staging buffer.  The block tables of a row are
+        written again only if the row's request or its tables changed since the last step: in
+        steady decoding a table changes once per page of tokens."""
         m = self.manager
         rows, off = state.rows, state.offsets
         buf = state.staging.numpy()
         g, pages, pt = len(m.groups), self.max_pages, m.page_tokens
-        buf[off[0]: off[1]] = 0                                         # token ids
-        buf[off[1]: off[2]] = -1                                        # position -1 marks padding
-        buf[off[2]: off[3]] = np.arange(rows, dtype=np.int32)           # request of each row
-        buf[off[3]: off[4]] = np.arange(rows, dtype=np.int32)
-        buf[off[4]: off[5]] = 0
-        buf[off[5]: off[6]] = 0
-        buf[off[6]: off[7]] = 0
-        buf[off[7]: off[8]] = np.arange(rows, dtype=np.int32)           # logits of every row
-        for i in range(g):
-            buf[off[8 + i]: off[9 + i]] = NO_PAGE
-            buf[off[8 + g + i]: off[9 + g + i]] = -1
+        n = len(entries)
+        if not state.row_tables:                                        # first use: everything is padding
+            state.row_tables = [None] * rows
+            buf[off[2]: off[3]] = np.arange(rows, dtype=np.int32)       # request of each row
+            buf[off[3]: off[4]] = np.arange(rows, dtype=np.int32)
+            buf[off[7]: off[8]] = np.arange(rows, dtype=np.int32)       # logits of every row
+            for i in range(g):
+                buf[off[8 + i]: off[9 + i]] = NO_PAGE
+        reqs = [m.get(e.request_id) for e in entries]
+        lengths = [req.length for req in reqs]
+        buf[off[0]: off[0] + n] = [int(e.tokens[0]) for e in entries]
+        buf[off[0] + n: off[1]] = 0
+        buf[off[1]: off[1] + n] = lengths
+        buf[off[1] + n: off[2]] = -1                                    # position -1 marks padding
+        buf[off[4]: off[4] + n] = 1
+        buf[off[4] + n: off[5]] = 0
+        buf[off[5]: off[5] + n] = lengths
+        buf[off[5] + n: off[6]] = 0
+        buf[off[6]: off[6] + n] = [req.state_slot for req in reqs]
+        buf[off[6] + n: off[7]] = 0
         src = off[8 + 2 * g]
         buf[src: src + rows] = -1                                       # token comes from the host
         if token_sources is not None:
-            buf[src: src + len(entries)] = token_sources
-        for r, e in enumerate(entries):
-            req = m.get(e.request_id)
-            buf[off[0] + r] = int(e.tokens[0])
-            buf[off[1] + r] = req.length
-            buf[off[4] + r] = 1
-            buf[off[5] + r] = req.length
-            buf[off[6] + r] = req.state_slot
+            buf[src: src + n] = token_sources
+        row_tables = state.row_tables
+        for i in range(g):
+            buf[off[8 + g + i] + n: off[9 + g + i]] = -1                # padding rows write nowhere
+        for r, req in enumerate(reqs):
+            held = (req.serial, req.version)
+            fresh = row_tables[r] != held
+            length = lengths[r]
             for i in range(g):
                 table = req.tables[i]
-                base = off[8 + i] + r * pages
-                buf[base: base + len(table)] = table
-                page = table[req.length // pt]
+                if fresh:
+                    base = off[8 + i] + r * pages
+                    buf[base: base + len(table)] = table
+                    buf[base + len(table): base + pages] = NO_PAGE
+                page = table[length // pt]
                 if page == NO_PAGE:
-                    raise StepError(f"request {e.request_id!r} writes to a page it gave back")
-                buf[off[8 + g + i] + r] = page * pt + req.length % pt
+                    raise StepError(f"request {entries[r].request_id!r} writes to a page it gave back")
+                buf[off[8 + g + i] + r] = page * pt + length % pt
+            row_tables[r] = held
+        for r in range(n, rows):                                        # rows that held a request last time
+            if row_tables[r] is not None:
+                for i in range(g):
+                    base = off[8 + i] + r * pages
+                    buf[base: base + pages] = NO_PAGE
+                row_tables[r] = None
 
     def _graph_step(self, entries: Sequence[StepEntry], copy: bool, token_sources=None,
                     previous_ids=None):
