@@ -109,6 +109,25 @@ def test_window_gives_pages_back_early():
     assert m.groups[0].pool.num_free == 16 and m.groups[1].pool.num_free == 16
 
 
+def test_every_change_of_a_table_shows_in_its_version():
+    """Whoever keeps a copy of a request's tables (the runner's staging buffers do) can tell by
+    (serial, version) whether it is stale: a new page, a page a window gave back and a new
+    admission under an old name all change it; a token inside a page does not."""
+    m = _manager(num_pages=8, page_tokens=4, specs=[PagedKVSpec(2, 16, window=6)])
+    a = m.admit("a")
+    seen = [(a.serial, a.version, [list(t) for t in a.tables])]
+    for length in range(1, 21):
+        assert m.reserve("a", length)
+        m.advance("a", length)
+        now = (a.serial, a.version, [list(t) for t in a.tables])
+        assert (now[:2] == seen[-1][:2]) == (now[2] == seen[-1][2]), f"length {length}"
+        seen.append(now)
+    assert len({s[:2] for s in seen}) > 5                       # pages came and went
+    m.release("a")
+    again = m.admit("a")
+    assert again.serial != a.serial
+
+
 def test_random_orders_lose_nothing():
     rng = random.Random(0)
     m = CacheManager([PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=10), FixedStateSpec((3,))],
