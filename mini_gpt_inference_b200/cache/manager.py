@@ -15,6 +15,7 @@ the tokens are now in the cache.
 
 from __future__ import annotations
 
+from collections.abc import Sequence
 from dataclasses import dataclass, field
 
 from .page_pool import PagePool, PoolError, SlotPool
@@ -44,6 +45,7 @@ class RequestCache:
     # counts their changes, so a copy of the tables kept elsewhere knows when it is stale
     serial: int = 0
     version: int = 0
+    capacity: int = 0                                 # tokens its pages have room for (every group)
 
 
 class CacheManager:
@@ -74,6 +76,8 @@ class CacheManager:
                 raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
         self.slots = SlotPool(max_requests)
         self.requests: dict[str, RequestCache] = {}
+        self._none_needed = (0,) * len(self.groups)
+        self._any_window = any(g.spec.window is not None for g in self.groups)
 
     # ---- sizes -------------------------------------------------------------------
     def pages_for(self, num_tokens: int) -> int:
@@ -104,7 +108,8 @@ class CacheManager:
         if self.slots.num_free == 0:
             raise CacheFullError("no state slot free")
         self._serial = getattr(self, "_serial", 0) + 1
-        req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups], self._serial)
+        req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups], self._serial,
+                           capacity=0 if self.groups else 1 << 30)
         self.requests[request_id] = req
         return req
 
@@ -117,11 +122,14 @@ class CacheManager:
         except KeyError:
             raise PoolError(f"request {request_id!r} is not admitted") from None
 
-    def pages_needed(self, request_id: str | None, new_length: int) -> list[int]:
+    def pages_needed(self, request_id: str | None, new_length: int) -> Sequence[int]:
         """Per group, pages that would have to be taken to reach ``new_length``."""
         if request_id is None or request_id not in self.requests:
             return [self.pages_for(new_length) for _ in self.groups]
-        return self._missing(self.requests[request_id], new_length)
+        req = self.requests[request_id]
+        if new_length <= req.capacity:
+            return self._none_needed
+        return self._missing(req, new_length)
 
     def can_reserve(self, request_id: str | None, new_length: int) -> bool:
         need = self.pages_needed(request_id, new_length)
@@ -142,6 +150,8 @@ class CacheManager:
         """Take the pages needed to hold ``new_length`` tokens.  All groups or none:
         returns False and changes nothing if any group is short."""
         req = self.get(request_id)
+        if new_length <= req.capacity:
+            return True
         need = self._missing(req, new_length)
         if any(n > group.pool.num_free for n, group in zip(need, self.groups)):
             return False
@@ -149,6 +159,7 @@ class CacheManager:
             if n:
                 req.tables[g].extend(group.pool.take(n))
                 req.version += 1
+        req.capacity = min(len(t) for t in req.tables) * self.page_tokens if req.tables else 1 << 30
         return True
 
     def advance(self, request_id: str, new_length: int) -> None:
@@ -156,10 +167,11 @@ class CacheManager:
         req = self.get(request_id)
         if new_length < req.length:
             raise PoolError("a request's cache cannot shrink; release and recompute instead")
-        for g in range(len(self.groups)):
-            if self.pages_for(new_length) > len(req.tables[g]):
-                raise PoolError(f"request {request_id!r} advanced past its reserved pages")
+        if new_length > req.capacity:
+            raise PoolError(f"request {request_id!r} advanced past its reserved pages")
         req.length = new_length
+        if not self._any_window:
+            return
         for g, group in enumerate(self.groups):
             first = self._first_live_page(group, new_length)
             table = req.tables[g]

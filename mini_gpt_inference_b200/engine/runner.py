@@ -173,19 +173,28 @@ class ModelRunner:
         m = self.manager
         need = [0] * len(m.groups)
         new_requests = 0
+        short = []                       # entries whose pages do not hold the new tokens yet
         for e in entries:
-            known = m.has(e.request_id)
-            new_requests += 0 if known else 1
-            end = self.length_of(e.request_id) + len(e.tokens)
-            for g, n in enumerate(m.pages_needed(e.request_id if known else None, end)):
+            req = m.requests.get(e.request_id)
+            if req is None:
+                new_requests += 1
+                end = len(e.tokens)
+            else:
+                end = req.length + len(e.tokens)
+                if end <= req.capacity:
+                    continue
+            short.append(e)
+            for g, n in enumerate(m.pages_needed(e.request_id if req is not None else None, end)):
                 need[g] += n
+        if not short:
+            return
         for g, n in enumerate(need):
             if n > m.groups[g].pool.num_free:
                 raise CacheFullError(
                     f"step needs {n} new pages in cache group {g}, {m.groups[g].pool.num_free} free")
         if new_requests > m.slots.num_free:
             raise CacheFullError("step admits more requests than there are free state slots")
-        for e in entries:
+        for e in short:
             if not m.has(e.request_id):
                 m.admit(e.request_id)
             ok = m.reserve(e.request_id, m.get(e.request_id).length + len(e.tokens))

@@ -139,12 +139,17 @@ class Scheduler:
                 return None
             rows.append(seq)
         need = [0] * len(self.cache.groups)
+        short = []
         for seq in rows:
-            for g, n in enumerate(self.cache.pages_needed(seq.request_id, seq.num_computed_tokens + 1)):
+            pages = self.cache.pages_needed(seq.request_id, seq.num_computed_tokens + 1)
+            if not any(pages):
+                continue
+            short.append(seq)
+            for g, n in enumerate(pages):
                 need[g] += n
         if any(n > group.pool.num_free for n, group in zip(need, self.cache.groups)):
             return None
-        for seq in rows:
+        for seq in short:
             ok = self.cache.reserve(seq.request_id, seq.num_computed_tokens + 1)
             assert ok
         return rows
