@@ -76,6 +76,7 @@ class CacheManager:
                 raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
         self.slots = SlotPool(max_requests)
         self.requests: dict[str, RequestCache] = {}
+        self._serial = 0                      # admissions so far
         self._none_needed = (0,) * len(self.groups)
         self._any_window = any(g.spec.window is not None for g in self.groups)
 
@@ -107,7 +108,7 @@ class CacheManager:
             raise PoolError(f"request {request_id!r} is already admitted")
         if self.slots.num_free == 0:
             raise CacheFullError("no state slot free")
-        self._serial = getattr(self, "_serial", 0) + 1
+        self._serial += 1
         req = RequestCache(request_id, self.slots.take_one(), 0, [[] for _ in self.groups], self._serial,
                            capacity=0 if self.groups else 1 << 30)
         self.requests[request_id] = req

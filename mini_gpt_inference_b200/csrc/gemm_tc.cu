@@ -157,12 +157,32 @@ struct __align__(8) Barriers {
     uint32_t failed;
 };
 
+// Where the QKV projection also leaves the key and value features of each token: its row of
+// the paged cache.  k_pages null: no such copy.
+struct KvSink {
+    bf16* k_pages;
+    bf16* v_pages;
+    const int* slots;                // [tokens] flat cache row, < 0: skip
+    int q_width, n_kv_head, head_dim, page_tokens;
+};
+
+// First element of feature n (>= q_width) of the token in cache row `slot`; *is_value says which array.
+__device__ __forceinline__ size_t kv_sink_index(const KvSink& k, int slot, int n, bool* is_value) {
+    const int kv_width = k.n_kv_head * k.head_dim;
+    const int f = n - k.q_width;
+    const int which = f / kv_width, fi = f - which * kv_width;
+    const int h = fi / k.head_dim, d = fi - h * k.head_dim;
+    const int page = slot / k.page_tokens, off = slot - page * k.page_tokens;
+    *is_value = which != 0;
+    return (((size_t)page * k.n_kv_head + h) * k.page_tokens + off) * k.head_dim + d;
+}
+
 template <int BN, bool SWAP>
 __global__ void __launch_bounds__(128)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                const float* __restrict__ bias, void* __restrict__ out_ptr, float* __restrict__ residual,
                int rows_p, int rows_q, int K, int ld_out, int epilogue, int out_bf16, int stages,
-               int* __restrict__ status) {
+               const KvSink sink, int* __restrict__ status) {
     constexpr int Q_TILE_BYTES = BN * BLOCK_K * 2;
     constexpr int STAGE_BYTES = P_TILE_BYTES + Q_TILE_BYTES;
     constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
@@ -177,7 +197,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     // The epilogue's operands are asked for while the main loop runs: the tile's slice of the
     // bias goes to shared memory, the thread's row of the residual stream is pulled towards L2.
     __shared__ __align__(16) float bias_tile[BN];
+    int cache_row = -1;                                   // of this thread's token (not SWAP)
     if (!SWAP) {
+        if (sink.k_pages != nullptr && p0 + tid < rows_p) cache_row = sink.slots[p0 + tid];
         for (int j = tid; j < BN; j += 128) bias_tile[j] = (bias && q0 + j < rows_q) ? bias[q0 + j] : 0.f;
         if (epilogue == EPI_RESIDUAL && p0 + tid < rows_p) {
             const float* rrow = residual + (size_t)(p0 + tid) * ld_out + q0;
@@ -311,6 +333,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
                                 o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
                                 dst[j] = o;
+                                if (cache_row >= 0 && qc + 8 * j >= sink.q_width) {
+                                    // eight features of one head (head sizes are multiples of 8 here)
+                                    bool is_value;
+                                    const size_t at = kv_sink_index(sink, cache_row, qc + 8 * j, &is_value);
+                                    *reinterpret_cast<uint4*>((is_value ? sink.v_pages : sink.k_pages) + at) = o;
+                                }
                             }
                         } else {
                             float4* dst = reinterpret_cast<float4*>((float*)out_ptr + row + qc);
@@ -325,8 +353,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 float v = __uint_as_float(r[j]) + bias_tile[c0 + j];
                                 if (epilogue == EPI_GELU) v = gelu_tanh(v);
                                 if (epilogue == EPI_RESIDUAL) residual[row + q] += v;
-                                else if (out_bf16) ((bf16*)out_ptr)[row + q] = __float2bfloat16_rn(v);
-                                else ((float*)out_ptr)[row + q] = v;
+                                else if (out_bf16) {
+                                    const bf16 hv = __float2bfloat16_rn(v);
+                                    ((bf16*)out_ptr)[row + q] = hv;
+                                    if (cache_row >= 0 && q >= sink.q_width) {
+                                        bool is_value;
+                                        const size_t at = kv_sink_index(sink, cache_row, q, &is_value);
+                                        (is_value ? sink.v_pages : sink.k_pages)[at] = hv;
+                                    }
+                                } else ((float*)out_ptr)[row + q] = v;
                             }
                         }
                     }
@@ -423,7 +458,8 @@ int tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out)
 
 template <int BN, bool SWAP>
 int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const float* bias, void* out,
-           float* residual, int ld_out, int epilogue, int out_bf16, int* status, cudaStream_t s) {
+           float* residual, int ld_out, int epilogue, int out_bf16, const KvSink& sink, int* status,
+           cudaStream_t s) {
     CUtensorMap map_p, map_q;
     int rc = tensor_map(p, rows_p, K, TILE_P, &map_p);
     if (rc != MG_OK) return rc;
@@ -446,7 +482,7 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
     }
     dim3 grid(ceil_div(rows_p, TILE_P), ceil_div(rows_q, BN));
     const cudaError_t le = mg_launch(gemm_tc_kernel<BN, SWAP>, grid, dim3(128), smem, s, true, map_p, map_q, bias, out,
-                                     residual, rows_p, rows_q, K, ld_out, epilogue, out_bf16, stages, status);
+                                     residual, rows_p, rows_q, K, ld_out, epilogue, out_bf16, stages, sink, status);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "gemm_tc: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("gemm_tc");
     return MG_OK;
@@ -459,7 +495,8 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
 // Returns MG_ERR_UNSUPPORTED (and launches nothing) for sizes or alignments TMA cannot take:
 // K not a multiple of 8, pointers not 16-byte aligned.
 MG_API int mg_linear_tc(const void* x, const void* w, const float* bias, void* out, float* residual, int M,
-                        int N, int K, int epilogue, int out_bf16, int* status, void* stream) {
+                        int N, int K, int epilogue, int out_bf16, void* k_pages, void* v_pages, const int* slots,
+                        int q_width, int n_kv_head, int head_dim, int page_tokens, int* status, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
@@ -467,15 +504,23 @@ MG_API int mg_linear_tc(const void* x, const void* w, const float* bias, void* o
     if (K % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
         return mg_set_error(MG_ERR_UNSUPPORTED, "linear: tensor-core path needs K %% 8 == 0 and 16-byte aligned operands");
     cudaStream_t s = (cudaStream_t)stream;
-    if (M <= 64) {
+    KvSink sink = {};
+    if (k_pages != nullptr) {
+        MG_REQUIRE(v_pages && slots && out_bf16 && epilogue == EPI_STORE, "linear: the key/value copy wants a bfloat16 store");
+        MG_REQUIRE(head_dim > 0 && head_dim % 8 == 0 && q_width % 8 == 0 && n_kv_head > 0 && page_tokens > 0 &&
+                       q_width + 2 * n_kv_head * head_dim == N,
+                   "linear: key/value copy with q_width=%d n_kv_head=%d head_dim=%d N=%d", q_width, n_kv_head, head_dim, N);
+        sink = KvSink{(bf16*)k_pages, (bf16*)v_pages, slots, q_width, n_kv_head, head_dim, page_tokens};
+    }
+    if (M <= 64 && k_pages == nullptr) {
         // few tokens: weight rows fill the 128-row side of the tile, the batch sits on the narrow side
         if (ceil_div(N, TILE_P) > 2147483647) return mg_set_error(MG_ERR_ARG, "linear: N too large");
-        if (M <= 16) return launch<16, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
-        if (M <= 32) return launch<32, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
-        return launch<64, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+        if (M <= 16) return launch<16, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, sink, status, s);
+        if (M <= 32) return launch<32, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, sink, status, s);
+        return launch<64, true>(w, x, N, M, K, bias, out, residual, N, epilogue, out_bf16, sink, status, s);
     }
     MG_REQUIRE(ceil_div(N, 64) <= 65535, "linear: N too large for one launch (%d)", N);
     if (N <= 64 || (long long)ceil_div(M, TILE_P) * ceil_div(N, 128) < 120)
-        return launch<64, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, status, s);
-    return launch<128, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, status, s);
+        return launch<64, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, sink, status, s);
+    return launch<128, false>(x, w, M, N, K, bias, out, residual, N, epilogue, out_bf16, sink, status, s);
 }

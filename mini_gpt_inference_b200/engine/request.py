@@ -7,8 +7,11 @@ cache, and a ``RequestOutput`` per step.  No torch in this module.
 
 from __future__ import annotations
 
+from array import array
 from dataclasses import dataclass, field
 from enum import Enum, auto
+
+import numpy as np
 
 from ..config.engine_config import SamplingParams
 
@@ -41,6 +44,9 @@ class SequenceState:
     # Tokens sampled on the device whose ids the host has not read yet (0 or 1): they count as
     # generated for scheduling, their values arrive one step later.
     num_inflight: int = 0
+    # The prompt as an int32 array, made when a portion of it is first asked for: portions are
+    # then views, and a long prompt is converted once instead of once per portion.
+    _prompt_array: np.ndarray | None = field(default=None, repr=False, compare=False)
 
     @property
     def request_id(self) -> str:
@@ -70,12 +76,19 @@ class SequenceState:
         p = self.prompt_len
         return self.request.prompt_token_ids[i] if i < p else self.output_token_ids[i - p]
 
-    def tokens(self, start: int, count: int) -> list[int]:
+    def tokens(self, start: int, count: int):
         """``count`` tokens from position ``start`` of prompt + generated, without building
         the whole list (a decoding step asks for one token of a long sequence)."""
         p = self.prompt_len
         end = start + count
         if end <= p:
+            if count > 16:
+                if self._prompt_array is None:
+                    try:
+                        self._prompt_array = np.frombuffer(array("i", self.request.prompt_token_ids), dtype=np.int32)
+                    except (OverflowError, TypeError):       # the step function names the bad id
+                        return self.request.prompt_token_ids[start:end]
+                return self._prompt_array[start:end]
             return self.request.prompt_token_ids[start:end]
         if start >= p:
             return self.output_token_ids[start - p: end - p]

@@ -15,6 +15,7 @@ pinned buffer and cross to the device in one copy.
 
 from __future__ import annotations
 
+from array import array
 from dataclasses import dataclass, field
 from typing import Sequence
 
@@ -59,7 +60,7 @@ class _Packed:
     """The integers of one step, packed on the host, and what the host itself needs of them."""
 
     buf: np.ndarray
-    offsets: np.ndarray
+    offsets: list
     total: int
     work_items: int
     q_len: list
@@ -141,8 +142,26 @@ class ModelRunner:
             self.manager.release(request_id)
 
     # ---- one step -----------------------------------------------------------------------
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    @staticmethod
+    def _as_int32(tokens) -> np.ndarray:
+        """A portion of a prompt as an int32 array (the one conversion of the list in a step)."""
+        if isinstance(tokens, np.ndarray):
+            if tokens.dtype == np.int32:
+                return tokens
+            if tokens.dtype.kind not in "iu" or (tokens.size and not (
+                    -2**31 <= int(tokens.min()) and int(tokens.max()) < 2**31)):
+                raise StepError("token ids must be integers that fit 32 bits")
+            return tokens.astype(np.int32)
+        try:
+            return np.frombuffer(array("i", tokens), dtype=np.int32)
+        except (OverflowError, TypeError) as err:
+            raise StepError(f"token ids must be integers that fit 32 bits ({err})") from None
+
+    def _validate(self, entries: Sequence[StepEntry]) -> list:
+        """Check the entries; returns, per entry, its tokens as an int32 array where the entry is
+        a portion of a prompt (None for the few tokens of a decoding request)."""
         seen = set()
+        arrays = []
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
@@ -151,11 +170,13 @@ class ModelRunner:
             if n == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
             if n > 16:                                   # a prompt portion: one pass in numpy
-                ids = np.asarray(e.tokens)
+                ids = self._as_int32(e.tokens)
                 low, high = int(ids.min()), int(ids.max())
                 bad = low if low < 0 else high if high >= self.vocab_size else None
+                arrays.append(ids)
             else:
                 bad = next((t for t in e.tokens if not (0 <= int(t) < self.vocab_size)), None)
+                arrays.append(None)
             if bad is not None:
                 raise StepError(f"token id {bad} of request {e.request_id!r} is outside "
                                 f"the vocabulary (0..{self.vocab_size - 1})")
@@ -168,6 +189,7 @@ class ModelRunner:
                 raise StepError(
                     f"request {e.request_id!r} would reach {end} tokens; the model's "
                     f"position table ends at {self.max_context}")
+        return arrays
 
     def _reserve(self, entries: Sequence[StepEntry]) -> None:
         m = self.manager
@@ -200,8 +222,9 @@ class ModelRunner:
             ok = m.reserve(e.request_id, m.get(e.request_id).length + len(e.tokens))
             assert ok, "pages were counted a moment ago"
 
-    def _pack(self, entries: Sequence[StepEntry]) -> _Packed:
-        """Pack the step's integers into one int32 buffer on the host."""
+    def _pack(self, entries: Sequence[StepEntry], arrays=None) -> _Packed:
+        """Pack the step's integers into one int32 buffer on the host.  ``arrays``: what
+        _validate returned for these entries, if it ran."""
         m = self.manager
         n_groups = len(m.groups)
         R = len(entries)
@@ -214,8 +237,10 @@ class ModelRunner:
         work = query_tiles(host_q_len, host_ctx, self._attention_slots)
         # layout of the packed int32 buffer
         sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [5 * len(work)]
-        offsets = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
-        total = int(offsets[-1])
+        offsets = [0]
+        for size in sizes:
+            offsets.append(offsets[-1] + size)
+        total = offsets[-1]
         buf = np.empty(max(total, 1), dtype=np.int32)
 
         def seg(i):
@@ -230,20 +255,32 @@ class ModelRunner:
         pt = m.page_tokens
         for r, e in enumerate(entries):
             req = m.get(e.request_id)
-            n = len(e.tokens)
+            n = host_q_len[r]
             q_start[r], q_len[r], ctx_before[r], state_slot[r] = row, n, req.length, req.state_slot
-            token_ids[row: row + n] = np.asarray(e.tokens, dtype=np.int32)
-            pos = np.arange(req.length, req.length + n, dtype=np.int32)
-            positions[row: row + n] = pos
+            ids = arrays[r] if arrays is not None else None
+            token_ids[row: row + n] = ids if ids is not None else np.asarray(e.tokens, dtype=np.int32)
             token_request[row: row + n] = r
+            if n == 1:
+                positions[row] = req.length
+                page_index, within = req.length // pt, req.length % pt
+            else:
+                pos = positions[row: row + n]
+                pos[:] = np.arange(req.length, req.length + n, dtype=np.int32)
+                page_index = pos // pt
+                within = pos - page_index * pt
             for g in range(n_groups):
-                table = np.asarray(req.tables[g], dtype=np.int32)
-                tables[g][r, :len(table)] = table
-                tables[g][r, len(table):] = NO_PAGE
-                pages = table[pos // pt]
-                if (pages == NO_PAGE).any():
+                held = req.tables[g]
+                tables[g][r, :len(held)] = held
+                tables[g][r, len(held):] = NO_PAGE
+                if n == 1:
+                    pages = held[page_index]
+                    bad = pages == NO_PAGE
+                else:
+                    pages = tables[g][r][page_index]
+                    bad = int(pages.min()) == NO_PAGE
+                if bad:
                     raise StepError(f"request {e.request_id!r} writes to a page it gave back")
-                slots[g][row: row + n] = pages * pt + pos % pt
+                slots[g][row: row + n] = pages * pt + within
             for k in e.want:
                 logit_rows[w] = row + int(k)
                 w += 1
@@ -456,8 +493,8 @@ class ModelRunner:
         return logits.clone() if copy else logits
 
     # ---- steps with prompt portions: eager, or replayed once their shape has come twice --------
-    def _prompt_step(self, entries: Sequence[StepEntry], copy: bool):
-        packed = self._pack(entries)
+    def _prompt_step(self, entries: Sequence[StepEntry], copy: bool, arrays=None):
+        packed = self._pack(entries, arrays)
         decode_only = all(n == 1 for n in packed.q_len)
         if not self.use_cuda_graphs or decode_only:
             return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
@@ -552,7 +589,7 @@ class ModelRunner:
         self._greedy_rows = 0
         if not entries:
             return None
-        self._validate(entries)
+        arrays = self._validate(entries)
         self._reserve(entries)
         if token_sources is not None and not (
                 self.can_feed_tokens_on_device(len(entries)) and all(len(e.tokens) == 1 for e in entries)):
@@ -561,7 +598,7 @@ class ModelRunner:
                 and all(len(e.tokens) == 1 for e in entries)):
             logits = self._graph_step(entries, copy, token_sources, previous_ids)
         else:
-            logits = self._prompt_step(entries, copy)
+            logits = self._prompt_step(entries, copy, arrays)
         for e in entries:
             self.manager.advance(e.request_id, self.manager.get(e.request_id).length + len(e.tokens))
         return logits

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "mg_linear_stream_parts": [_I],
     "mg_argmax_merge": [_P, _P, _P, _I, _I, _P],
     "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
-    "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _P, _P],

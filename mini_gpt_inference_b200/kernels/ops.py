@@ -295,12 +295,15 @@ class CudaOps:
                 self._run(code, "linear (mid batch)")
                 return kv_sink is not None
         if x.dtype == torch.bfloat16 and self.use_tensor_cores:
+            # the key/value copy moves 16 bytes at a time: head sizes that are multiples of 8
+            fused = kv_sink is not None and kv_sink[4] % 8 == 0
+            sink = self._sink_args(kv_sink if fused else None)
             code = self.lib.mg_linear_tc(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
-                                         m, n, k, epilogue, out_bf16, _ptr(self.status),
+                                         m, n, k, epilogue, out_bf16, *sink, _ptr(self.status),
                                          self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "linear (tensor cores)")
-                return False
+                return fused
         self._run(self.lib.mg_linear_simt(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                       m, n, k, epilogue, self._is_bf16(x), out_bf16, self._stream()),
               "linear")

@@ -74,23 +74,27 @@ def query_tiles(q_lens, ctx_befores, slots=None):
     less than half, longer parts (up to twice KEY_CHUNK) are tried, so that a second round of a
     few CTAs is not added to the first."""
 
-    def cut(limit):
-        runs = []
-        row = 0
-        for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
-            for b in range(0, n, QUERY_TILE):
-                rows = min(QUERY_TILE, n - b)
-                keys = before + b + rows
-                chunks = max(1, -(-keys // limit))
-                runs.append((-(keys / chunks), len(runs), r, row + b, rows, chunks))
-            row += n
-        runs.sort()
-        return [(r, row0, rows, c, chunks) for _, _, r, row0, rows, chunks in runs for c in range(chunks)]
+    runs = []                                     # (request, first row, rows, keys it may see)
+    row = 0
+    for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
+        for b in range(0, n, QUERY_TILE):
+            rows = min(QUERY_TILE, n - b)
+            runs.append((r, row + b, rows, before + b + rows))
+        row += n
 
-    items = cut(KEY_CHUNK)
-    if slots and slots < len(items) <= slots + slots // 2:
-        for limit in range(KEY_CHUNK + QUERY_TILE, 2 * KEY_CHUNK + 1, QUERY_TILE):
-            longer = cut(limit)
-            if len(longer) <= slots:
-                return longer
-    return items
+    def count(limit):
+        return sum(max(1, -(-keys // limit)) for _, _, _, keys in runs)
+
+    limit = KEY_CHUNK
+    items = count(limit)
+    if slots and slots < items <= slots + slots // 2:
+        for longer in range(KEY_CHUNK + QUERY_TILE, 2 * KEY_CHUNK + 1, QUERY_TILE):
+            if count(longer) <= slots:
+                limit = longer
+                break
+    cut = []
+    for i, (r, row0, rows, keys) in enumerate(runs):
+        chunks = max(1, -(-keys // limit))
+        cut.append((-(keys / chunks), i, r, row0, rows, chunks))
+    cut.sort()
+    return [(r, row0, rows, c, chunks) for _, _, r, row0, rows, chunks in cut for c in range(chunks)]

@@ -220,9 +220,13 @@ def test_streaming_projection_of_a_wide_matrix_takes_up_to_64_rows(ops, m):
     ops.check_status()
 
 
-@pytest.mark.parametrize("m", [1, 4, 8, 9, 40])
-def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m):
-    n_head, n_kv, d, pt, pages, k = 6, 2, 32, 8, 12, 96
+@pytest.mark.parametrize("heads", [(6, 2, 32), (3, 1, 48)])
+@pytest.mark.parametrize("m", [1, 4, 8, 9, 40, 70, 200, 333])
+def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m, heads):
+    # every projection kernel (small batch, mid batch, tensor cores) has the copy in its epilogue
+    n_head, n_kv, d = heads
+    pt, k = 8, 96
+    pages = max(12, m // pt + 3)
     width = (n_head + 2 * n_kv) * d
     x = randn(m, k, dtype=torch.bfloat16, seed=31)
     w = randn(width, k, dtype=torch.bfloat16, seed=32, scale=0.1)
