@@ -37,7 +37,7 @@ _SIGNATURES = {
     "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
     "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
                                  _F, _P, _P],
-    "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
+    "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
                                 ctypes.c_longlong, _I, _I, _F, _P, _P],
     "mg_copy_ints": [_P, _P, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],

@@ -390,15 +390,16 @@ class CudaOps:
                 and self.use_tensor_cores and self.use_prefill_tc):
             # portions of prompts: query tiles of 128 on the tensor cores
             self._want(work, torch.int32, "attn_work", 2)
-            # tiles cut along the keys leave partial rows in scratch, merged by a second kernel
+            # tiles cut along the keys leave partial rows in scratch; the part that finishes last merges them
             merge = int(ctx.max_ctx_after > KEY_CHUNK)
-            partial = None
+            partial = counters = None
             if merge:
                 floats = self.lib.mg_attention_prefill_scratch_floats(work.shape[0], n_head)
                 partial = torch.empty((floats,), dtype=torch.float32, device=self.device)
+                counters = self._counters(work.shape[0] * n_head)
             code = self.lib.mg_attention_prefill_tc(
                 _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(work), _ptr(table),
-                _ptr(ctx.positions), _ptr(out), _ptr(partial), merge, work.shape[0], n, n_head,
+                _ptr(ctx.positions), _ptr(out), _ptr(partial), _ptr(counters), merge, work.shape[0], n, n_head,
                 n_kv_head, head_dim,
                 cache.page_tokens, cache.k_pages.shape[0], table.shape[1], window, float(scale),
                 _ptr(self.status), self._stream())
