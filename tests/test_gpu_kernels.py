@@ -251,8 +251,10 @@ def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m, heads):
 
 
 def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window, lengths, q_lens,
-                    seed=0):
-    """Requests with `lengths[i]` tokens in total, of which the last `q_lens[i]` are new."""
+                    seed=0, spike=None):
+    """Requests with `lengths[i]` tokens in total, of which the last `q_lens[i]` are new.
+    spike = (request, key position, gain): that key is `gain` in every feature and the request's
+    queries of head 0 are all ones, so that its score stands far above every other."""
     g = torch.Generator().manual_seed(seed)
     R = len(lengths)
     max_pages = max(-(-n // page_tokens) for n in lengths) + 1
@@ -265,6 +267,8 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
     for r, n in enumerate(lengths):
         k = torch.randn(n, n_kv_head, head_dim, generator=g).to(dtype).float()
         v = torch.randn(n, n_kv_head, head_dim, generator=g).to(dtype).float()
+        if spike is not None and spike[0] == r:
+            k[spike[1]] = spike[2]
         k_all.append(k)
         v_all.append(v)
         for i in range(-(-n // page_tokens)):
@@ -278,6 +282,8 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
     scale = 1.0 / math.sqrt(head_dim)
     for r, (n, ql) in enumerate(zip(lengths, q_lens)):
         q = torch.randn(ql, n_head, head_dim, generator=g).to(dtype).float() * 2.0
+        if spike is not None and spike[0] == r:
+            q[:, 0] = 1.0
         for i in range(ql):
             p = n - ql + i
             lo = 0 if not window else max(0, p - window + 1)
@@ -321,12 +327,31 @@ def test_paged_attention_general(ops, dtype, n_head, n_kv_head, head_dim, page_t
     assert (got - want).abs().max() <= _tol(dtype, 1.0)
 
 
+@pytest.mark.parametrize("gain", [4.0, 9.0, 24.0])
+def test_prompt_attention_with_a_key_far_above_the_others(ops, gain):
+    """One key, hundreds of positions into the prompt, scores 8 * gain above the rest (head 0; other
+    heads see it at random heights, above and below).  The tensor-core kernel takes each row's
+    reference exponent from the first block and must move it when this key comes: at 9 the
+    weights leave the range it allows, at 24 they leave the range of 32-bit floats.  Queries
+    before the key must not see it; the tile is cut along the keys, so parts with references far
+    apart are merged."""
+    lengths, q_lens = [1000, 300], [700, 300]
+    got, want = _attention_case(ops, torch.bfloat16, 4, 2, 64, 16, 0, lengths, q_lens, seed=5,
+                                spike=(0, 611, gain))
+    ops.check_status()
+    assert not torch.isnan(got).any()
+    # rows that see the key return its value row, not an average of many: the results are as
+    # large as single values are (up to 4), and a bfloat16 result is that much coarser
+    assert (got - want).abs().max() <= _tol(torch.bfloat16, max(1.0, float(want.abs().max())))
+    assert float(want.abs().max()) > 2.0
+
+
 @pytest.mark.parametrize("n_head,n_kv_head,page_tokens,window", [
     (8, 8, 16, 0), (2, 2, 8, 0), (4, 1, 64, 0), (2, 2, 128, 0), (2, 1, 256, 0), (3, 3, 32, 0),
     (4, 2, 16, 33), (2, 2, 64, 200)])
 def test_prompt_portions_on_the_tensor_cores(ops, n_head, n_kv_head, page_tokens, window):
     """Portions of prompts with head size 64 in bfloat16 take the tcgen05 kernel: query tiles of
-    128 rows over key blocks of 128 from the pages; tiles that start anywhere in a request,
+    128 rows over key blocks of 64 from the pages; tiles that start anywhere in a request,
     tiles of one row, contexts that end at any place inside a block or a page."""
     lengths = [300, 129, 128, 1000, 1, 77, 513, 1300, 2048]
     q_lens = [300, 129, 5, 700, 1, 2, 257, 3, 130]
