@@ -277,6 +277,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     tc_fence_after();
     if (good) {
         const int p = p0 + warp * 32 + lane;             // this thread's row of D
+        // first element of the token's cache row for kv head 0: [page][kv head][offset in page][feature]
+        long long kv_row_base = 0;
+        if (cache_row >= 0) {
+            const int page = cache_row / sink.page_tokens;
+            kv_row_base = (long long)page * sink.n_kv_head * sink.page_tokens + (cache_row - page * sink.page_tokens);
+        }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
         constexpr int CHUNK = BN < 32 ? BN : 32;
 #pragma unroll 1
@@ -323,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             }
                         } else if (out_bf16) {
                             uint4* dst = reinterpret_cast<uint4*>((bf16*)out_ptr + row + qc);
+                            int kv_which = 0, kv_h = 0, kv_d = -1;        // -1: not worked out for this chunk yet
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 __nv_bfloat162 h0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]);
@@ -334,10 +341,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                                 o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
                                 dst[j] = o;
                                 if (cache_row >= 0 && qc + 8 * j >= sink.q_width) {
-                                    // eight features of one head (head sizes are multiples of 8 here)
-                                    bool is_value;
-                                    const size_t at = kv_sink_index(sink, cache_row, qc + 8 * j, &is_value);
-                                    *reinterpret_cast<uint4*>((is_value ? sink.v_pages : sink.k_pages) + at) = o;
+                                    // eight features of one head (head sizes are multiples of 8 here); the
+                                    // place of the chunk's first such group is worked out once, the groups
+                                    // after it step through the head, the heads and from keys to values
+                                    if (kv_d < 0) {
+                                        const int f = qc + 8 * j - sink.q_width, kv_width = sink.n_kv_head * sink.head_dim;
+                                        kv_which = f >= kv_width ? 1 : 0;
+                                        const int fi = f - kv_which * kv_width;
+                                        kv_h = fi / sink.head_dim;
+                                        kv_d = fi - kv_h * sink.head_dim;
+                                    } else {
+                                        kv_d += 8;
+                                        if (kv_d >= sink.head_dim) {
+                                            kv_d = 0;
+                                            if (++kv_h == sink.n_kv_head) { kv_h = 0; kv_which = 1; }
+                                        }
+                                    }
+                                    const size_t at = ((size_t)kv_row_base + (size_t)kv_h * sink.page_tokens) * sink.head_dim + kv_d;
+                                    *reinterpret_cast<uint4*>((kv_which ? sink.v_pages : sink.k_pages) + at) = o;
                                 }
                             }
                         } else {
