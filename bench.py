@@ -2,6 +2,7 @@
 """Serving benchmark: decode tokens per second of the GPT-2 style 50M decoder on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--sizes 50m|gpt2-small|gpt2-xl] [--layers L] [--batch B] [--context S]
 
 A "step" is one decode step: every request of the batch advances by one token.  The default
 run has the layer sizes of the 50M configuration (8 layers, width 512, 8 heads of 64, MLP
@@ -15,6 +16,9 @@ bfloat16, a batch of 8 and contexts that end at 2048 tokens.  One JSON line is p
 * ``e2e``: the same through ``LLMEngine.step()`` with host token ids in and out, wall clock;
 * ``prefill``: one 2,048-token prompt; ``roofline``: bytes a decode step must read / its time;
 * ``points``: decode at batch 1 and 64.
+
+``--sizes`` runs the same measurement at the layer sizes of GPT-2 small or GPT-2 XL (position
+table of 1,024: the prefill step is then two whole prompts of 1,024 tokens).
 
 The reference's own benchmark times decode the same way — prefill untimed, then per-token
 steps (bench/bench_hardware.py:96-128) — on its static cache; ``--impl reference`` runs that
@@ -35,8 +39,18 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-MODEL = dict(vocab_size=50304, n_positions=2048, n_layer=8, n_head=8, n_embd=512, n_inner=2048,
-             bias=True, layer_norm_epsilon=1e-5)
+# Layer sizes by name.  The default is the 50M model; the two others are the same architecture at
+# the layer sizes of GPT-2 small and GPT-2 XL (random weights), for measurements at further sizes.
+SIZES = {
+    "50m": dict(vocab_size=50304, n_positions=2048, n_layer=8, n_head=8, n_embd=512, n_inner=2048,
+                bias=True, layer_norm_epsilon=1e-5),
+    "gpt2-small": dict(vocab_size=50257, n_positions=1024, n_layer=12, n_head=12, n_embd=768,
+                       n_inner=3072, bias=True, layer_norm_epsilon=1e-5),
+    "gpt2-xl": dict(vocab_size=50257, n_positions=1024, n_layer=48, n_head=25, n_embd=1600,
+                    n_inner=6400, bias=True, layer_norm_epsilon=1e-5),
+}
+MODEL_NAMES = {"50m": "gpt2-style-50M", "gpt2-small": "gpt2-small-sizes", "gpt2-xl": "gpt2-xl-sizes"}
+MODEL = SIZES["50m"]
 BASELINE_T4_DECODE_B8 = 1671.8      # tok/s, Tesla T4 fp16, context 8..40 (docs/BENCHMARKS.md:622)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 PREFILL_TOKENS = 2048
@@ -49,8 +63,11 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=MODEL["n_positions"])
-    ap.add_argument("--layers", type=int, default=MODEL["n_layer"],
+    ap.add_argument("--sizes", choices=sorted(SIZES), default="50m",
+                    help="layer sizes: the 50M model (default) or the same architecture at the "
+                         "layer sizes of GPT-2 small / GPT-2 XL")
+    ap.add_argument("--context", type=int, default=None, help="default: the position table's length")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
@@ -58,7 +75,12 @@ def parse_args():
     ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial)")
-    return ap.parse_args()
+    args = ap.parse_args()
+    global MODEL
+    MODEL = SIZES[args.sizes]
+    args.context = args.context or MODEL["n_positions"]
+    args.layers = args.layers or MODEL["n_layer"]
+    return args
 
 
 def peaks() -> tuple[dict, str]:
@@ -138,7 +160,7 @@ def build_engine(args, batch: int, max_tokens_per_request: int):
     from mini_gpt_inference_b200.weights import random_tensors
 
     cfg = GPTConfig.from_dict({**MODEL, "n_layer": args.layers})
-    key = (args.layers, args.dtype)
+    key = (args.sizes, args.layers, args.dtype)
     if key not in build_engine.cache:
         model = DecoderModel(lookup(cfg.architecture).describe(cfg))
         store = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -154,6 +176,11 @@ def build_engine(args, batch: int, max_tokens_per_request: int):
 
 
 build_engine.cache = {}
+
+
+def metric_name(args) -> str:
+    what = "GPT-2 style 50M" if args.sizes == "50m" else f"{args.sizes} layer sizes"
+    return f"decode tok/s at batch {args.batch}, context {args.context} ({what}, random weights)"
 
 
 def weight_bytes(cfg, dtype_bytes: int) -> int:
@@ -265,28 +292,33 @@ def e2e_decode(args, batch: int, steps: int, warmup: int):
 
 
 def prefill_once(args):
+    """One step of 2,048 prompt tokens: one prompt where the position table holds it, else as
+    many whole prompts of the table's length as make 2,048 tokens (two of 1,024)."""
     import torch
 
     from mini_gpt_inference_b200.engine.runner import StepEntry
 
-    cfg, engine = build_engine(args, 1, PREFILL_TOKENS)
+    length = min(PREFILL_TOKENS, MODEL["n_positions"])
+    count = PREFILL_TOKENS // length
+    cfg, engine = build_engine(args, count, length)
     runner = engine.runner
     gen = torch.Generator().manual_seed(3)
-    prompt = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (length,), generator=gen).tolist() for _ in range(count)]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
     times = []
     for rep in range(6):
         flush.zero_()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
-        logits = runner.step([StepEntry("p", prompt, [PREFILL_TOKENS - 1])])
+        logits = runner.step([StepEntry(f"p{i}", p, [length - 1]) for i, p in enumerate(prompts)])
         end.record()
         torch.cuda.synchronize()
-        assert logits.shape == (1, cfg.vocab_size)
-        runner.finish("p")
+        assert logits.shape == (count, cfg.vocab_size)
+        for i in range(count):
+            runner.finish(f"p{i}")
         if rep >= 2:
             times.append(start.elapsed_time(end))
-    return cfg, statistics.median(times)
+    return cfg, statistics.median(times), length, count
 
 
 def run_ours(args) -> dict:
@@ -295,7 +327,7 @@ def run_ours(args) -> dict:
     pk, peak_source = peaks()
     dtype_bytes = 2 if args.dtype == "bfloat16" else 4
     if args.only == "prefill":
-        cfg, pre_ms = prefill_once(args)
+        cfg, pre_ms, _, _ = prefill_once(args)
         return {"impl": "ours", "partial": "prefill only", "prefill": {
             "value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4)}}
     if args.only == "decode":
@@ -311,7 +343,7 @@ def run_ours(args) -> dict:
     achieved = step_bytes / (ms * 1e-3) / 1e9
     e2e_value, e2e_ms, h2d, d2h = e2e_decode(args, args.batch, args.steps, args.warmup)
     line = {
-        "metric": "decode tok/s at batch 8, context 2048 (GPT-2 style 50M, random weights)",
+        "metric": metric_name(args),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms, 4), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": round(value / BASELINE_T4_DECODE_B8, 2),
@@ -319,7 +351,7 @@ def run_ours(args) -> dict:
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic",
         "impl": "ours",
         "config": {
-            "model": "gpt2-style-50M", "global_batch": args.batch, "seq_len": args.context,
+            "model": MODEL_NAMES[args.sizes], "global_batch": args.batch, "seq_len": args.context,
             "parallelism": "single-gpu", "n_layer": args.layers, "n_layer_config": MODEL["n_layer"],
             "n_embd": cfg.n_embd, "n_head": cfg.n_head, "head_dim": cfg.head_dim,
             "n_inner": cfg.n_inner, "vocab_size": cfg.vocab_size, "n_positions": cfg.n_positions,
@@ -341,11 +373,11 @@ def run_ours(args) -> dict:
             _, t, _, _, _ = device_decode(args, b, min(args.steps, 64), max(3, min(args.warmup, 8)))
             points[f"decode_b{b}"] = round(b / (statistics.fmean(t) * 1e-3), 1)
         line["points"] = points
-        _, pre_ms = prefill_once(args)
-        flops = prefill_flops(cfg, PREFILL_TOKENS)
+        _, pre_ms, pre_len, pre_count = prefill_once(args)
+        flops = pre_count * prefill_flops(cfg, pre_len)
         peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else None
         line["prefill"] = {"value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS,
-                           "ms": round(pre_ms, 4),
+                           "prompts": pre_count, "ms": round(pre_ms, 4),
                            "frac": round(flops / (pre_ms * 1e-3) / (peak * 1e12), 4) if peak else None,
                            "of": peak_source}
     torch.cuda.synchronize()
@@ -412,12 +444,12 @@ def run_reference(args) -> dict:
         assert host_ids.shape == (batch, 1)
     ms = statistics.fmean(times)
     return {
-        "metric": "decode tok/s at batch 8, context 2048 (GPT-2 style 50M, random weights)",
+        "metric": metric_name(args),
         "value": round(batch / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps,
         "warmup": warmup, "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": round(batch / (ms * 1e-3) / BASELINE_T4_DECODE_B8, 2),
         "dtype": "bf16" if args.dtype == "bfloat16" else "fp32", "data": "synthetic", "impl": "reference",
-        "config": {"model": "gpt2-style-50M", "global_batch": batch, "seq_len": args.context,
+        "config": {"model": MODEL_NAMES[args.sizes], "global_batch": batch, "seq_len": args.context,
                    "parallelism": "single-gpu", "n_layer": args.layers, "n_layer_config": MODEL["n_layer"],
                    "path": "GPT + StaticKVCache, eager (bench/bench_hardware.py method)",
                    "l2": "flushed between timed steps (256 MiB write)"},
