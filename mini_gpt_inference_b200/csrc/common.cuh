@@ -51,6 +51,76 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Four consecutive outputs at once (16 bytes of 32-bit values, 8 bytes of bfloat16).
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// LayerNorm of one row by one warp, for any width that is a multiple of 4: the row is read three
+// times in chunks of 1024 values with 16-byte loads (the second and third time it comes from the
+// L1 cache): the mean, then the biased variance of the centred values, then the affine map.
+// gain and shift (shift may be null) in global or shared memory; src, gain, shift and dst
+// 16-byte aligned (dst 8 for bfloat16).  A row's result depends on nothing but the row.
+template <typename TOut>
+__device__ __forceinline__ void layernorm_row_chunked(const float* src, int width, const float* gain, const float* shift,
+                                                      float eps, TOut* dst, int lane) {
+    const float4* src4 = reinterpret_cast<const float4*>(src);
+    const int n4 = width / 4;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    float sum = 0.f;
+    for (int i0 = 0; i0 < n4; i0 += 256) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = i0 + lane + 32 * i;
+            v[i] = c < n4 ? src4[c] : zero;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = warp_sum(sum) / (float)width;
+    float sq = 0.f;
+    for (int i0 = 0; i0 < n4; i0 += 256) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = i0 + lane + 32 * i;
+            v[i] = c < n4 ? src4[c] : make_float4(mean, mean, mean, mean);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+            sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    for (int i0 = 0; i0 < n4; i0 += 256) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = i0 + lane + 32 * i;
+            v[i] = c < n4 ? src4[c] : zero;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = i0 + lane + 32 * i;
+            if (c < n4) {
+                const float4 gn = reinterpret_cast<const float4*>(gain)[c];
+                const float4 sh = shift ? reinterpret_cast<const float4*>(shift)[c] : zero;
+                store4(dst + 4 * c, (v[i].x - mean) * rstd * gn.x + sh.x, (v[i].y - mean) * rstd * gn.y + sh.y,
+                       (v[i].z - mean) * rstd * gn.z + sh.z, (v[i].w - mean) * rstd * gn.w + sh.w);
+            }
+        }
+    }
+}
+
 // tanh-GELU evaluated in 32-bit: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))).
 __device__ __forceinline__ float gelu_tanh(float u) {
     const float k = 0.7978845608028654f;  // sqrt(2/pi)

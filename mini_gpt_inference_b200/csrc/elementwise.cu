@@ -51,17 +51,6 @@ MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void*
 // ---- LayerNorm -----------------------------------------------------------------------------
 // One warp per row.  Mean, then the biased variance of the centred values, then the affine
 // map; all in 32-bit.  y = (x - mean) * rsqrt(var + eps) * gain (+ shift).
-__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
-    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
-}
-__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
-    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
-    uint2 raw;
-    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
-    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(p) = raw;
-}
-
 template <typename TOut>
 __global__ void layernorm_kernel(const float* __restrict__ x, const float* __restrict__ gain,
                                  const float* __restrict__ shift, TOut* __restrict__ y,
@@ -111,6 +100,10 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const float* __res
                 store4(yr + c, (v[i].x - mean) * rstd * gn[i].x + sh[i].x, (v[i].y - mean) * rstd * gn[i].y + sh[i].y,
                        (v[i].z - mean) * rstd * gn[i].z + sh[i].z, (v[i].w - mean) * rstd * gn[i].w + sh[i].w);
             }
+        return;
+    }
+    if (width % 4 == 0 && (((uintptr_t)x | (uintptr_t)gain | (uintptr_t)shift | (uintptr_t)y) & 15) == 0) {
+        layernorm_row_chunked<TOut>(xr, width, gain, shift, eps, yr, lane);     // wide rows, 16-byte loads
         return;
     }
     float sum = 0.f;

@@ -116,8 +116,9 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     if (a.x32 != nullptr && a.row_index != nullptr && warp < a.M) first_row = a.row_index[warp];
     // Gain and shift of the LayerNorm prologue are weights too: they go to shared memory now, so
     // that the normalisation does not wait for them after the statistics.
-    const bool ln_fast = a.x32 != nullptr && K % 128 == 0 && K <= 1024;
-    if (ln_fast) {
+    const bool ln = a.x32 != nullptr;
+    const bool ln_fast = ln && K % 128 == 0 && K <= 1024;                 // the row fits a warp's registers
+    if (ln) {
         for (int i = tid; i < K / 4; i += THREADS) {
             reinterpret_cast<float4*>(gain_s)[i] = reinterpret_cast<const float4*>(a.gain)[i];
             reinterpret_cast<float4*>(shift_s)[i] =
@@ -127,7 +128,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     // Weights and bias do not depend on the kernel before this one; everything below does.
     pdl_trigger();
     pdl_wait();
-    if (ln_fast) __syncthreads();
+    if (ln) __syncthreads();
 
     // ---- stage the activations (with the LayerNorm prologue if asked) as bfloat16 ----
     // Rows at and past M stay as they are: a token's results depend on its own row only.
@@ -168,20 +169,8 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
                     }
                 continue;
             }
-            float sum = 0.f;
-            for (int c = lane; c < K; c += 32) sum += src[c];
-            const float mean = warp_sum(sum) / (float)K;
-            float sq = 0.f;
-            for (int c = lane; c < K; c += 32) {
-                const float d = src[c] - mean;
-                sq += d * d;
-            }
-            const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + a.eps);
-            for (int c = lane; c < K; c += 32) {
-                float v = (src[c] - mean) * rstd * a.gain[c];
-                if (a.shift) v += a.shift[c];
-                reinterpret_cast<bf16*>(dst)[c] = __float2bfloat16_rn(v);
-            }
+            // longer or odd rows: three passes in chunks (K is a multiple of 8 here), gain and shift from shared memory
+            layernorm_row_chunked<bf16>(src, K, gain_s, a.shift ? shift_s : nullptr, a.eps, reinterpret_cast<bf16*>(dst), lane);
         }
     } else {
         const int chunks8 = K / 8;

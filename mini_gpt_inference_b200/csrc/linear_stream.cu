@@ -41,7 +41,9 @@ struct StreamArgs {
     LinearEpilogue ep;
     int M, N, K;
     int tiles_per_cta;
-    int stages;                      // tiles a warp has in flight
+    int stages;                      // copies (a tile's rows over one K chunk) a warp has in flight
+    int kc;                          // K chunk: columns of a tile that one stage holds (a multiple of 32, or K)
+    int nchunks;                     // ceil(K / kc)
     float* amax_v;                   // [M][gridDim.x * WARPS] candidates of the greedy argmax, or null
     int* amax_i;
     int amax_limit;
@@ -75,8 +77,10 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
     constexpr int MG = MT <= 16 ? 1 : MT / 16;                          // groups of 16 tokens (one mma each)
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const int K = a.K;
-    const int xstride = K * 2 + XPAD;                                   // bytes per row, activations and weights alike
-    const int tile_bytes = TILE_N * xstride;
+    const int xstride = K * 2 + XPAD;                                   // bytes per row of activations
+    const int kc = a.kc, nch = a.nchunks;
+    const int wstride = kc * 2 + XPAD;                                  // bytes per weight row of a stage
+    const int tile_bytes = TILE_N * wstride;
     uint8_t* xs = smem_raw;                                             // [MT][xstride]
     float* gain_s = reinterpret_cast<float*>(xs + (size_t)MT * xstride);
     float* shift_s = gain_s + K;
@@ -91,21 +95,24 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
     const int tile_end = min(total_tiles, tile_begin + a.tiles_per_cta);
     // this warp takes tiles tile_begin + warp, + WARPS, ...
     const int n_mine = tile_begin + warp < tile_end ? (tile_end - tile_begin - warp + WARPS - 1) / WARPS : 0;
+    const int n_items = n_mine * nch;                                   // (tile, K chunk), chunks of a tile in a row
 
     // Ask for tile j of this warp (the whole warp calls): lane 0 announces the bytes, then lane r
     // asks for weight row r with a bulk copy of its own: one instruction for the eight copies
     // (issued one after the other by a single lane they cost the warp a microsecond a tile).
     auto issue = [&](int j) {
-        const int tile = tile_begin + warp + j * WARPS, s = j % stages;
+        const int jt = j / nch, ch = j - jt * nch;
+        const int tile = tile_begin + warp + jt * WARPS, s = j % stages;
         const int rows = min(TILE_N, a.N - tile * TILE_N);
+        const int k0 = ch * kc, len = min(kc, K - k0);                  // len * 2 is a multiple of 16 bytes (K % 8 == 0)
         const uint32_t bar = smem_u32(&bars[warp][s]);
         if (lane == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)rows * K * 2) : "memory");
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"((uint32_t)rows * len * 2) : "memory");
         __syncwarp();
         if (lane < rows)
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                         ::"r"(smem_u32(my_ring + (size_t)s * tile_bytes + (size_t)lane * xstride)),
-                           "l"(a.w + ((size_t)tile * TILE_N + lane) * K), "r"((uint32_t)K * 2), "r"(bar)
+                         ::"r"(smem_u32(my_ring + (size_t)s * tile_bytes + (size_t)lane * wstride)),
+                           "l"(a.w + ((size_t)tile * TILE_N + lane) * K + k0), "r"((uint32_t)len * 2), "r"(bar)
                          : "memory");
     };
     if (lane == 0) {
@@ -113,12 +120,13 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();
-    for (int j = 0; j < stages && j < n_mine; ++j) issue(j);           // weights depend on no kernel before
+    for (int j = 0; j < stages && j < n_items; ++j) issue(j);           // weights depend on no kernel before
     // Which rows to normalise, and gain and shift, are inputs and weights as well.
     int first_row = warp;
     if (a.x32 != nullptr && a.row_index != nullptr && warp < a.M) first_row = a.row_index[warp];
-    const bool ln_fast = a.x32 != nullptr && K % 128 == 0 && K <= 1024;
-    if (ln_fast) {
+    const bool ln = a.x32 != nullptr;
+    const bool ln_fast = ln && K % 128 == 0 && K <= 1024;                 // the row fits a warp's registers
+    if (ln) {
         for (int i = tid; i < K / 4; i += THREADS) {
             reinterpret_cast<float4*>(gain_s)[i] = reinterpret_cast<const float4*>(a.gain)[i];
             reinterpret_cast<float4*>(shift_s)[i] =
@@ -127,7 +135,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
     }
     pdl_trigger();
     pdl_wait();
-    if (ln_fast) __syncthreads();
+    if (ln) __syncthreads();
 
     // ---- stage the activations (with the LayerNorm prologue if asked) as bfloat16, once per CTA ----
     if (a.x32 != nullptr) {
@@ -166,20 +174,8 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
                     }
                 continue;
             }
-            float sum = 0.f;
-            for (int c = lane; c < K; c += 32) sum += src[c];
-            const float mean = warp_sum(sum) / (float)K;
-            float sq = 0.f;
-            for (int c = lane; c < K; c += 32) {
-                const float d = src[c] - mean;
-                sq += d * d;
-            }
-            const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + a.eps);
-            for (int c = lane; c < K; c += 32) {
-                float v = (src[c] - mean) * rstd * a.gain[c];
-                if (a.shift) v += a.shift[c];
-                reinterpret_cast<bf16*>(dst)[c] = __float2bfloat16_rn(v);
-            }
+            // longer or odd rows: three passes in chunks (K is a multiple of 8 here), gain and shift from shared memory
+            layernorm_row_chunked<bf16>(src, K, gain_s, a.shift ? shift_s : nullptr, a.eps, reinterpret_cast<bf16*>(dst), lane);
         }
     } else {
         const int chunks8 = K / 8;
@@ -193,7 +189,6 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
 
     // ---- every warp walks its tiles ----
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
-    const int kblocks = (K + 31) / 32;
     float best_v[MG][2];                                                 // tokens 16 mg + g and 16 mg + g + 8
     int best_i[MG][2];
 #pragma unroll
@@ -204,23 +199,29 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
             best_i[mg][h] = 0x7fffffff;
         }
     bool good = true;
-    for (int j = 0; j < n_mine; ++j) {
-        const int tile = tile_begin + warp + j * WARPS, s = j % stages;
+    float c[MG][4];                                                     // a tile's sums, kept over its K chunks
+    for (int j = 0; j < n_items; ++j) {
+        const int jt = j / nch, ch = j - jt * nch;
+        const int tile = tile_begin + warp + jt * WARPS, s = j % stages;
         if (!mbar_wait(smem_u32(&bars[warp][s]), (uint32_t)(j / stages) & 1u)) {
             good = false;
             break;                                                      // uniform in the warp
         }
-        const uint8_t* wrow = my_ring + (size_t)s * tile_bytes + (size_t)g * xstride;
-        float c[MG][4];
+        const uint8_t* wrow = my_ring + (size_t)s * tile_bytes + (size_t)g * wstride;
+        const int k0 = ch * kc, len = min(kc, K - k0);
+        const int kblocks = (len + 31) / 32;
+        if (ch == 0) {
 #pragma unroll
-        for (int mg = 0; mg < MG; ++mg)
+            for (int mg = 0; mg < MG; ++mg)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) c[mg][i] = 0.f;
+                for (int i = 0; i < 4; ++i) c[mg][i] = 0.f;
+        }
 #pragma unroll 2
         for (int b = 0; b < kblocks; ++b) {
-            const int k = b * 32 + 8 * t;
-            const bool in = k < K;
-            const uint4 wv = in ? *reinterpret_cast<const uint4*>(wrow + k * 2) : zero4;
+            const int kl = b * 32 + 8 * t;                              // column inside the chunk
+            const bool in = kl < len;
+            const int k = k0 + kl;
+            const uint4 wv = in ? *reinterpret_cast<const uint4*>(wrow + kl * 2) : zero4;
 #pragma unroll
             for (int mg = 0; mg < MG; ++mg) {
                 const uint4 x0 = in ? *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 16 + g) * xstride + k * 2) : zero4;
@@ -231,10 +232,11 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
             }
         }
         __syncwarp();                                                   // every lane has read the stage
-        if (j + stages < n_mine) {                                      // uniform in the warp
+        if (j + stages < n_items) {                                     // uniform in the warp
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             issue(j + stages);
         }
+        if (ch != nch - 1) continue;                                    // the tile's other chunks first
         // c0, c1: token 16 mg + g, rows 2t and 2t+1 of the tile; c2, c3: token 16 mg + g + 8
 #pragma unroll
         for (int mg = 0; mg < MG; ++mg)
@@ -294,7 +296,8 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
 // CTAs and tiles per CTA for an [N, K] matrix on a device of `sms` SMs.
 int stream_split(int N, int sms, int* tiles_per_cta) {
     const int tiles = (N + TILE_N - 1) / TILE_N;
-    int ctas = sms < (tiles + WARPS - 1) / WARPS ? sms : (tiles + WARPS - 1) / WARPS;
+    // (a matrix of fewer tiles than the device has warps spreads over all SMs, with idle warps)
+    int ctas = sms < tiles ? sms : tiles;
     if (ctas < 1) ctas = 1;
     const int per = (tiles + ctas - 1) / ctas;
     *tiles_per_cta = per;
@@ -323,12 +326,18 @@ MG_API int mg_linear_stream_parts(int N) {
 }
 
 // As mg_linear_skinny (same operands, prologue, epilogues and greedy choice), for wide matrices.
-// Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 64, K % 8 != 0, operands that are not
-// 16-byte aligned, a key/value sink, or rows too long for two stages per warp in shared memory.
+// A stage holds a tile's rows whole where two such stages per warp fit beside the activations;
+// longer rows are cut into K chunks (four stages per warp), a tile's sums staying in registers from
+// chunk to chunk (at most `max_chunks` of them: every row copy then moves a few hundred bytes, and
+// the copies' own cost shows).  Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 64,
+// K % 8 != 0, operands that are not 16-byte aligned, rows that need more chunks than allowed, or
+// activations that leave no room for stages of 64 columns.
 MG_API int mg_linear_stream(const void* x, const float* x32, const int* row_index, const float* gain,
                             const float* shift, float eps, const void* w, const float* bias, void* out,
-                            float* residual, int M, int N, int K, int epilogue, int out_bf16, float* amax_v,
-                            int* amax_i, int amax_limit, int* status, void* stream) {
+                            float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
+                            void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
+                            int page_tokens, float* amax_v, int* amax_i, int amax_limit, int max_chunks,
+                            int* status, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0 && status != nullptr, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
@@ -342,7 +351,18 @@ MG_API int mg_linear_stream(const void* x, const float* x32, const int* row_inde
     const size_t budget = 226 * 1024;
     int stages = fixed < budget ? (int)((budget - fixed) / ((size_t)WARPS * TILE_N * xstride)) : 0;
     if (stages > 4) stages = 4;
-    if (sms <= 0 || M > MAX_M || K % 8 != 0 || stages < 2 || ((uintptr_t)w & 15) || (x && ((uintptr_t)x & 15)) ||
+    int kc = K;
+    if (stages < 2 && fixed < budget) {
+        // four stages of K chunks: TILE_N * (2 kc + XPAD) bytes each, kc a multiple of 32
+        const long long per_stage = (long long)((budget - fixed) / ((size_t)WARPS * 4 * TILE_N));
+        kc = (int)((per_stage - XPAD) / 2) / 32 * 32;
+        stages = kc >= 64 ? 4 : 0;
+    }
+    const int nchunks = kc > 0 ? (K + kc - 1) / kc : 0;
+    MG_REQUIRE(k_pages == nullptr || (out_bf16 && epilogue == EPI_STORE && slots && v_pages && head_dim > 0 &&
+                                      n_kv_head > 0 && page_tokens > 0 && N == q_width + 2 * n_kv_head * head_dim),
+               "linear: bad key/value sink");
+    if (sms <= 0 || M > MAX_M || K % 8 != 0 || stages < 2 || nchunks > max_chunks || ((uintptr_t)w & 15) || (x && ((uintptr_t)x & 15)) ||
         (x32 && !x && ((uintptr_t)x32 & 15)) || (gain && ((uintptr_t)gain & 15)) || (shift && ((uintptr_t)shift & 15)))
         return mg_set_error(MG_ERR_UNSUPPORTED, "linear (stream): needs M <= 64, K %% 8 == 0, aligned operands, rows that fit");
     StreamArgs a;
@@ -350,13 +370,15 @@ MG_API int mg_linear_stream(const void* x, const float* x32, const int* row_inde
     a.w = (const bf16*)w; a.M = M; a.N = N; a.K = K;
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
-    a.ep.k_pages = nullptr; a.ep.v_pages = nullptr; a.ep.slots = nullptr;
-    a.ep.q_width = 0; a.ep.n_kv_head = 0; a.ep.head_dim = 0; a.ep.page_tokens = 0;
+    a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
     a.amax_v = amax_v; a.amax_i = amax_i; a.amax_limit = (amax_limit <= 0 || amax_limit > N) ? N : amax_limit;
     a.status = status;
     a.stages = stages;
+    a.kc = kc;
+    a.nchunks = nchunks;
     const int grid = stream_split(N, sms, &a.tiles_per_cta);
-    const size_t smem = fixed + (size_t)WARPS * stages * TILE_N * xstride;
+    const size_t smem = fixed + (size_t)WARPS * stages * TILE_N * ((size_t)kc * 2 + XPAD);
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(linear_stream_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)budget);

@@ -29,7 +29,8 @@ _SIGNATURES = {
     "mg_linear_skinny": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
                          _I, _I, _I, _I, _P, _P, _I, _P],
     "mg_linear_skinny_ctas": [_I, _I],
-    "mg_linear_stream": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _I, _P, _P],
+    "mg_linear_stream": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
+                         _I, _I, _I, _I, _P, _P, _I, _I, _P, _P],
     "mg_linear_stream_parts": [_I],
     "mg_argmax_merge": [_P, _P, _P, _I, _I, _P],
     "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],

@@ -73,6 +73,12 @@ class CudaOps:
         self.use_skinny = True
         self.use_cluster = True
         self.use_stream = True
+        # The streaming kernel also takes any matrix of at least `stream_min_bytes` (None: only tall
+        # ones, the head) and rows cut into up to `stream_max_chunks` K chunks.  Measured at widths
+        # 1600 and 6400 with row copies of 640 bytes it was slower than the small-batch kernel
+        # (a 20 MB matrix in 30 us against 20 us), so both stay off by default.
+        self.stream_min_bytes = None
+        self.stream_max_chunks = 1
         self.greedy_taken = False
         self.use_dependent_launch = True
         self.use_prefill_tc = True
@@ -227,9 +233,11 @@ class CudaOps:
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
-        if (self.use_stream and kv_sink is None and n >= STREAM_MIN_ROWS and weight.dtype == torch.bfloat16
-                and 0 < m <= STREAM_ROWS and k % 8 == 0):
-            # a wide matrix (the head): one CTA per SM streams it through shared memory
+        if (self.use_stream and weight.dtype == torch.bfloat16 and 0 < m <= STREAM_ROWS and k % 8 == 0
+                and (n >= STREAM_MIN_ROWS
+                     or (self.stream_min_bytes is not None and 2 * n * k >= self.stream_min_bytes))):
+            # a tall matrix (the head) or one of many megabytes: one CTA per SM streams it through
+            # shared memory
             if deferred is not None and m > SKINNY_ROWS:
                 # more rows than a CTA normalises quickly: the norm runs as a kernel of its own
                 x, deferred = deferred.materialize(), None
@@ -247,15 +255,15 @@ class CudaOps:
                 part_i = torch.empty((m * parts,), dtype=torch.int32, device=self.device)
                 amax = [_ptr(part_v), _ptr(part_i), int(limit or 0)]
             code = self.lib.mg_linear_stream(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
-                                             m, n, k, epilogue, out_bf16, *amax, _ptr(self.status),
-                                             self._stream())
+                                             m, n, k, epilogue, out_bf16, *self._sink_args(kv_sink), *amax,
+                                             self.stream_max_chunks, _ptr(self.status), self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "linear (wide matrix)")
                 if greedy is not None:
                     self._run(self.lib.mg_argmax_merge(_ptr(part_v), _ptr(part_i), _ptr(ids_out), m, parts,
                                                        self._stream()), "argmax (merge)")
                     self.greedy_taken = True
-                return False
+                return kv_sink is not None
         if self._skinny_ok(m, k, weight.dtype):
             sink = self._sink_args(kv_sink)
             if deferred is not None:

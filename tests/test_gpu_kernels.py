@@ -220,6 +220,85 @@ def test_streaming_projection_of_a_wide_matrix_takes_up_to_64_rows(ops, m):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("n,k", [(640, 1600), (203, 6400), (9001, 1608), (77, 3080)])
+def test_streamed_projection_of_long_rows(ops, m, n, k):
+    """Rows too long for whole-row stages go through the streaming kernel in K chunks (a tile's
+    sums stay in registers from chunk to chunk), with the LayerNorm prologue on rows of any length:
+    one launch, and the same numbers as the separate kernels."""
+    x32 = randn(m + 3, k, seed=81, scale=2.0) + 0.5
+    rows = torch.tensor([(3 * i + 1) % (m + 3) for i in range(m)], dtype=torch.int32).cuda()
+    gain, shift = randn(k, seed=82) + 1.0, randn(k, seed=83)
+    w = randn(n, k, dtype=torch.bfloat16, seed=84, scale=1 / math.sqrt(k))
+    b = randn(n, seed=85)
+    want = torch.nn.functional.layer_norm(x32[rows.long()].double(), (k,), gain.double(), shift.double(), 1e-5)
+    want = want.to(torch.bfloat16).double() @ w.double().T + b.double()
+    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster)
+    ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = 0, 1 << 20, False, False
+    # 16 rows of 6400 values leave no room for stages beside them: refused, other kernels take it
+    fits = (8 if m <= 8 else 16) * (2 * k + 64) + 8 * k + 8 * 4 * 8 * (2 * 64 + 64) <= 226 * 1024
+    try:
+        before = ops.launches
+        fused = ops.linear(ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16, rows), w, b, "none",
+                           torch.float32)
+        assert (ops.launches == before + 1) == fits, "norm, gather and projection in one streaming kernel"
+        y = ops.layernorm(ops.gather_rows(x32, rows), gain, shift, 1e-5, torch.bfloat16)
+        streamed = ops.linear(y, w, b, "none", torch.float32)
+        g = ops.linear(y, w, b, "gelu_tanh", torch.bfloat16)
+        res = randn(m, n, seed=86)
+        keep = res.clone()
+        ops.linear_residual(y, w, b, res)
+        ops.use_stream = False
+        apart = ops.linear(y, w, b, "none", torch.float32)
+    finally:
+        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = flags
+        ops.use_stream = True
+    assert (fused.double() - want).abs().max() <= 2e-2       # bf16 rounding of the normalised rows
+    assert (fused - streamed).abs().max() <= 2e-5             # the fused norm rounds as the stand-alone kernel
+    assert (streamed - apart).abs().max() <= 2e-5             # same bf16 inputs, 32-bit sums
+    assert (res.double() - (keep.double() + want)).abs().max() <= 2e-2
+    assert (g.double() - plain_gpt.gelu_tanh(want)).abs().max() <= 5e-2
+    ops.check_status()
+
+
+@pytest.mark.parametrize("m", [1, 8, 16])
+def test_streamed_qkv_projection_writes_keys_and_values(ops, m):
+    """A QKV matrix of many megabytes is streamed as well; the epilogue of the streaming kernel
+    copies key and value features to their cache rows like the other projection kernels."""
+    n_head, n_kv, d, pt, k = 5, 5, 64, 16, 1600
+    width = (n_head + 2 * n_kv) * d
+    x = randn(m, k, dtype=torch.bfloat16, seed=91)
+    w = randn(width, k, dtype=torch.bfloat16, seed=92, scale=1 / math.sqrt(k))
+    b = randn(width, seed=93)
+    pages = 6
+    slots = torch.randperm(pages * pt)[:m].to(torch.int32)
+    if m > 1:
+        slots[0] = -1                                        # a padding row writes nothing
+    slots = slots.cuda()
+    cache = SimpleNamespace(k_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                            v_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                            page_tokens=pt, writes=True)
+    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster)
+    ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = 0, 1 << 20, False, False
+    try:
+        before = ops.launches
+        qkv = ops.linear_qkv(x, w, b, n_head, n_kv, d, cache, slots, torch.bfloat16)
+        assert ops.launches == before + 1, "projection and page write were expected in one streaming kernel"
+    finally:
+        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = flags
+    kk = qkv[:, n_head * d: (n_head + n_kv) * d].reshape(m, n_kv, d)
+    vv = qkv[:, (n_head + n_kv) * d:].reshape(m, n_kv, d)
+    want_k, want_v = torch.zeros_like(cache.k_pages), torch.zeros_like(cache.v_pages)
+    for i, s_ in enumerate(slots.tolist()):
+        if s_ >= 0:
+            want_k[s_ // pt, :, s_ % pt] = kk[i]
+            want_v[s_ // pt, :, s_ % pt] = vv[i]
+    assert torch.equal(cache.k_pages, want_k) and torch.equal(cache.v_pages, want_v)
+    ref = x.double() @ w.double().T + b.double()
+    assert (qkv.double() - ref).abs().max() <= 5e-2
+    ops.check_status()
+
+
 @pytest.mark.parametrize("heads", [(6, 2, 32), (3, 1, 48)])
 @pytest.mark.parametrize("m", [1, 4, 8, 9, 40, 70, 200, 333])
 def test_qkv_projection_writes_keys_and_values_to_their_pages(ops, m, heads):
