@@ -79,6 +79,11 @@ def test_mixed_requests_with_page_reuse(which, dtype, sharp):
     # room for the four longest at once, no more
     pool = sum(sorted(-(-n // pt) for n in lengths)[-4:])
     cfg, tensors, runner, tol = _setup(which, dtype, sharp, num_pages=pool)
+    # Every cache row starts as NaN and a finished request's pages become NaN again: a query that
+    # reads a row its own request did not write (beyond its length, or left by the page's last
+    # holder) turns its logits into NaN.
+    for pages in runner.storage.k + runner.storage.v:
+        pages.fill_(float("nan"))
     reqs = {f"q{i}": tokens_for(cfg, n, 20 + i) for i, n in enumerate(lengths)}
     want = {rid: plain_logits(cfg, tensors, toks) for rid, toks in reqs.items()}
     got = {rid: [] for rid in reqs}
@@ -107,12 +112,17 @@ def test_mixed_requests_with_page_reuse(which, dtype, sharp):
             got[rid].append(logits[row: row + n])
             row += n
         for rid in [r for r, p in live.items() if p == len(reqs[r])]:
+            held = torch.tensor([p for p in runner.manager.block_table(rid, 0) if p >= 0],
+                                dtype=torch.long, device="cuda")
             runner.finish(rid)
+            for pages in runner.storage.k + runner.storage.v:
+                pages[:, held] = float("nan")
             del live[rid]
         runner.manager.check()
         steps += 1
     assert runner.manager.stats()["allocated_blocks"] == 0
     for rid in reqs:
+        assert not torch.isnan(torch.cat(got[rid])).any(), f"request {rid} read a cache row that was not its own"
         assert_close(torch.cat(got[rid]), want[rid], tol, f"mixed batch, request {rid}")
 
 
