@@ -74,11 +74,11 @@ class CudaOps:
         self.use_cluster = True
         self.use_stream = True
         # The streaming kernel also takes any matrix of at least `stream_min_bytes` (None: only tall
-        # ones, the head) and rows cut into up to `stream_max_chunks` K chunks.  Measured at widths
-        # 1600 and 6400 with row copies of 640 bytes it was slower than the small-batch kernel
-        # (a 20 MB matrix in 30 us against 20 us), so both stay off by default.
-        self.stream_min_bytes = None
-        self.stream_max_chunks = 1
+        # ones, the head), with rows cut into up to `stream_max_chunks` K chunks.  At width 1600
+        # (5 chunks, row copies of 640 bytes) it is a little faster than the small-batch kernel; at
+        # 6400 (67 chunks, copies of 192 bytes) it was measured far slower, hence the limit.
+        self.stream_min_bytes = 8 << 20
+        self.stream_max_chunks = 8
         self.greedy_taken = False
         self.use_dependent_launch = True
         self.use_prefill_tc = True
