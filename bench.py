@@ -17,6 +17,9 @@ bfloat16, a batch of 8 and contexts that end at 2048 tokens.  One JSON line is p
 * ``prefill``: one 2,048-token prompt; ``roofline``: bytes a decode step must read / its time;
 * ``points``: decode at batch 1 and 64.
 
+``--only serve`` prints a line of its own: 64 requests (prompts of 16 to 512 tokens, 256 greedy
+tokens each) through ``LLMEngine.generate``, wall clock: the scheduler's mixed batches.
+
 ``--sizes`` runs the same measurement at the layer sizes of GPT-2 small or GPT-2 XL (position
 table of 1,024: the prefill step is then two whole prompts of 1,024 tokens).
 
@@ -72,9 +75,11 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
-                         "the 2,048-token prefill (the printed line is then partial)")
+                         "the 2,048-token prefill (the printed line is then partial); serve: 64 "
+                         "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
+                         "through LLMEngine.generate (mixed batches, wall clock)")
     args = ap.parse_args()
     global MODEL
     MODEL = SIZES[args.sizes]
@@ -321,6 +326,37 @@ def prefill_once(args):
     return cfg, statistics.median(times), length, count
 
 
+def serve_mixed(args, requests: int = 64, new_tokens: int = 256) -> dict:
+    """Many requests at once through the public entry point: prompts of 16 to 512 uniform random
+    tokens, `new_tokens` greedy tokens each; the scheduler mixes prompt portions with decoding.
+    Wall clock from the first add_request to the last token, host token ids in and out."""
+    import torch
+
+    from mini_gpt_inference_b200 import SamplingParams
+
+    longest = min(512, MODEL["n_positions"] - new_tokens)
+    cfg, engine = build_engine(args, requests, longest + new_tokens)
+    gen = torch.Generator().manual_seed(4)
+    lengths = torch.randint(16, longest + 1, (requests,), generator=gen).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in lengths]
+    params = SamplingParams(max_tokens=new_tokens, temperature=0.0)
+    engine.generate(prompts[:4], SamplingParams(max_tokens=8, temperature=0.0))     # warm-up
+    before = engine.stats()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = engine.generate(prompts, params)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    after = engine.stats()
+    generated = sum(len(o["token_ids"]) for o in outs)
+    return {"impl": "ours", "partial": "serve", "model": MODEL_NAMES[args.sizes], "requests": requests,
+            "prompt_tokens": sum(lengths), "generated_tokens": generated, "seconds": round(wall, 4),
+            "value": round(generated / wall, 1), "unit": "generated tokens/s",
+            "steps": after["steps"] - before["steps"],
+            "preemptions": after["preemptions"] - before["preemptions"],
+            "finish_reasons": sorted({o["finish_reason"] for o in outs})}
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -330,6 +366,8 @@ def run_ours(args) -> dict:
         cfg, pre_ms, _, _ = prefill_once(args)
         return {"impl": "ours", "partial": "prefill only", "prefill": {
             "value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4)}}
+    if args.only == "serve":
+        return serve_mixed(args)
     if args.only == "decode":
         cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup)
         ms = statistics.fmean(times)
