@@ -5,7 +5,8 @@ Option names and meanings are the reference's where it has them:
 with temperature 0.8 and top-k 50 — the defaults here), ``--device``, ``--kv-block-size``,
 ``--num-kv-blocks`` and ``--max-batch-size`` (scripts/serve.py:23-33).  The reference fetches
 its checkpoint from a hub (``--repo-id``, ``--filename``); this engine reads a local folder
-(``--model``) with ``config.json`` and ``model.safetensors``.
+(``--model``) with ``config.json`` and ``model.safetensors``.  The reference's scripts mask the
+padding rows of the vocabulary (src/minigpt_infer/tokenizer.py:37-46); here ``--vocab-limit`` does.
 
     generate --model DIR --prompt-ids 5,17,3 --max-new-tokens 20
     generate --random-weights 0 --config config.json --write-model DIR
@@ -29,6 +30,9 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--top-k", type=int, default=50)
     ap.add_argument("--top-p", type=float, default=None)
     ap.add_argument("--seed", type=int, default=None)
+    ap.add_argument("--vocab-limit", type=int, default=None,
+                    help="ids at and above this are never sampled: rows that only pad the embedding "
+                         "table (the reference masks ids >= 50257 of its 50304 rows)")
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--kv-block-size", type=int, default=16)
@@ -83,7 +87,7 @@ def main(argv=None) -> int:
     engine = LLMEngine.from_pretrained(args.model, EngineConfig(
         block_size=args.kv_block_size, num_blocks=args.num_kv_blocks,
         max_batch_size=args.max_batch_size, max_num_batched_tokens=args.max_num_batched_tokens,
-        dtype=args.dtype, device=args.device))
+        dtype=args.dtype, device=args.device), vocab_limit=args.vocab_limit)
     print(f"config: {engine.config}", file=sys.stderr)
     print(f"params: {engine.config.num_parameters() / 1e6:.1f}M", file=sys.stderr)
     params = SamplingParams(max_tokens=args.max_new_tokens, temperature=args.temperature,
