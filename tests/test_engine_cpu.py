@@ -88,3 +88,58 @@ def test_cancel_frees_pages():
     assert engine.stats()["allocated_blocks"] == 3
     assert engine.cancel_request("a") and not engine.cancel_request("a")
     assert engine.stats()["allocated_blocks"] == 0 and not engine.has_unfinished_requests()
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_random_arrivals_small_pools_and_cancellations(seed):
+    """Requests arrive while others run, in pools and budgets drawn at random (small enough to
+    force portions, waiting and preemption); some are cancelled half-way.  After every step the
+    cache manager's books must balance; a request that finishes has the plain greedy tokens, a
+    cancelled one a prefix of them; nothing is held at the end."""
+    import random
+
+    rng = random.Random(seed)
+    which = "AB"[seed % 2]
+    block = rng.choice([2, 4, 8])
+    longest = 24
+    ecfg = EngineConfig(block_size=block,
+                        num_blocks=rng.randint(-(-longest // block) + 1, 2 * longest // block),
+                        max_batch_size=rng.randint(2, 4), max_num_batched_tokens=rng.choice([8, 13, 32]),
+                        max_prefill_chunk=rng.choice([None, 5, 9]), dtype="float32", device="cpu")
+    cfg, tensors, engine = engine_for(which, ecfg, seed=7 + seed)
+    asked = {}
+    for i in range(10):
+        n_prompt = rng.randint(1, 14)
+        asked[f"r{i}"] = (tokens_for(cfg, n_prompt, 100 * seed + i), rng.randint(1, longest - n_prompt))
+    todo = list(asked)
+    cancel_at = {f"r{rng.randrange(10)}": rng.randint(1, 6) for _ in range(2)}
+    got, reasons, alive = {}, {}, {}
+    steps = 0
+    while todo or engine.has_unfinished_requests():
+        for _ in range(rng.randint(0, 2)):
+            if todo:
+                rid = todo.pop(0)
+                prompt, new = asked[rid]
+                engine.add_request(Request(rid, prompt, SamplingParams(max_tokens=new, temperature=0.0)))
+                got[rid], alive[rid] = [], 0
+        for out in engine.step():
+            got[out.request_id].extend(out.new_token_ids)
+            if out.finished:
+                reasons[out.request_id] = out.finish_reason
+        engine.runner.manager.check()
+        for rid in alive:
+            alive[rid] += 1
+            if cancel_at.get(rid) == alive[rid] and rid not in reasons and engine.cancel_request(rid):
+                reasons[rid] = "cancelled"
+        steps += 1
+        assert steps < 2000, "the engine does not finish"
+    assert set(reasons) == set(asked)
+    for rid, (prompt, new) in asked.items():
+        want = plain_greedy(cfg, tensors, prompt, new)
+        if reasons[rid] == "cancelled":
+            assert got[rid] == want[: len(got[rid])], rid
+        else:
+            assert reasons[rid] == "length" and got[rid] == want, rid
+    stats = engine.stats()
+    assert stats["allocated_blocks"] == 0 and stats["running"] == 0 and stats["waiting"] == 0
+    engine.runner.manager.check()
