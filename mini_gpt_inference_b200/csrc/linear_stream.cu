@@ -1,4 +1,5 @@
-// Projection of up to 64 tokens onto a WIDE matrix (the head: tens of thousands of rows):
+// Projection of up to 64 tokens onto a LARGE matrix (the head: tens of thousands of rows; or any
+// matrix of many megabytes):
 // out[m, n] = x[m, :] . w[n, :], the weights streamed once through shared memory.
 //
 // The small-batch kernel (linear_skinny.cu) holds a warp's weights in registers: right for a
@@ -13,9 +14,15 @@
 // 190 KB are in flight per SM the whole time, and the first tiles are asked for before the wait
 // for the kernel in front.
 //
+// Rows too long for whole-row stages beside the activations (width 1600, say) are cut into K chunks:
+// a stage then holds the tile's 8 rows over one chunk, chunks of a tile follow one another in the
+// warp's ring, and the tile's sums stay in registers from chunk to chunk.  With chunks of a few
+// hundred bytes a row the copies' own cost shows; the caller limits the number of chunks.
+//
 // Fused as in the small-batch kernel: LayerNorm prologue (with row gather), bias / tanh-GELU /
-// residual / store epilogue, and the first stage of the greedy argmax over the rows.  A warp
-// owns whole rows of K, so every output sums its terms in k order, independent of M.
+// residual / store epilogue, the copy of key and value features to their cache rows, and the first
+// stage of the greedy argmax over the rows.  A warp owns whole rows of K, so every output sums
+// its terms in k order, independent of M.
 // The waits are bounded: if one runs out, the kernel records a code in `status` and stops.
 #include <math.h>
 
