@@ -170,3 +170,28 @@ def test_missing_file(tmp_path):
     (tmp_path / "model.safetensors").write_bytes(b"\x05\x00\x00")
     with pytest.raises(WeightsError, match="too short"):
         load_checkpoint(tmp_path, {})
+
+
+def test_malformed_safetensors_files_give_clear_errors(tmp_path):
+    import json
+    import struct
+
+    from mini_gpt_inference_b200.weights.safetensors_io import SafetensorsError
+
+    def attempt(data: bytes, match: str):
+        path = tmp_path / "bad.safetensors"
+        path.write_bytes(data)
+        with pytest.raises(SafetensorsError, match=match):
+            load_file(path)
+
+    def with_header(header: dict, payload: bytes) -> bytes:
+        raw = json.dumps(header).encode()
+        return struct.pack("<Q", len(raw)) + raw + payload
+
+    attempt(b"", "too short")
+    attempt(struct.pack("<Q", 1 << 40) + b"{}", "does not fit")
+    attempt(struct.pack("<Q", 5) + b"hello", "not JSON")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}, b"\0" * 8), "offsets")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 8]}}, b"\0" * 8), "offsets")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 8]}}, b"\0" * 8), "offsets")
+    attempt(with_header({"a": {"dtype": "Q7", "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 8), "unsupported dtype")
