@@ -209,8 +209,21 @@ def prefill_flops(cfg, tokens: int) -> float:
     return linear + attention + head
 
 
-def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None):
-    """K decode steps of `batch` requests whose contexts end at args.context; device time."""
+def window_stats(per_window_ms: list) -> dict:
+    """Median and interquartile range of the windows' mean step times."""
+    ordered = sorted(per_window_ms)
+    n = len(ordered)
+    q1, q3 = ordered[n // 4], ordered[(3 * n) // 4 if n > 1 else 0]
+    return {"count": n, "median_ms": round(statistics.median(ordered), 4),
+            "iqr_ms": round(q3 - q1, 4), "min_ms": round(ordered[0], 4), "max_ms": round(ordered[-1], 4)}
+
+
+def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None, min_seconds: float = 0.5,
+                  max_windows: int = 96, flush_l2: bool = True):
+    """Windows of K decode steps of `batch` requests whose contexts end at args.context; device
+    time.  A window prefills fresh requests (untimed), runs W warm-up steps and times exactly K
+    steps with CUDA events around each step; windows are repeated until `min_seconds` of device
+    time have been timed (at most `max_windows`).  Returns the mean step time of each window."""
     import torch
 
     from mini_gpt_inference_b200.config import SamplingParams
@@ -221,48 +234,56 @@ def device_decode(args, batch: int, steps: int, warmup: int, clock_sampler=None)
     prompt_len = args.context - (steps + warmup)
     gen = torch.Generator().manual_seed(1)
     rids = [f"d{i}" for i in range(batch)]
-    for rid in rids:                                   # prefill, untimed
-        prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
-        runner.step([StepEntry(rid, prompt, [])])
-    last = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
     greedy = [SamplingParams(temperature=0.0)] * batch
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
-    events, ids, feed = [], None, list(range(batch))
-    launches_before = getattr(runner.ops, "launches", 0)
-    torch.cuda.synchronize()
-    for step in range(steps + warmup):
-        flush.zero_()                                  # evict L2 between steps, outside the events
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        if step == warmup:
-            torch.cuda.synchronize()
-            launches_before = getattr(runner.ops, "launches", 0)
-            if clock_sampler is not None:
-                clock_sampler.start()                   # clocks of the timed steps only
-        start.record()
-        if ids is None:
-            logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
-        else:
-            # the tokens sampled by the step before are taken on the device, as the engine does
-            # in steady decoding: the host prepares this step while the device runs the last one
-            logits = runner.step([StepEntry(rid, [0], [0]) for rid in rids], copy=False,
-                                 token_sources=feed, previous_ids=ids)
-        ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch,
-                             greedy_ids=runner.greedy_ids(batch), out=runner.sampled_ids[:batch])
-        end.record()
-        events.append((start, end))
-    torch.cuda.synchronize()
-    last = ids.tolist()                                # device -> host: the last step's result
-    times = [a.elapsed_time(b) for a, b in events[warmup:]]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0") if flush_l2 else None
+    feed = list(range(batch))
+    per_window, launches, timed = [], 0, 0.0
+    while len(per_window) < max_windows and (timed < min_seconds or not per_window):
+        for rid in rids:                                   # prefill, untimed
+            prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
+            runner.step([StepEntry(rid, prompt, [])])
+        last = torch.randint(0, cfg.vocab_size, (batch,), generator=gen).tolist()
+        events, ids = [], None
+        launches_before = getattr(runner.ops, "launches", 0)
+        torch.cuda.synchronize()
+        for step in range(steps + warmup):
+            if flush is not None:
+                flush.zero_()                              # evict L2 between steps, outside the events
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            if step == warmup:
+                torch.cuda.synchronize()
+                launches_before = getattr(runner.ops, "launches", 0)
+                if clock_sampler is not None and not per_window:
+                    clock_sampler.start()                   # clocks of the timed steps of all windows
+            start.record()
+            if ids is None:
+                logits = runner.step([StepEntry(rid, [tok], [0]) for rid, tok in zip(rids, last)], copy=False)
+            else:
+                # the tokens sampled by the step before are taken on the device, as the engine does
+                # in steady decoding: the host prepares this step while the device runs the last one
+                logits = runner.step([StepEntry(rid, [0], [0]) for rid in rids], copy=False,
+                                     token_sources=feed, previous_ids=ids)
+            ids = sampler.sample(logits, greedy, [0] * batch, [step] * batch,
+                                 greedy_ids=runner.greedy_ids(batch), out=runner.sampled_ids[:batch])
+            end.record()
+            events.append((start, end))
+        torch.cuda.synchronize()
+        ids.tolist()                                       # device -> host: the last step's result
+        times = [a.elapsed_time(b) for a, b in events[warmup:]]
+        per_window.append(statistics.fmean(times))
+        timed += sum(times) * 1e-3
+        launches = getattr(runner.ops, "launches", 0) - launches_before
+        for rid in rids:
+            runner.finish(rid)
     clocks = clock_sampler.stop() if clock_sampler is not None else None
-    launches = getattr(runner.ops, "launches", 0) - launches_before
-    for rid in rids:
-        runner.finish(rid)
+    runner.ops.check_status()
     mean_context = args.context - steps / 2.0
-    return cfg, times, launches, mean_context, clocks
+    return cfg, per_window, launches, mean_context, clocks
 
 
-def e2e_decode(args, batch: int, steps: int, warmup: int):
-    """The same through LLMEngine.step(): host token ids in, sampled ids out, wall clock."""
+def e2e_decode(args, batch: int, steps: int, warmup: int, min_seconds: float = 0.3, max_windows: int = 48):
+    """The same through LLMEngine.step(): host token ids in, sampled ids out, wall clock.  Windows
+    of K steps on fresh requests, repeated like the device-timed ones; the median window counts."""
     import torch
 
     from mini_gpt_inference_b200 import Request, SamplingParams
@@ -273,30 +294,37 @@ def e2e_decode(args, batch: int, steps: int, warmup: int):
     max_tokens = steps + warmup + batch + 8
     prompt_len = args.context - max_tokens
     gen = torch.Generator().manual_seed(2)
-    for i in range(batch):
-        prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
-        engine.add_request(Request(f"e{i}", prompt, SamplingParams(max_tokens=max_tokens,
-                                                                    temperature=0.0)))
-    # prompts first (untimed), until every request is decoding
-    while any(s.num_pending_tokens > 1 or s.num_computed_tokens == 0
-              for s in list(engine.scheduler.running) + list(engine.scheduler.waiting)):
-        engine.step()
-    for _ in range(warmup - 1):
-        engine.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    produced = 0
-    for _ in range(steps):
-        produced += len(engine.step())
-    torch.cuda.synchronize()
-    wall = time.perf_counter() - t0
-    h2d = engine.runner.last_h2d_bytes if hasattr(engine.runner, "last_h2d_bytes") else None
-    while engine.has_unfinished_requests():
-        engine.step()
-    return produced / wall, wall / steps * 1e3, h2d, batch * 4
+    rates, walls, total, window = [], [], 0.0, 0
+    h2d = None
+    while window < max_windows and (total < min_seconds or not rates):
+        for i in range(batch):
+            prompt = torch.randint(0, cfg.vocab_size, (prompt_len,), generator=gen).tolist()
+            engine.add_request(Request(f"e{window}_{i}", prompt, SamplingParams(max_tokens=max_tokens,
+                                                                                 temperature=0.0)))
+        # prompts first (untimed), until every request is decoding
+        while any(s.num_pending_tokens > 1 or s.num_computed_tokens == 0
+                  for s in list(engine.scheduler.running) + list(engine.scheduler.waiting)):
+            engine.step()
+        for _ in range(warmup - 1):
+            engine.step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        produced = 0
+        for _ in range(steps):
+            produced += len(engine.step())
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        h2d = engine.runner.last_h2d_bytes if hasattr(engine.runner, "last_h2d_bytes") else None
+        while engine.has_unfinished_requests():
+            engine.step()
+        rates.append(produced / wall)
+        walls.append(wall / steps * 1e3)
+        total += wall
+        window += 1
+    return statistics.median(rates), statistics.median(walls), h2d, batch * 4, len(rates)
 
 
-def prefill_once(args):
+def prefill_once(args, reps: int = 6):
     """One step of 2,048 prompt tokens: one prompt where the position table holds it, else as
     many whole prompts of the table's length as make 2,048 tokens (two of 1,024)."""
     import torch
@@ -311,7 +339,7 @@ def prefill_once(args):
     prompts = [torch.randint(0, cfg.vocab_size, (length,), generator=gen).tolist() for _ in range(count)]
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda:0")
     times = []
-    for rep in range(6):
+    for rep in range(reps):
         flush.zero_()
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
@@ -321,8 +349,9 @@ def prefill_once(args):
         assert logits.shape == (count, cfg.vocab_size)
         for i in range(count):
             runner.finish(f"p{i}")
-        if rep >= 2:
+        if rep >= min(2, reps - 1):
             times.append(start.elapsed_time(end))
+    runner.ops.check_status()
     return cfg, statistics.median(times), length, count
 
 
@@ -357,6 +386,51 @@ def serve_mixed(args, requests: int = 64, new_tokens: int = 256) -> dict:
             "finish_reasons": sorted({o["finish_reason"] for o in outs})}
 
 
+def check_decode_logits(args) -> dict:
+    """Outside every timed region: the decode step that the benchmark times (batch 8, contexts of
+    2,048, the replayed graph) is run once on fixed tokens and its logits are compared with rows
+    that the tests' plain implementation computed for the same weights and tokens
+    (tests/golden/bench_decode_rows.json, written by tests/golden/make_bench_rows.py).  Raises if
+    they differ by more than the bfloat16 tolerance of the tests (3% of the logits' spread)."""
+    import torch
+
+    from mini_gpt_inference_b200.engine.runner import StepEntry
+
+    path = ROOT / "tests" / "golden" / "bench_decode_rows.json"
+    if not path.is_file():
+        return {"checked": False, "why": "tests/golden/bench_decode_rows.json is absent"}
+    stored = json.loads(path.read_text())
+    same = (args.sizes == "50m" and args.dtype == "bfloat16" and args.layers == stored["config"]["n_layer"]
+            and all(MODEL[k] == v for k, v in stored["config"].items()))
+    if not same:
+        return {"checked": False, "why": "rows are stored for the default configuration only"}
+    batch, length = stored["tokens"]["batch"], stored["tokens"]["length"]
+    check_args = argparse.Namespace(**{**vars(args), "context": length})
+    cfg, engine = build_engine(check_args, batch, length)
+    runner = engine.runner
+    gen = torch.Generator().manual_seed(stored["tokens"]["seed"])
+    tokens = [torch.randint(0, cfg.vocab_size, (length,), generator=gen).tolist() for _ in range(batch)]
+    for i, t in enumerate(tokens):
+        runner.step([StepEntry(f"c{i}", t[:-1], [])])
+    replays = runner.graph_replays
+    logits = runner.step([StepEntry(f"c{i}", t[-1:], [0]) for i, t in enumerate(tokens)])
+    torch.cuda.synchronize()
+    runner.ops.check_status()
+    columns = torch.tensor(stored["columns"], device=logits.device)
+    got = logits[:, columns].double().cpu()
+    want = torch.tensor(stored["logits"], dtype=torch.float64)
+    diff = float((got - want).abs().max())
+    tol = 0.03 * stored["logits_std"]
+    for i in range(batch):
+        runner.finish(f"c{i}")
+    out = {"checked": True, "max_abs_diff": round(diff, 6), "tolerance": round(tol, 6),
+           "argmax_equal": logits.argmax(-1).tolist() == stored["argmax"],
+           "graph_replayed": runner.graph_replays == replays + 1}
+    if not diff <= tol:
+        raise SystemExit(f"bench.py: the decode step's logits differ from the plain implementation's: {out}")
+    return out
+
+
 def run_ours(args) -> dict:
     import torch
 
@@ -369,17 +443,22 @@ def run_ours(args) -> dict:
     if args.only == "serve":
         return serve_mixed(args)
     if args.only == "decode":
-        cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup)
-        ms = statistics.fmean(times)
+        cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
+                                                                 min_seconds=0.0)
+        ms = statistics.median(windows)
         return {"impl": "ours", "partial": "decode only", "value": round(args.batch / (ms * 1e-3), 1),
                 "ms_per_step": round(ms, 4), "gpu_launches": launches}
-    cfg, times, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
-                                                           ClockSampler(0))
-    ms = statistics.fmean(times)
+
+    def roofline_of(cfg, batch, mean_ctx, ms, nbytes=dtype_bytes):
+        step_bytes = weight_bytes(cfg, nbytes) + kv_bytes(cfg, batch, mean_ctx, nbytes)
+        return step_bytes, step_bytes / (ms * 1e-3) / 1e9
+
+    cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
+                                                             ClockSampler(0))
+    ms = statistics.median(windows)                 # the median window of K steps is the reported one
     value = args.batch / (ms * 1e-3)
-    step_bytes = weight_bytes(cfg, dtype_bytes) + kv_bytes(cfg, args.batch, mean_ctx, dtype_bytes)
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-    e2e_value, e2e_ms, h2d, d2h = e2e_decode(args, args.batch, args.steps, args.warmup)
+    step_bytes, achieved = roofline_of(cfg, args.batch, mean_ctx, ms)
+    e2e_value, e2e_ms, h2d, d2h, e2e_windows = e2e_decode(args, args.batch, args.steps, args.warmup)
     line = {
         "metric": metric_name(args),
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
@@ -397,8 +476,11 @@ def run_ours(args) -> dict:
             "l2": "flushed between timed steps (256 MiB write)", "weights": "random seed 0",
             "mean_context": mean_ctx, "peaks": peak_source,
         },
+        # windows of exactly K timed steps on freshly prefilled requests, repeated until half a
+        # second of device time is timed; `value` is the median window
+        "windows": window_stats(windows),
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "windows": e2e_windows},
         "gpu_launches": launches,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
@@ -407,10 +489,15 @@ def run_ours(args) -> dict:
     }
     if not args.no_points:
         points = {}
+        small_k, small_w = min(args.steps, 64), max(3, min(args.warmup, 8))
         for b in (1, 64):
-            _, t, _, _, _ = device_decode(args, b, min(args.steps, 64), max(3, min(args.warmup, 8)))
-            points[f"decode_b{b}"] = round(b / (statistics.fmean(t) * 1e-3), 1)
-        line["points"] = points
+            _, t, _, ctx_b, _ = device_decode(args, b, small_k, small_w, min_seconds=0.25)
+            ms_b = statistics.median(t)
+            points[f"decode_b{b}"] = round(b / (ms_b * 1e-3), 1)
+            points[f"decode_b{b}_roofline_frac"] = round(roofline_of(cfg, b, ctx_b, ms_b)[1] / pk["hbm_gbs"], 4)
+        # the same step with whatever the step before left in L2 (no flush between steps)
+        _, t, _, _, _ = device_decode(args, args.batch, small_k, small_w, min_seconds=0.1, flush_l2=False)
+        points[f"decode_b{args.batch}_no_l2_flush"] = round(args.batch / (statistics.median(t) * 1e-3), 1)
         _, pre_ms, pre_len, pre_count = prefill_once(args)
         flops = pre_count * prefill_flops(cfg, pre_len)
         peak = pk["bf16_tflops"] if args.dtype == "bfloat16" else None
@@ -418,6 +505,22 @@ def run_ours(args) -> dict:
                            "prompts": pre_count, "ms": round(pre_ms, 4),
                            "frac": round(flops / (pre_ms * 1e-3) / (peak * 1e12), 4) if peak else None,
                            "of": peak_source}
+        if args.dtype == "bfloat16":
+            # the true 32-bit path of the same model (FMA kernels, 32-bit weights and cache)
+            args32 = argparse.Namespace(**{**vars(args), "dtype": "float32"})
+            _, t, _, ctx32, _ = device_decode(args32, args.batch, min(args.steps, 16), 3, min_seconds=0.0,
+                                              max_windows=2)
+            ms32 = statistics.median(t)
+            points[f"decode_b{args.batch}_fp32"] = round(args.batch / (ms32 * 1e-3), 1)
+            points[f"decode_b{args.batch}_fp32_roofline_frac"] = round(
+                roofline_of(cfg, args.batch, ctx32, ms32, 4)[1] / pk["hbm_gbs"], 4)
+            _, pre32, _, _ = prefill_once(args32, reps=3)
+            points["prefill_fp32_tok_s"] = round(PREFILL_TOKENS / (pre32 * 1e-3), 1)
+            build_engine.cache.pop((args.sizes, args.layers, "float32"), None)     # give the memory back
+        serve = serve_mixed(args)
+        points["serve_64_requests_tok_s"] = serve["value"]
+        line["points"] = points
+        line["logits_check"] = check_decode_logits(args)
     torch.cuda.synchronize()
     return line
 
@@ -480,6 +583,27 @@ def run_reference(args) -> dict:
                 wall += time.perf_counter() - t0
         clocks = sampler.stop()
         assert host_ids.shape == (batch, 1)
+        # How much of a step the device is busy: the sum of the kernels' own durations over a few
+        # further steps (the events above bracket the host's work between launches as well).
+        busy_ms = None
+        try:
+            from torch.profiler import ProfilerActivity, profile
+
+            probe_steps = 3
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                for _ in range(probe_steps):
+                    next_id = torch.argmax(logits, dim=-1, keepdim=True)
+                    cur_len = int(cache.seq_lens[0].item())
+                    if cur_len >= cfg.block_size:
+                        break
+                    p = torch.full((batch, 1), cur_len, device="cuda", dtype=torch.long)
+                    logits = model(ForwardBatch(input_ids=next_id, position_ids=p, is_prefill=False, cache=cache))
+                    cache.advance(1, batch)
+                torch.cuda.synchronize()
+            total_us = sum(getattr(e, "self_device_time_total", 0.0) for e in prof.key_averages())
+            busy_ms = round(total_us / 1e3 / probe_steps, 4) if total_us else None
+        except Exception:  # noqa: BLE001 - no profiler on this machine: the figure is left out
+            busy_ms = None
     ms = statistics.fmean(times)
     return {
         "metric": metric_name(args),
@@ -494,6 +618,8 @@ def run_reference(args) -> dict:
         "e2e": {"value": round(batch * steps / wall, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": 0, "d2h_bytes_per_step": batch * 8},
         "gpu_launches": 0, "clocks": clocks,
+        # kernels' own time per step beside the event time: far below it means the arm waits for its host
+        "device_busy_ms_per_step": busy_ms,
     }
 
 

@@ -1,7 +1,8 @@
 """Host-side cache manager: page tables per request and per layer group, state slots.
 
 It owns no tensors.  Layers with equal needs (``PagedKVSpec``) form a group; each group
-has a page pool of its own and every request has one block table per group, shared by
+has a page pool and a page size of its own (the manager's defaults unless its spec says
+otherwise) and every request has one block table per group, shared by
 the group's layers — the same page id indexes every layer's storage, as in the
 reference (src/minigpt_infer/cache/paged.py:122-123, 154-155).  Pages are given back
 when a request is released (src/minigpt_infer/cache/paged.py:79-81) or, in a group with
@@ -33,6 +34,14 @@ class CacheGroup:
     spec: PagedKVSpec
     layers: list[int]
     pool: PagePool
+    page_tokens: int
+
+    @property
+    def num_pages(self) -> int:
+        return self.pool.num_pages
+
+    def pages_for(self, num_tokens: int) -> int:
+        return (num_tokens + self.page_tokens - 1) // self.page_tokens
 
 
 @dataclass
@@ -49,12 +58,18 @@ class RequestCache:
 
 
 class CacheManager:
-    def __init__(self, layer_specs, page_tokens: int, num_pages: int, max_requests: int) -> None:
+    def __init__(self, layer_specs, page_tokens: int, num_pages: int, max_requests: int,
+                 window_slack_tokens: int | None = None) -> None:
+        """``page_tokens`` and ``num_pages``: the geometry of every group whose spec names none.
+        ``window_slack_tokens``: the most tokens a request writes in one step (a windowed group
+        sizes its pool for ``window + slack`` tokens per request slot); None: no such bound is
+        known, and a windowed group gets the default pool."""
         if page_tokens <= 0:
             raise ValueError("page_tokens must be positive")
         self.page_tokens = page_tokens
         self.num_pages = num_pages
         self.max_requests = max_requests
+        self.window_slack_tokens = window_slack_tokens
         self.groups: list[CacheGroup] = []
         self.group_of_layer: dict[int, int] = {}
         self.state_layers: dict[int, FixedStateSpec] = {}
@@ -71,7 +86,8 @@ class CacheManager:
                         break
                 else:
                     self.group_of_layer[layer] = len(self.groups)
-                    self.groups.append(CacheGroup(spec, [layer], PagePool(num_pages)))
+                    pt, pages = self._geometry(spec)
+                    self.groups.append(CacheGroup(spec, [layer], PagePool(pages), pt))
             else:
                 raise TypeError(f"layer {layer}: unknown cache spec {spec!r}")
         self.slots = SlotPool(max_requests)
@@ -81,25 +97,53 @@ class CacheManager:
         self._any_window = any(g.spec.window is not None for g in self.groups)
 
     # ---- sizes -------------------------------------------------------------------
-    def pages_for(self, num_tokens: int) -> int:
-        return (num_tokens + self.page_tokens - 1) // self.page_tokens
+    def _geometry(self, spec: PagedKVSpec) -> tuple[int, int]:
+        pt = spec.page_tokens or self.page_tokens
+        if spec.num_pages is not None:
+            return pt, spec.num_pages
+        # the default pool holds num_pages * page_tokens tokens, whatever the group's page size
+        pages = max(1, self.num_pages * self.page_tokens // pt)
+        if spec.window is not None and self.window_slack_tokens is not None:
+            # pages a request can hold at once: the window, the tokens of one step, and the two
+            # pages that the window's and the portion's ends share with their neighbours
+            per_request = (spec.window + self.window_slack_tokens + pt - 1) // pt + 2
+            pages = min(pages, self.max_requests * per_request)
+        return pt, pages
 
-    def max_pages_per_request(self, max_tokens: int) -> int:
-        return max(1, self.pages_for(max_tokens))
+    def pages_for(self, num_tokens: int, group: int = 0) -> int:
+        pt = self.groups[group].page_tokens if self.groups else self.page_tokens
+        return (num_tokens + pt - 1) // pt
+
+    def max_pages_per_request(self, max_tokens: int, group: int = 0) -> int:
+        """Width of a block table of ``group``: page indices are absolute positions / page size,
+        also in a group with a window (pages it gave back stay in the table as NO_PAGE)."""
+        return max(1, self.pages_for(max_tokens, group))
+
+    def can_ever_hold(self, num_tokens: int) -> bool:
+        """Whether a request of ``num_tokens`` tokens fits the pools when it is alone (a group
+        with a window counts the pages it holds at once, see ``_geometry``)."""
+        for group in self.groups:
+            need = group.pages_for(num_tokens)
+            if group.spec.window is not None:
+                slack = self.window_slack_tokens if self.window_slack_tokens is not None else num_tokens
+                need = min(need, (group.spec.window + slack + group.page_tokens - 1) // group.page_tokens + 2)
+            if need > group.num_pages:
+                return False
+        return True
 
     def _first_live_page(self, group: CacheGroup, length: int) -> int:
         """Index of the first page that a query at position >= length may still read."""
         if group.spec.window is None:
             return 0
         first_key = max(0, length - group.spec.window + 1)
-        return first_key // self.page_tokens
+        return first_key // group.page_tokens
 
     def _missing(self, req: RequestCache, new_length: int) -> list[int]:
         """Pages each group still needs so that positions < new_length have a page."""
         need = []
         for g, group in enumerate(self.groups):
             have = len(req.tables[g])
-            need.append(max(0, self.pages_for(new_length) - have))
+            need.append(max(0, group.pages_for(new_length) - have))
         return need
 
     # ---- life of a request ----------------------------------------------------------
@@ -126,7 +170,7 @@ class CacheManager:
     def pages_needed(self, request_id: str | None, new_length: int) -> Sequence[int]:
         """Per group, pages that would have to be taken to reach ``new_length``."""
         if request_id is None or request_id not in self.requests:
-            return [self.pages_for(new_length) for _ in self.groups]
+            return [group.pages_for(new_length) for group in self.groups]
         req = self.requests[request_id]
         if new_length <= req.capacity:
             return self._none_needed
@@ -143,7 +187,7 @@ class CacheManager:
         length = req.length if length is None else length
         room = None
         for g, group in enumerate(self.groups):
-            cap = (len(req.tables[g]) + group.pool.num_free) * self.page_tokens - length
+            cap = (len(req.tables[g]) + group.pool.num_free) * group.page_tokens - length
             room = cap if room is None else min(room, cap)
         return max(0, room) if room is not None else 1 << 30
 
@@ -160,7 +204,8 @@ class CacheManager:
             if n:
                 req.tables[g].extend(group.pool.take(n))
                 req.version += 1
-        req.capacity = min(len(t) for t in req.tables) * self.page_tokens if req.tables else 1 << 30
+        req.capacity = (min(len(t) * group.page_tokens for t, group in zip(req.tables, self.groups))
+                        if req.tables else 1 << 30)
         return True
 
     def advance(self, request_id: str, new_length: int) -> None:
@@ -197,10 +242,11 @@ class CacheManager:
 
     def slot_of(self, request_id: str, group: int, position: int) -> int:
         """Flat index of a position's row in the group's storage."""
-        page = self.get(request_id).tables[group][position // self.page_tokens]
+        pt = self.groups[group].page_tokens
+        page = self.get(request_id).tables[group][position // pt]
         if page == NO_PAGE:
             raise PoolError(f"position {position} of {request_id!r} was given back already")
-        return page * self.page_tokens + position % self.page_tokens
+        return page * pt + position % pt
 
     # ---- accounting ---------------------------------------------------------------------
     def num_free_pages(self, group: int = 0) -> int:
@@ -208,17 +254,16 @@ class CacheManager:
 
     def stats(self) -> dict[str, int]:
         """As src/minigpt_infer/cache/paged.py:83-94, summed over groups."""
-        held = sum(sum(1 for p in t if p != NO_PAGE) for r in self.requests.values()
-                   for t in r.tables)
-        used_tokens = 0
+        held_tokens = used_tokens = 0
         for r in self.requests.values():
             for g, group in enumerate(self.groups):
-                first = self._first_live_page(group, r.length) * self.page_tokens
+                held_tokens += sum(1 for p in r.tables[g] if p != NO_PAGE) * group.page_tokens
+                first = self._first_live_page(group, r.length) * group.page_tokens
                 used_tokens += max(0, r.length - first)
         return {
             "free_blocks": sum(g.pool.num_free for g in self.groups),
             "allocated_blocks": sum(g.pool.num_used for g in self.groups),
-            "internal_fragmentation_slots": held * self.page_tokens - used_tokens,
+            "internal_fragmentation_slots": held_tokens - used_tokens,
             "free_state_slots": self.slots.num_free,
             "live_requests": len(self.requests),
         }

@@ -42,8 +42,8 @@ class CacheStorage:
         self.k: list[torch.Tensor] = []
         self.v: list[torch.Tensor] = []
         for group in manager.groups:
-            shape = (len(group.layers), manager.num_pages, group.spec.n_kv_head,
-                     manager.page_tokens, group.spec.head_dim)
+            shape = (len(group.layers), group.num_pages, group.spec.n_kv_head,
+                     group.page_tokens, group.spec.head_dim)
             self.k.append(torch.zeros(shape, dtype=dtype, device=self.device))
             self.v.append(torch.zeros(shape, dtype=dtype, device=self.device))
         self.state: dict[int, torch.Tensor] = {}
@@ -56,7 +56,7 @@ class CacheStorage:
         if cache_layer in m.group_of_layer:
             g = m.group_of_layer[cache_layer]
             idx = m.groups[g].layers.index(cache_layer)
-            return PagedKVView(self.k[g][idx], self.v[g][idx], g, m.page_tokens,
+            return PagedKVView(self.k[g][idx], self.v[g][idx], g, m.groups[g].page_tokens,
                                m.groups[g].spec.window, writes)
         if cache_layer in self.state:
             return StateView(self.state[cache_layer], writes)

@@ -60,7 +60,8 @@ class SamplingParams:
     top_k: int | None = None
     top_p: float | None = None
     repetition_penalty: float = 1.0      # accepted; not applied (as in the reference engine)
-    stop: list[str] = field(default_factory=list)   # needs a tokenizer; ids-only engine ignores it
+    stop: list[str] = field(default_factory=list)   # stop strings: honoured by an engine that was given
+                                                    # token_bytes=, refused by an ids-only engine
     seed: int | None = None
     n: int = 1
     stop_token_ids: list[int] = field(default_factory=list)

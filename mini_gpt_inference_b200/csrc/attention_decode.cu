@@ -435,6 +435,15 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         merge_row<D>(part_out, part_ml, (pair0 + row) * max_splits, splits, weights, WCAP, out + (pair0 + row) * D, lane);
 }
 
+// Whether the CTA that finishes last merges the key blocks of its row (one launch), or a second
+// kernel does (two launches): a grid of more than MERGE_INSIDE_CTAS CTAs takes the second form.
+constexpr long long MERGE_INSIDE_CTAS = 1536;
+inline bool merges_inside(int n_tokens, int n_head, int n_kv_head, int max_splits) {
+    const int group = n_head / n_kv_head;
+    const long long head_tiles = (group + HEAD_ROWS - 1) / HEAD_ROWS;
+    return max_splits == 1 || (long long)n_tokens * n_kv_head * head_tiles * max_splits <= MERGE_INSIDE_CTAS;
+}
+
 template <int D>
 int launch(const void* qkv, const void* k_pages, const void* v_pages, const int* block_table,
            const int* token_request, const int* positions, void* out, float* part_out, float* part_ml,
@@ -457,8 +466,7 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
     // A grid of several waves (six CTAs fit an SM) merges in a second kernel, so that its CTAs do
     // not hold their shared memory while a counter answers; a small grid merges inside, which
     // saves a launch.
-    const long long ctas = (long long)n_tokens * n_kv_head * head_tiles * max_splits;
-    const int merge_inside = (max_splits == 1 || ctas <= 1536) ? 1 : 0;
+    const int merge_inside = merges_inside(n_tokens, n_head, n_kv_head, max_splits) ? 1 : 0;
     cudaError_t le =
         nh_max <= 8 ? mg_launch(attention_split_kernel<D, 1>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
                                 (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
@@ -487,6 +495,19 @@ MG_API int mg_attention_split_count(int max_context, int window, int head_dim) {
     int span = (window > 0 && window < max_context) ? window : max_context;
     if (span < 1) span = 1;
     return (span - 1) / split_keys(head_dim) + 1;
+}
+
+// Key positions per block at this head size (0 if the head size is not served).
+MG_API int mg_attention_split_keys(int head_dim) {
+    return (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256)
+               ? split_keys(head_dim) : 0;
+}
+
+// Kernels that mg_paged_attention_split() launches for these sizes: 1, or 2 when the merge of the
+// key blocks runs as a kernel of its own.
+MG_API int mg_attention_split_launches(int n_tokens, int n_head, int n_kv_head, int max_splits) {
+    if (n_tokens <= 0 || n_kv_head <= 0 || n_head % n_kv_head != 0) return 1;
+    return merges_inside(n_tokens, n_head, n_kv_head, max_splits) ? 1 : 2;
 }
 
 // Floats of scratch the split kernel needs (partial outputs, then maxima and sums).

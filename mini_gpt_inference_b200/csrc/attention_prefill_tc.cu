@@ -1,29 +1,32 @@
 // Causal attention of prompt portions over the paged cache on the 5th-generation tensor cores
 // (bfloat16, head_dim 64).
 //
-// A CTA takes up to 128 consecutive query tokens of one request and one head and walks over the
-// key blocks (128 positions, anchored at absolute multiples of 128) that those queries may see.
-// Keys and values come straight from the cache pages by TMA (one tile load per page and
-// tensor, 128-byte swizzle), two blocks ahead in rings of two stages each; the keys of this very
-// step were written to the pages before the launch, so a portion of a prompt and a whole prompt
-// read the same numbers.  Per key block:
+// A work item is up to 128 consecutive query tokens of one request, one head, and one chunk of
+// the key positions those queries may see (the host cuts long contexts into chunks, see
+// kernels/attention_plan.py); a CTA walks over its chunk in key blocks of 64 positions anchored
+// at absolute multiples of 64.  The CTA's six warps have three jobs and hand over through
+// mbarriers only (no __syncthreads in the loop, every wait bounded):
 //
-//   S = Q K^T        tcgen05.mma, 128 x 128, accumulator in TMEM; issued one block ahead, as soon
-//                    as every thread has taken the block before out of TMEM, so the tensor core
-//                    computes it while the threads are busy with that block;
-//   softmax          every thread owns one query row: it takes its whole row of S into registers
-//                    (four tcgen05.ld in flight, one wait), masks keys after its own position
-//                    (and before its window), and writes P = 2^(s - ref) as bfloat16 into a
-//                    swizzled shared-memory tile; the sum of P stays in 32-bit;
-//   O += P V         tcgen05.mma, 128 x 64, V taken as it lies in the page (MN-major operand),
-//                    accumulated in TMEM over all blocks.
+//   load warp        TMA tile loads of keys and values straight from the cache pages (one load
+//                    per page and tensor, 128-byte swizzle) into a ring of four stages; the keys of
+//                    this very step were written to the pages before the launch, so a portion of
+//                    a prompt and a whole prompt read the same numbers;
+//   issue warp       S = Q K^T by tcgen05.mma (128 x 64, accumulator in one of two TMEM buffers,
+//                    issued one block ahead of the softmax), then O += P V (128 x 64, V taken as
+//                    it lies in the page as an MN-major operand, accumulated in TMEM over all
+//                    blocks of the chunk);
+//   softmax warps    four warps, a thread per query row: the row of S comes from TMEM into
+//                    registers in one trip, keys after the row's own position (and before its
+//                    window) are masked, P = 2^(s - ref) goes as bfloat16 into one of two swizzled
+//                    shared-memory tiles; the sum of P stays in 32-bit.
 //
-// `ref`, the exponent P is taken relative to, follows the row's running maximum lazily: it moves
-// only when a block's maximum exceeds it by more than 2^8, and then the row's accumulator is
-// rescaled in TMEM (tcgen05.ld, multiply, tcgen05.st) and its sum with it.  After the first
-// blocks that almost never happens, so a block costs one pass over S and no pass over O; P lies
-// in (0, 2^8], which bfloat16 and the 32-bit sum hold with room to spare.  The result, O / sum,
-// does not depend on ref beyond rounding.
+// `ref`, the exponent P is taken relative to, is the maximum of the row's first block.  It moves
+// only if a later block's weights would leave the range 2^60 relative to it (REF_LIMIT); then the
+// row's accumulator is rescaled in TMEM (tcgen05.ld, multiply, tcgen05.st) and its sum with it.
+// That almost never happens, so a block costs one pass over S and none over O.  The result,
+// O / sum, does not depend on ref beyond rounding.  A tile whose keys were cut into chunks leaves
+// (O, ref, sum) per chunk in scratch; the chunk that finishes last (a counter per tile and head
+// that resets itself) merges them.  Two CTAs share an SM.
 //
 // Rows of the tile that belong to no query of this work item are computed and dropped; value
 // rows past the item's last key are cleared in shared memory before they are multiplied.  Pages
@@ -36,7 +39,7 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "blackwell.cuh"
 
 namespace {
 
@@ -48,7 +51,6 @@ constexpr int SOFTMAX_THREADS = 128;   // one per query row: warps 0..3, each on
 constexpr int ISSUE_WARP = 4;          // issues the tensor-core instructions
 constexpr int LOAD_WARP = 5;           // issues the TMA loads
 constexpr int THREADS = SOFTMAX_THREADS + 64;
-constexpr uint32_t SPIN_LIMIT = 2000000u;
 constexpr int Q_BYTES = BQ * D * 2;           // 16 KB
 constexpr int KV_BYTES = BK * D * 2;          // 8 KB per tensor and stage
 constexpr int P_BYTES = BQ * BK * 2;          // 16 KB, two of them
@@ -56,100 +58,6 @@ constexpr uint32_t TMEM_COLS = 256;           // S: two buffers of 64 columns, O
 constexpr uint32_t O_COL = 128;
 constexpr float REF_LIMIT = 1.152921504606846976e18f;   // 2^60: a block's sum of P above it moves the row's reference
 constexpr uint32_t ALIGN_SLACK = 768;         // bytes the tiles may have to move up to reach a 1024-byte boundary
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-// The same for a whole warp: true only if every lane saw the phase complete, so that what follows
-// (warp-wide tcgen05 instructions, votes) is reached by all lanes or by none.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
-        : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tmem_store_32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
-          "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// Descriptor of a tile whose rows are 128 bytes, 128-byte swizzle, 1024 bytes between groups of 8
-// rows (version 1, layout type 2).  Serves K-major operands (rows = M or N index) and MN-major
-// operands 64 elements wide (rows = K index) alike.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr >> 4) & 0x3FFFu);
-    d |= (uint64_t)1u << 16;
-    d |= (uint64_t)(1024u >> 4) << 32;
-    d |= (uint64_t)1u << 46;
-    d |= (uint64_t)2u << 61;
-    return d;
-}
-// kind::f16, D = F32, A = B = BF16, A K-major; bit 16 set: B is MN-major.
-__host__ __device__ constexpr uint32_t instr_desc(int m, int n, bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) |
-           ((uint32_t)(m >> 4) << 24);
-}
 
 struct __align__(8) Sync {
     uint64_t q_full, kv_full[KV_STAGES], kv_free[KV_STAGES], s_done[2], pv_done[2], block_done[2];
@@ -280,7 +188,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             ok = ok && warp_wait(smem_u32(&sync->kv_full[stage]), (j / KV_STAGES) & 1);
             tc_fence_after();
             if (lane == 0) {
-                constexpr uint32_t idesc_s = instr_desc(BQ, BK, false);
+                constexpr uint32_t idesc_s = instr_desc_bf16(BQ, BK, false);
                 const uint64_t dq = smem_desc_sw128(smem_u32(q_tile));
                 const uint64_t dk = smem_desc_sw128(smem_u32(k_tiles + stage * KV_BYTES));
 #pragma unroll
@@ -302,7 +210,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!warp_wait(smem_u32(&sync->block_done[it & 1]), (it >> 1) & 1)) { code = 29; break; }
             tc_fence_after();
             if (lane == 0) {
-                constexpr uint32_t idesc_pv = instr_desc(BQ, D, true);
+                constexpr uint32_t idesc_pv = instr_desc_bf16(BQ, D, true);
                 const uint32_t p_addr = smem_u32(p_tiles + (it & 1) * P_BYTES);
                 const uint32_t v_addr = smem_u32(v_tiles + (it % KV_STAGES) * KV_BYTES);
 #pragma unroll

@@ -26,6 +26,7 @@
 // The waits are bounded: if one runs out, the kernel records a code in `status` and stops.
 #include <math.h>
 
+#include "blackwell.cuh"
 #include "linear_epilogue.cuh"
 
 namespace {
@@ -35,7 +36,6 @@ constexpr int TILE_N = 8;            // weight rows per tile
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int XPAD = 64;             // bytes between rows beyond K bf16 (no bank conflicts)
-constexpr uint32_t SPIN_LIMIT = 4000000u;
 
 struct StreamArgs {
     const bf16* x;                   // [M, K] bfloat16 activations, or null with a LayerNorm prologue
@@ -57,26 +57,9 @@ struct StreamArgs {
     int* status;
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < SPIN_LIMIT; ++i) {
-        uint32_t done;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(done)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (done) return true;
-    }
-    return false;
 }
 
 template <int MT>   // token rows held: 8 (rows 8..15 of the A operand are zero), 16, 32 or 64

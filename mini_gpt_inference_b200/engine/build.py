@@ -47,8 +47,13 @@ def load_model(model_dir: str | Path | None = None, *, config=None, tensors=None
 
 
 def make_runner(loaded: LoadedModel, ops, page_tokens: int, num_pages: int,
-                max_requests: int, use_cuda_graphs: bool = True) -> ModelRunner:
-    manager = CacheManager(loaded.model.cache_specs(), page_tokens, num_pages, max_requests)
+                max_requests: int, use_cuda_graphs: bool = True,
+                max_step_tokens: int | None = None) -> ModelRunner:
+    """``page_tokens`` and ``num_pages``: the geometry of every cache group that names none of its
+    own.  ``max_step_tokens``: the most tokens one request brings in a step, if the caller keeps
+    to such a bound (cache groups with a window then get smaller pools)."""
+    manager = CacheManager(loaded.model.cache_specs(), page_tokens, num_pages, max_requests,
+                           window_slack_tokens=max_step_tokens)
     storage = CacheStorage(manager, loaded.dtype, loaded.device)
     return ModelRunner(loaded.model, manager, storage, ops, loaded.dtype, loaded.device,
                        use_cuda_graphs=use_cuda_graphs)

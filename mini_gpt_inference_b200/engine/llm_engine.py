@@ -8,8 +8,10 @@ A request is refused when it is added if its prompt plus ``max_tokens`` would ru
 position table (src/minigpt_infer/engine/engine.py:69-88).  ``generate`` is a convenience the
 reference's engine lacks (its ``generation.py`` has one for the static cache only).
 
-The engine works on token ids; text is the caller's business (the reference's tokenizer needs
-files from the network).  Stop conditions are therefore token ids (``stop_token_ids``).
+The engine works on token ids (the reference's tokenizer needs files from the network).  Stop
+conditions are token ids (``stop_token_ids``); with a ``token_bytes`` function from the caller's
+tokenizer the engine also streams text (``RequestOutput.text_delta``) and honours stop strings
+(``SamplingParams.stop``), see ``text.py``.  Without it a request that sets ``stop`` is refused.
 """
 
 from __future__ import annotations
@@ -26,6 +28,7 @@ from .build import LoadedModel, load_model, make_runner
 from .request import Request, RequestOutput, SequenceState
 from .runner import ModelRunner, StepEntry
 from .scheduler import Scheduler
+from .text import IncrementalText, cut_at_stop
 
 
 @dataclass
@@ -36,12 +39,15 @@ class _InFlight:
     ids_device: Any            # int32 ids on the device (input of the next step)
     ids_host: Any              # pinned copy in progress
     ready: Any                 # event recorded after the copy
+    status_host: Any = None    # pinned copy of the kernels' status word, taken with the ids
 
 
 class LLMEngine:
     def __init__(self, loaded: LoadedModel, engine_cfg: EngineConfig | None = None, ops=None,
-                 vocab_limit: int | None = None, seed: int = 0) -> None:
+                 vocab_limit: int | None = None, seed: int = 0, token_bytes=None) -> None:
         self.engine_cfg = engine_cfg or EngineConfig()
+        self.token_bytes = token_bytes                  # token id -> bytes, or None (ids only)
+        self._texts: dict[str, IncrementalText] = {}
         if ops is None:
             from ..kernels.ops import default_ops
 
@@ -50,7 +56,8 @@ class LLMEngine:
         self.config = loaded.config
         self.runner: ModelRunner = make_runner(
             loaded, ops, self.engine_cfg.block_size, self.engine_cfg.num_blocks,
-            self.engine_cfg.max_batch_size, self.engine_cfg.use_cuda_graphs)
+            self.engine_cfg.max_batch_size, self.engine_cfg.use_cuda_graphs,
+            max_step_tokens=self.engine_cfg.prefill_chunk)
         self.scheduler = Scheduler(self.runner.manager, self.engine_cfg.max_batch_size,
                                    self.engine_cfg.max_num_batched_tokens,
                                    self.engine_cfg.prefill_chunk)
@@ -66,6 +73,10 @@ class LLMEngine:
         self._inflight: _InFlight | None = None
         self._held_outputs: list[RequestOutput] = []
         self._pinned_ids = [None, None]
+        # The kernels' status word (non-zero after a bounded wait ran out) travels to the host with
+        # every step's ids and is checked where the ids are read.
+        self._watch_status = hasattr(ops, "status_to_host")
+        self._pinned_status = [None, None]
         self.num_overlapped_steps = 0
         self.num_steps = 0
         self.num_tokens_run = 0
@@ -96,6 +107,13 @@ class LLMEngine:
                 f"prompt_len ({prompt_len}) + max_tokens ({request.sampling_params.max_tokens}) "
                 f"= {longest} > {self.max_context}; this request can never finish without "
                 "running past the position table")
+        if request.sampling_params.stop and self.token_bytes is None:
+            raise ValueError(
+                f"request {request.request_id!r} sets stop strings, but the engine was given no "
+                "token_bytes function to turn ids into text; use stop_token_ids, or construct "
+                "the engine with token_bytes=")
+        if self.token_bytes is not None:
+            self._texts[request.request_id] = IncrementalText(self.token_bytes)
         seed = request.sampling_params.seed
         seq = SequenceState(request=request,
                             seed=self.sampler.fresh_seed() if seed is None else int(seed))
@@ -110,6 +128,7 @@ class LLMEngine:
         # (the cancelled request's own last token included, as it was generated before the call).
         self._held_outputs.extend(self._drain())
         self._sequences.pop(request_id, None)
+        self._texts.pop(request_id, None)
         return self.scheduler.cancel_by_id(request_id)
 
     # ---- one step ---------------------------------------------------------------------------
@@ -159,31 +178,29 @@ class LLMEngine:
                                                  dtype=torch.int32, pin_memory=True)
         host = self._pinned_ids[slot][: len(rows)]
         host.copy_(ids, non_blocking=True)
+        status_host = None
+        if self._watch_status:
+            status_host = self._pinned_status[slot] = self.runner.ops.status_to_host(self._pinned_status[slot])
         ready = torch.cuda.Event()
         ready.record()
         for seq in rows:
             seq.num_computed_tokens += 1
             seq.num_inflight += 1
-        self._inflight = _InFlight(rows, ids, host, ready)
+        self._inflight = _InFlight(rows, ids, host, ready, status_host)
         # while the device runs this step, read the ids of the step before
         return self._process(previous) if previous else []
 
     def _process(self, flight: _InFlight) -> list[RequestOutput]:
         """The ids of an earlier step have arrived (or are waited for): record them."""
         flight.ready.synchronize()
+        if flight.status_host is not None:
+            self.runner.ops.raise_on_status(flight.status_host)
         outputs = []
         for seq, token in zip(flight.seqs, flight.ids_host.tolist()):
             if seq.is_finished():
                 continue                                # it ended a step earlier; this token is dropped
             seq.num_inflight -= 1
-            seq.output_token_ids.append(int(token))
-            self.num_tokens_generated += 1
-            reason = self._check_finish(seq, int(token))
-            if reason is not None:
-                self.scheduler.finish(seq, reason)
-                self._sequences.pop(seq.request_id, None)
-            outputs.append(RequestOutput(seq.request_id, [int(token)], "", seq.is_finished(),
-                                         seq.finish_reason))
+            outputs.append(self._record(seq, int(token)))
         return outputs
 
     def _drain(self) -> list[RequestOutput]:
@@ -209,27 +226,49 @@ class LLMEngine:
             return []
         ids = self.sampler.sample(
             logits, [s.request.sampling_params for s in sampled], [s.seed for s in sampled],
-            [len(s.output_token_ids) for s in sampled]).tolist()
+            [len(s.output_token_ids) for s in sampled])
+        status_host = None
+        if self._watch_status:
+            status_host = self._pinned_status[0] = self.runner.ops.status_to_host(self._pinned_status[0])
+        ids = ids.tolist()                                   # waits for the step, the status copy included
+        if status_host is not None:
+            self.runner.ops.raise_on_status(status_host)
         outputs = []
         for seq, token in zip(sampled, ids):
-            seq.output_token_ids.append(int(token))
-            self.num_tokens_generated += 1
-            reason = self._check_finish(seq, int(token))
-            if reason is not None:
-                self.scheduler.finish(seq, reason)
-                self._sequences.pop(seq.request_id, None)
-            outputs.append(RequestOutput(seq.request_id, [int(token)], "", seq.is_finished(),
-                                         seq.finish_reason))
+            outputs.append(self._record(seq, int(token)))
         return outputs
 
+    def _record(self, seq: SequenceState, token: int) -> RequestOutput:
+        """A request's next token has reached the host: append it, extend its text, and end the
+        request if a finish condition holds."""
+        seq.output_token_ids.append(token)
+        self.num_tokens_generated += 1
+        text = self._texts.get(seq.request_id)
+        delta = text.add_token(token) if text is not None else ""
+        reason = self._check_finish(seq, token, text.text if text is not None else "")
+        whole = None
+        if reason is not None:
+            if text is not None:
+                delta += text.finalize()
+                whole = text.text
+                delta, stop = cut_at_stop(whole, delta, seq.request.sampling_params.stop)
+                if stop is not None:
+                    reason, whole = "stop", whole[: whole.find(stop)]
+            self.scheduler.finish(seq, reason)
+            self._sequences.pop(seq.request_id, None)
+            self._texts.pop(seq.request_id, None)
+        return RequestOutput(seq.request_id, [token], delta, seq.is_finished(), seq.finish_reason, whole)
+
     @staticmethod
-    def _check_finish(seq: SequenceState, token: int) -> str | None:
+    def _check_finish(seq: SequenceState, token: int, text: str = "") -> str | None:
         params = seq.request.sampling_params
         if seq.request.eot_token_id is not None and token == seq.request.eot_token_id:
             return "eot"
         if len(seq.output_token_ids) >= params.max_tokens:
             return "length"
         if token in params.stop_token_ids:
+            return "stop"
+        if any(stop and stop in text for stop in params.stop):
             return "stop"
         return None
 
@@ -238,7 +277,8 @@ class LLMEngine:
                  sampling_params: SamplingParams | Sequence[SamplingParams] | None = None,
                  eot_token_id: int | None = None) -> list[dict]:
         """Run the prompts to completion.  Returns, in the order of the prompts, dicts with
-        ``token_ids`` (generated only) and ``finish_reason``."""
+        ``token_ids`` (generated only), ``finish_reason`` and ``text`` (empty without a
+        ``token_bytes`` function)."""
         if sampling_params is None:
             sampling_params = SamplingParams()
         if isinstance(sampling_params, SamplingParams):
@@ -250,11 +290,14 @@ class LLMEngine:
             rid = f"gen-{self.num_steps}-{i}-{len(self._sequences)}"
             self.add_request(Request(rid, list(prompt), params, eot_token_id))
             ids.append(rid)
-        results = {rid: {"token_ids": [], "finish_reason": None} for rid in ids}
+        results = {rid: {"token_ids": [], "finish_reason": None, "text": ""} for rid in ids}
         while self.has_unfinished_requests():
             for out in self.step():
                 if out.request_id in results:
                     results[out.request_id]["token_ids"].extend(out.new_token_ids)
+                    results[out.request_id]["text"] += out.text_delta
+                    if out.text is not None:
+                        results[out.request_id]["text"] = out.text
                     if out.finished:
                         results[out.request_id]["finish_reason"] = out.finish_reason
         return [results[rid] for rid in ids]

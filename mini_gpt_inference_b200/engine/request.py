@@ -105,6 +105,10 @@ class RequestOutput:
     text_delta: str = ""
     finished: bool = False
     finish_reason: str | None = None
+    # On the output that finishes a request of an engine that makes text: the request's whole text,
+    # ending where a stop string begins.  (The deltas are handed out as they come; the beginning of
+    # a stop string that was spread over several tokens may already have gone out with them.)
+    text: str | None = None
 
 
 @dataclass

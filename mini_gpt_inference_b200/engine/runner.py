@@ -24,7 +24,8 @@ import torch
 
 from ..cache.manager import NO_PAGE, CacheFullError, CacheManager
 from ..cache.storage import CacheStorage
-from ..parts.context import KEY_CHUNK, StepContext, query_tiles
+from ..parts.base import Part
+from ..parts.context import HostBatch, StepContext, StepPlan
 from ..parts.model import DecoderModel
 
 
@@ -62,11 +63,12 @@ class _Packed:
     buf: np.ndarray
     offsets: list
     total: int
-    work_items: int
     q_len: list
     ctx_before: list
     state_slot: list
     wanted: int
+    extra: list = field(default_factory=list)      # (name, shape) of what the parts planned
+    signature: tuple = ()                          # what else decides the parts' launches
 
 
 @dataclass
@@ -98,14 +100,14 @@ class ModelRunner:
         self.max_context = limit if max_context is None else (
             max_context if limit is None else min(limit, max_context))
         if self.max_context is None:
-            self.max_context = manager.num_pages * manager.page_tokens
-        self.max_pages = manager.max_pages_per_request(self.max_context)
-        # work items of the tiled attention kernel that run at once, per head (two CTAs per SM)
-        heads = max((getattr(layer.mixer, "n_head", 0) for layer in getattr(model, "layers", [])), default=0)
-        self._attention_slots = None
-        if self.device.type == "cuda" and heads:
-            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
-            self._attention_slots = max(1, 2 * sms // heads)
+            self.max_context = (min(g.num_pages * g.page_tokens for g in manager.groups)
+                                if manager.groups else manager.num_pages * manager.page_tokens)
+        # width of a block table, per cache group (groups may differ in page size)
+        self.max_pages = [manager.max_pages_per_request(self.max_context, g)
+                          for g in range(len(manager.groups))]
+        # parts that prepare something on the host for every step (Part.plan_step)
+        self._planners = [part for part in model.parts()
+                          if getattr(type(part), "plan_step", Part.plan_step) is not Part.plan_step]
         self._pinned = None
         self._pinned_size = 0
         self.last_h2d_bytes = 0          # bytes of the last step's one host-to-device copy
@@ -233,10 +235,17 @@ class ModelRunner:
         P = self.max_pages
         host_q_len = [len(e.tokens) for e in entries]
         host_ctx = [m.get(e.request_id).length for e in entries]
-        # work items of the tiled attention kernels (runs of queries x chunks of keys)
-        work = query_tiles(host_q_len, host_ctx, self._attention_slots)
+        host_slot = [m.get(e.request_id).state_slot for e in entries]
+        # what the parts plan on the host for this batch (work lists of their kernels and the like)
+        plan = StepPlan()
+        if self._planners:
+            batch = HostBatch(host_q_len, host_ctx, host_slot, self.act_dtype)
+            for part in self._planners:
+                part.plan_step(batch, plan, self.ops)
+        planned = [(name, np.ascontiguousarray(a, dtype=np.int32)) for name, a in plan.arrays.items()]
         # layout of the packed int32 buffer
-        sizes = [N, N, N, R, R, R, R, W] + [R * P] * n_groups + [N] * n_groups + [5 * len(work)]
+        sizes = ([N, N, N, R, R, R, R, W] + [R * P[g] for g in range(n_groups)] + [N] * n_groups
+                 + [a.size for _, a in planned])
         offsets = [0]
         for size in sizes:
             offsets.append(offsets[-1] + size)
@@ -248,11 +257,10 @@ class ModelRunner:
 
         token_ids, positions, token_request = seg(0), seg(1), seg(2)
         q_start, q_len, ctx_before, state_slot, logit_rows = seg(3), seg(4), seg(5), seg(6), seg(7)
-        tables = [seg(8 + g).reshape(R, P) for g in range(n_groups)]
+        tables = [seg(8 + g).reshape(R, P[g]) for g in range(n_groups)]
         slots = [seg(8 + n_groups + g) for g in range(n_groups)]
         row = 0
         w = 0
-        pt = m.page_tokens
         for r, e in enumerate(entries):
             req = m.get(e.request_id)
             n = host_q_len[r]
@@ -262,13 +270,16 @@ class ModelRunner:
             token_request[row: row + n] = r
             if n == 1:
                 positions[row] = req.length
-                page_index, within = req.length // pt, req.length % pt
             else:
                 pos = positions[row: row + n]
                 pos[:] = np.arange(req.length, req.length + n, dtype=np.int32)
-                page_index = pos // pt
-                within = pos - page_index * pt
             for g in range(n_groups):
+                pt = m.groups[g].page_tokens
+                if n == 1:
+                    page_index, within = req.length // pt, req.length % pt
+                else:
+                    page_index = pos // pt
+                    within = pos - page_index * pt
                 held = req.tables[g]
                 tables[g][r, :len(held)] = held
                 tables[g][r, len(held):] = NO_PAGE
@@ -286,9 +297,10 @@ class ModelRunner:
                 w += 1
             row += n
 
-        seg(8 + 2 * n_groups)[:] = np.asarray(work, dtype=np.int32).reshape(-1)
-        return _Packed(buf, offsets, total, len(work), host_q_len, host_ctx,
-                       [m.get(e.request_id).state_slot for e in entries], W)
+        for i, (_, a) in enumerate(planned):
+            seg(8 + 2 * n_groups + i)[:] = a.reshape(-1)
+        return _Packed(buf, offsets, total, host_q_len, host_ctx, host_slot, W,
+                       [(name, a.shape) for name, a in planned], tuple(plan.signature))
 
     def _context(self, dev: torch.Tensor, packed: _Packed) -> StepContext:
         """Describe the batch whose packed integers lie in ``dev``."""
@@ -303,9 +315,10 @@ class ModelRunner:
             token_ids=dseg(0), positions=dseg(1), token_request=dseg(2),
             req_q_start=dseg(3), req_q_len=dseg(4), req_ctx_before=dseg(5),
             req_state_slot=dseg(6), logit_rows=dseg(7),
-            block_tables=[dseg(8 + g).view(R, P) for g in range(n_groups)],
+            block_tables=[dseg(8 + g).view(R, P[g]) for g in range(n_groups)],
             slot_mapping=[dseg(8 + n_groups + g) for g in range(n_groups)],
-            attn_work=dseg(8 + 2 * n_groups).view(packed.work_items, 5),
+            extra={name: dseg(8 + 2 * n_groups + i).view(shape)
+                   for i, (name, shape) in enumerate(packed.extra)},
             host_q_len=packed.q_len, host_ctx_before=packed.ctx_before,
             host_state_slot=packed.state_slot,
             max_q_len=max(packed.q_len),
@@ -340,7 +353,7 @@ class ModelRunner:
     # ---- decode steps as CUDA graphs ---------------------------------------------------------
     def _graph_layout(self, rows: int):
         g, pages = len(self.manager.groups), self.max_pages
-        sizes = [rows] * 8 + [rows * pages] * g + [rows] * g + [rows]     # last: token sources
+        sizes = [rows] * 8 + [rows * pages[i] for i in range(g)] + [rows] * g + [rows]     # last: token sources
         offsets = [0]
         for n in sizes:
             offsets.append(offsets[-1] + n)
@@ -359,7 +372,7 @@ class ModelRunner:
             ops=self.ops, act_dtype=self.act_dtype, num_tokens=rows, num_requests=rows,
             token_ids=seg(0), positions=seg(1), token_request=seg(2), req_q_start=seg(3),
             req_q_len=seg(4), req_ctx_before=seg(5), req_state_slot=seg(6), logit_rows=seg(7),
-            block_tables=[seg(8 + i).view(rows, pages) for i in range(g)],
+            block_tables=[seg(8 + i).view(rows, pages[i]) for i in range(g)],
             slot_mapping=[seg(8 + g + i) for i in range(g)],
             host_q_len=[1] * rows, host_ctx_before=[0] * rows, host_state_slot=[0] * rows,
             max_q_len=1, max_ctx_after=self.max_context, decode_only=True, storage=self.storage)
@@ -409,7 +422,7 @@ class ModelRunner:
         m = self.manager
         rows, off = state.rows, state.offsets
         buf = state.staging.numpy()
-        g, pages, pt = len(m.groups), self.max_pages, m.page_tokens
+        g, pages = len(m.groups), self.max_pages
         n = len(entries)
         if not state.row_tables:                                        # first use: everything is padding
             state.row_tables = [None] * rows
@@ -443,10 +456,11 @@ class ModelRunner:
             length = lengths[r]
             for i in range(g):
                 table = req.tables[i]
+                pt = m.groups[i].page_tokens
                 if fresh:
-                    base = off[8 + i] + r * pages
+                    base = off[8 + i] + r * pages[i]
                     buf[base: base + len(table)] = table
-                    buf[base + len(table): base + pages] = NO_PAGE
+                    buf[base + len(table): base + pages[i]] = NO_PAGE
                 page = table[length // pt]
                 if page == NO_PAGE:
                     raise StepError(f"request {entries[r].request_id!r} writes to a page it gave back")
@@ -455,8 +469,8 @@ class ModelRunner:
         for r in range(n, rows):                                        # rows that held a request last time
             if row_tables[r] is not None:
                 for i in range(g):
-                    base = off[8 + i] + r * pages
-                    buf[base: base + pages] = NO_PAGE
+                    base = off[8 + i] + r * pages[i]
+                    buf[base: base + pages[i]] = NO_PAGE
                 row_tables[r] = None
 
     def _graph_step(self, entries: Sequence[StepEntry], copy: bool, token_sources=None,
@@ -499,8 +513,7 @@ class ModelRunner:
         if not self.use_cuda_graphs or decode_only:
             return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
         # what the launches of a step depend on besides the device-side integers
-        merge = max(a + b for a, b in zip(packed.q_len, packed.ctx_before)) > KEY_CHUNK
-        key = (tuple(packed.q_len), packed.work_items, packed.wanted, merge)
+        key = (tuple(packed.q_len), packed.wanted, tuple(packed.extra), packed.signature)
         state = self._shape_graphs.get(key)
         if state is None:
             seen = self._shape_seen.get(key, 0) + 1

@@ -49,10 +49,10 @@ class Scheduler:
     def add_request(self, seq: SequenceState) -> None:
         # The last sampled token is never fed back, so the cache holds one token less.
         total = seq.prompt_len + seq.request.sampling_params.max_tokens - 1
-        if self.cache.pages_for(total) > self.cache.num_pages:
+        if not self.cache.can_ever_hold(total):
             raise ValueError(
-                f"request {seq.request_id!r} can never fit: {total} tokens need "
-                f"{self.cache.pages_for(total)} pages, the pool has {self.cache.num_pages}")
+                f"request {seq.request_id!r} can never fit: its {total} tokens need more pages "
+                f"than a pool has ({', '.join(f'{g.pages_for(total)} of {g.num_pages}' for g in self.cache.groups)})")
         seq.arrival = self._arrivals
         self._arrivals += 1
         self.waiting.append(seq)

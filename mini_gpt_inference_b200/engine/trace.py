@@ -20,8 +20,8 @@ import json
 import sys
 from pathlib import Path
 
-PAGE_ROUND = 64      # --max-tokens counts each request rounded up to this many tokens
-LIVE_REQUESTS = 8    # state slots; a trace keeps at most four requests live
+PAGE_ROUND = 64      # default of --page-round
+LIVE_REQUESTS = 8    # default of --live-requests
 
 
 def parse_args(argv=None):
@@ -30,8 +30,14 @@ def parse_args(argv=None):
     ap.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time, each request's count rounded "
+                         "up to a multiple of --page-round")
     ap.add_argument("--page-tokens", type=int, default=16, help="tokens per cache page")
+    ap.add_argument("--page-round", type=int, default=PAGE_ROUND,
+                    help="the multiple to which --max-tokens counts each request rounded up "
+                         "(a multiple of --page-tokens; default 64)")
+    ap.add_argument("--live-requests", type=int, default=LIVE_REQUESTS,
+                    help="most requests that are live at a time (state slots; default 8)")
     ap.add_argument("--device", default="cuda:0")
     return ap.parse_args(argv)
 
@@ -47,17 +53,18 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     from .build import load_model, make_runner
     from .runner import StepEntry
 
-    if args.max_tokens <= 0 or args.page_tokens <= 0 or PAGE_ROUND % args.page_tokens != 0:
-        print("trace_run: --max-tokens must be positive and --page-tokens must divide 64",
-              file=sys.stderr)
+    if (args.max_tokens <= 0 or args.page_tokens <= 0 or args.page_round <= 0 or args.live_requests <= 0
+            or args.page_round % args.page_tokens != 0):
+        print("trace_run: --max-tokens, --page-tokens, --page-round and --live-requests must be "
+              "positive, and --page-tokens must divide --page-round", file=sys.stderr)
         return 2
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
     ops = default_ops(args.device)
     loaded = load_model(args.model, dtype=args.dtype, device=args.device)
-    pool_tokens = (args.max_tokens + PAGE_ROUND - 1) // PAGE_ROUND * PAGE_ROUND
+    pool_tokens = (args.max_tokens + args.page_round - 1) // args.page_round * args.page_round
     runner = make_runner(loaded, ops, page_tokens=args.page_tokens,
-                         num_pages=pool_tokens // args.page_tokens, max_requests=LIVE_REQUESTS)
+                         num_pages=pool_tokens // args.page_tokens, max_requests=args.live_requests)
     for line in stdin:
         line = line.strip()
         if not line:
@@ -72,6 +79,8 @@ def main(argv=None, stdin=None, stdout=None) -> int:
             np.ascontiguousarray(host).tofile(out_dir / f"{step}.f32")
         elif entries:
             torch.cuda.synchronize()
+        if entries:
+            ops.check_status()                 # a kernel that gave up waiting ends the replay
         for rid in record.get("end", []):
             runner.finish(str(rid))
         stdout.write(f"done {step}\n")

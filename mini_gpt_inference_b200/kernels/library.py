@@ -43,6 +43,7 @@ _SIGNATURES = {
     "mg_copy_ints": [_P, _P, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_wait_probe": [_I, _P, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
@@ -82,6 +83,10 @@ def load(verbose: bool = True):
     lib.mg_argmax_parts.restype = c_int
     lib.mg_attention_split_count.argtypes = [c_int, c_int, c_int]
     lib.mg_attention_split_count.restype = c_int
+    lib.mg_attention_split_keys.argtypes = [c_int]
+    lib.mg_attention_split_keys.restype = c_int
+    lib.mg_attention_split_launches.argtypes = [c_int, c_int, c_int, c_int]
+    lib.mg_attention_split_launches.restype = c_int
     lib.mg_attention_split_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mg_attention_split_scratch_floats.restype = ctypes.c_longlong
     _lib = lib

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import library
-from ..parts.context import KEY_CHUNK
+from .attention_plan import KEY_CHUNK, query_tiles
 from .library import KernelLibraryError, check
 
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
@@ -83,6 +83,8 @@ class CudaOps:
         self.use_dependent_launch = True
         self.use_prefill_tc = True
         self._counter_buf = None
+        self._retired_counters = []
+        self._sm_count = None
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -118,9 +120,16 @@ class CudaOps:
 
     def _counters(self, count: int):
         """Zeroed ints that the split attention kernel uses to find its last block per row and
-        leaves zeroed; kept for the life of the object, grown on demand."""
+        leaves zeroed; kept for the life of the object, grown on demand (a buffer that was
+        handed out once is never freed)."""
         if self._counter_buf is None or self._counter_buf.numel() < count:
-            self._counter_buf = torch.zeros(max(count, 4096), dtype=torch.int32, device=self.device)
+            if self._counter_buf is not None:
+                # A captured graph may hold the old buffer's address: it stays alive (and zeroed,
+                # as its kernels leave it) for as long as this object does.
+                self._retired_counters.append(self._counter_buf)
+            self._counter_buf = torch.zeros(max(count, 4096, 2 * (self._counter_buf.numel()
+                                                                   if self._counter_buf is not None else 0)),
+                                            dtype=torch.int32, device=self.device)
         return self._counter_buf
 
     def set_dependent_launch(self, on: bool) -> None:
@@ -132,6 +141,27 @@ class CudaOps:
     def check_status(self) -> None:
         """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
         code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
+
+    def wait_probe(self, limit: int = 1000) -> None:
+        """Run a kernel whose bounded wait runs out (it waits ``limit`` tries on a barrier that is
+        never completed, with the wait all kernels share) and records its code in the status
+        word: what ``check_status`` and the engine then do can be seen without any fault."""
+        self._run(self.lib.mg_wait_probe(int(limit), _ptr(self.status), self._stream()), "wait probe")
+
+    def status_to_host(self, pinned=None):
+        """Queue a copy of the status word into pinned host memory on the current stream and
+        return that memory; once the stream has been synchronised (or an event recorded after
+        this call has), ``raise_on_status(pinned)`` tells whether a kernel before it gave up."""
+        if pinned is None:
+            pinned = torch.zeros(1, dtype=torch.int32, pin_memory=True)
+        pinned.copy_(self.status, non_blocking=True)
+        return pinned
+
+    def raise_on_status(self, pinned) -> None:
+        code = int(pinned[0])
         if code != 0:
             self.status.zero_()
             raise KernelLibraryError(f"a kernel gave up waiting (code {code}); its results are invalid")
@@ -370,6 +400,29 @@ class CudaOps:
                                    cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
 
     SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
+    PREFILL_TC_HEAD_DIMS = (64,)
+
+    def _attention_tiles_name(self, n_head: int) -> str:
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # work items of the tiled kernel that run at once, per head (two CTAs per SM)
+        return f"attention_tiles/{max(1, 2 * self._sm_count // n_head)}"
+
+    def plan_prompt_attention(self, batch, plan, n_head, n_kv_head, head_dim) -> None:
+        """Host half of the tiled prompt attention: the work list of a step (``attention_plan``),
+        added to ``plan`` under a name that layers of equal head count share.  Nothing is planned
+        for steps that the tiled kernel does not serve."""
+        if (batch.decode_only or batch.act_dtype != torch.bfloat16 or not self.use_tensor_cores
+                or not self.use_prefill_tc or head_dim not in self.PREFILL_TC_HEAD_DIMS):
+            return
+        name = self._attention_tiles_name(n_head)
+        if name not in plan.arrays:
+            import numpy as np
+
+            slots = int(name.rsplit("/", 1)[1])
+            work = query_tiles(batch.q_len, batch.ctx_before, slots)
+            plan.arrays[name] = np.asarray(work, dtype=np.int32).reshape(-1, 5)
+            plan.signature.append(("attention_merge", batch.max_ctx_after > KEY_CHUNK))
 
     def paged_attention(self, qkv, n_head, n_kv_head, head_dim, scale, cache, ctx):
         self._want(qkv, cache.k_pages.dtype, "qkv", 2)
@@ -389,15 +442,15 @@ class CudaOps:
                 _ptr(self._counters(n * n_head)), n, n_head, n_kv_head, head_dim, cache.page_tokens,
                 table.shape[1], window, splits, float(scale), _ptr(self.status), self._stream()),
                 "paged_attention (split)")
-            group = n_head // n_kv_head
-            if splits > 1 and n * n_kv_head * ((group + 15) // 16) * splits > 1536:
-                self.launches += 1         # a grid of several waves merges in a kernel of its own
+            # a grid of several waves merges in a kernel of its own
+            self.launches += self.lib.mg_attention_split_launches(n, n_head, n_kv_head, splits) - 1
             return out
-        work = getattr(ctx, "attn_work", None)
+        work = getattr(ctx, "extra", {}).get(self._attention_tiles_name(n_head))
         if (qkv.dtype == torch.bfloat16 and work is not None and work.shape[0] > 0
-                and self.use_tensor_cores and self.use_prefill_tc):
+                and self.use_tensor_cores and self.use_prefill_tc
+                and head_dim in self.PREFILL_TC_HEAD_DIMS):
             # portions of prompts: query tiles of 128 on the tensor cores
-            self._want(work, torch.int32, "attn_work", 2)
+            self._want(work, torch.int32, "attention tiles", 2)
             # tiles cut along the keys leave partial rows in scratch; the part that finishes last merges them
             merge = int(ctx.max_ctx_after > KEY_CHUNK)
             partial = counters = None

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from ..config.model_config import GPTConfig
 from ..config.registry import register_model
-from ..parts.spec import LayerCall, LayerSpec, ModelSpec, PartSpec
+from ..parts.spec import LayerCall, ModelSpec, PartSpec, pre_norm_layer
 
 
 @register_model("MiniGPTLMHeadModel", "minigpt", "MiniGPT", "GPT", config_class=GPTConfig)
@@ -17,7 +17,7 @@ def describe_minigpt(cfg: GPTConfig) -> ModelSpec:
     norm = {"width": cfg.n_embd, "eps": cfg.layer_norm_epsilon, "bias": cfg.bias}
     layers = []
     for i in range(cfg.n_layer):
-        layers.append(LayerSpec(
+        layers.append(pre_norm_layer(
             prefix=f"blocks.{i}.",
             norm1=PartSpec("layernorm", norm, "ln1"),
             mixer=PartSpec("causal_attention", {
@@ -26,8 +26,7 @@ def describe_minigpt(cfg: GPTConfig) -> ModelSpec:
             norm2=PartSpec("layernorm", norm, "ln2"),
             feed_forward=PartSpec("dense_mlp", {
                 "width": cfg.n_embd, "inner": cfg.n_inner, "bias": cfg.bias,
-                "activation": cfg.activation_function}, "mlp"),
-            arrangement="pre_norm"))
+                "activation": cfg.activation_function}, "mlp")))
     return ModelSpec(
         architecture=cfg.architecture,
         width=cfg.n_embd,

@@ -11,7 +11,9 @@ src/minigpt_infer/cache/paged.py:139-165).  The output projection adds into the
 residual stream (src/minigpt_infer/model.py:90, 113).
 
 Heads may share keys (``n_kv_head`` divides ``n_head``) and may look back only
-``window`` positions; this architecture uses neither, the part takes them as parameters.
+``window`` positions; this architecture uses neither, the part takes them as parameters, and
+with them the page size and the pool size of its cache group (layers that agree in all of these
+share a group).
 """
 
 from __future__ import annotations
@@ -29,7 +31,8 @@ class CausalAttention(Mixer):
 
     def __init__(self, prefix: str, width: int, n_head: int, head_dim: int, bias: bool,
                  n_kv_head: int | None = None, scale: float | None = None,
-                 window: int | None = None, position=None) -> None:
+                 window: int | None = None, cache_page_tokens: int | None = None,
+                 cache_pages: int | None = None, position=None) -> None:
         super().__init__(prefix)
         self.width, self.n_head, self.head_dim = width, n_head, head_dim
         self.n_kv_head = n_head if n_kv_head is None else n_kv_head
@@ -38,6 +41,8 @@ class CausalAttention(Mixer):
         self.has_bias = bool(bias)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.window = window
+        # page size and pool size of this layer's cache group (None: the cache manager's)
+        self.cache_page_tokens, self.cache_pages = cache_page_tokens, cache_pages
         self.position = position
         self.qkv_weight = self.qkv_bias = self.proj_weight = self.proj_bias = None
 
@@ -58,7 +63,8 @@ class CausalAttention(Mixer):
         return specs
 
     def cache_spec(self):
-        return PagedKVSpec(self.n_kv_head, self.head_dim, self.window)
+        return PagedKVSpec(self.n_kv_head, self.head_dim, self.window, self.cache_page_tokens,
+                           self.cache_pages)
 
     accepts_deferred_norm = True
 
@@ -67,6 +73,12 @@ class CausalAttention(Mixer):
 
         return (self.position is not None
                 and type(self.position).rotate is not PositionEncoding.rotate)
+
+    def plan_step(self, batch, plan, ops) -> None:
+        # the kernel set cuts prompt portions into the tiles of its attention kernel, if it has one
+        planner = getattr(ops, "plan_prompt_attention", None)
+        if planner is not None:
+            planner(batch, plan, self.n_head, self.n_kv_head, self.head_dim)
 
     def forward(self, ctx, cache, y, residual32) -> None:
         ops = ctx.ops

@@ -42,6 +42,14 @@ class Part:
     def tensor_specs(self) -> dict[str, TensorSpec]:
         return {}
 
+    def plan_step(self, batch, plan, ops) -> None:
+        """Prepare on the host what this part's kernels need for one step besides the batch's own
+        integers.  ``batch`` is a ``HostBatch`` (tokens per request, tokens already cached, state
+        slots); add int32 arrays to ``plan.arrays[name]`` (they reach ``forward`` as
+        ``ctx.extra[name]`` on the device) and to ``plan.signature`` whatever else decides the
+        launches.  Called for every step that is not replayed from a captured single-token graph;
+        a part that needs a plan in those too sets ``graph_safe = False``.  Default: nothing."""
+
     def bind(self, tensors: Mapping[str, Any]) -> None:
         """Receive device tensors by full name (only the names of tensor_specs)."""
         for full_name in self.tensor_specs():

@@ -16,6 +16,42 @@ import torch
 
 
 @dataclass
+class HostBatch:
+    """The batch of a step as the host knows it before anything is on the device: what a part's
+    ``plan_step`` sees."""
+
+    q_len: list                            # per request: tokens it brings
+    ctx_before: list                       # per request: tokens already in the cache
+    state_slot: list                       # per request: its slot of the state pool
+    act_dtype: Any = None
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(self.q_len)
+
+    @property
+    def decode_only(self) -> bool:
+        return all(n == 1 for n in self.q_len)
+
+    @property
+    def max_ctx_after(self) -> int:
+        return max(a + b for a, b in zip(self.q_len, self.ctx_before))
+
+
+@dataclass
+class StepPlan:
+    """What parts prepare on the host for one step.  ``arrays``: int32 numpy arrays by name; the
+    step function packs them into the step's one upload and hands them to the parts as
+    ``ctx.extra[name]`` (same shape, on the device).  Parts that would plan the same thing share
+    a name, and the second one finds it there.  ``signature``: anything else that decides which
+    kernels a part launches with which sizes (a step is replayed from a captured graph only if
+    the token counts, the shapes of the arrays and the signature all repeat)."""
+
+    arrays: dict = field(default_factory=dict)
+    signature: list = field(default_factory=list)
+
+
+@dataclass
 class StepContext:
     ops: Any                              # the kernel set the parts call
     act_dtype: torch.dtype                # compute dtype between norm and projection
@@ -32,8 +68,8 @@ class StepContext:
     block_tables: list[torch.Tensor]      # per cache group [R, max_pages], -1 = no page
     slot_mapping: list[torch.Tensor]      # per cache group [N] flat row of each new token
     logit_rows: torch.Tensor              # [W] rows whose logits are wanted
-    # work list of kernels that take tiles of queries: see query_tiles(); None if not built
-    attn_work: torch.Tensor | None = None
+    # What parts planned for this step on the host (``Part.plan_step``): int32 tensors by name.
+    extra: dict = field(default_factory=dict)
     # Optional: where token_source[i] >= 0, token i is fed_ids[token_source[i]] (a token the step
     # before sampled, still on the device) instead of token_ids[i].
     token_source: torch.Tensor | None = None
@@ -54,47 +90,3 @@ class StepContext:
 
     def cache_view(self, cache_layer: int, writes: bool = True):
         return self.storage.layer_view(cache_layer, writes) if self.storage is not None else None
-
-
-QUERY_TILE = 128       # most consecutive tokens of one request in a tile
-KEY_CHUNK = 512        # most key positions one work item walks over
-
-
-def query_tiles(q_lens, ctx_befores, slots=None):
-    """Cut a ragged batch into work items ``(request, first row, rows, chunk, chunks)``.
-
-    The tokens of each request are cut into runs of at most QUERY_TILE rows.  The keys a run
-    may see (positions 0 .. its last token) are cut into ``chunks`` parts of at most KEY_CHUNK
-    positions, one work item each, so that a long context is spread over several CTAs; their
-    partial results are merged afterwards.  Items of one run are consecutive, chunk 0 first; the
-    runs come longest item first, so that when the grid does not fit the GPU at once, the CTAs
-    that start last are the short ones.
-
-    ``slots``: how many work items the GPU runs at once (per head).  If the items exceed it by
-    less than half, longer parts (up to twice KEY_CHUNK) are tried, so that a second round of a
-    few CTAs is not added to the first."""
-
-    runs = []                                     # (request, first row, rows, keys it may see)
-    row = 0
-    for r, (n, before) in enumerate(zip(q_lens, ctx_befores)):
-        for b in range(0, n, QUERY_TILE):
-            rows = min(QUERY_TILE, n - b)
-            runs.append((r, row + b, rows, before + b + rows))
-        row += n
-
-    def count(limit):
-        return sum(max(1, -(-keys // limit)) for _, _, _, keys in runs)
-
-    limit = KEY_CHUNK
-    items = count(limit)
-    if slots and slots < items <= slots + slots // 2:
-        for longer in range(KEY_CHUNK + QUERY_TILE, 2 * KEY_CHUNK + 1, QUERY_TILE):
-            if count(longer) <= slots:
-                limit = longer
-                break
-    cut = []
-    for i, (r, row0, rows, keys) in enumerate(runs):
-        chunks = max(1, -(-keys // limit))
-        cut.append((-(keys / chunks), i, r, row0, rows, chunks))
-    cut.sort()
-    return [(r, row0, rows, c, chunks) for _, _, r, row0, rows, chunks in cut for c in range(chunks)]

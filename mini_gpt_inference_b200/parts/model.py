@@ -24,12 +24,14 @@ class DecoderModel:
         self.layers: list[Layer] = []
         for layer_spec in spec.layers:
             p = layer_spec.prefix
-            self.layers.append(Layer(
-                norm1=NORMS.build(layer_spec.norm1, p),
-                mixer=MIXERS.build(layer_spec.mixer, p, position=self.position),
-                norm2=NORMS.build(layer_spec.norm2, p),
-                feed_forward=FEED_FORWARDS.build(layer_spec.feed_forward, p),
-                run=ARRANGEMENTS.get(layer_spec.arrangement)))
+            parts, roles = {}, {}
+            for name, part_spec in layer_spec.parts.items():
+                role = roles[name] = layer_spec.role_of(name)
+                if role == "mixer":
+                    parts[name] = MIXERS.build(part_spec, p, position=self.position)
+                else:
+                    parts[name] = (NORMS if role == "norm" else FEED_FORWARDS).build(part_spec, p)
+            self.layers.append(Layer(parts, roles, ARRANGEMENTS.get(layer_spec.arrangement), p))
         self.final_norm = NORMS.build(spec.final_norm, "")
         self.head = HEADS.build(spec.head, "", embedding=self.embedding)
         self.layer_order = spec.layer_order
@@ -60,7 +62,7 @@ class DecoderModel:
         return self.position.max_positions
 
     def cache_specs(self) -> list[Any]:
-        return [layer.mixer.cache_spec() for layer in self.layers]
+        return [layer.cache_spec() for layer in self.layers]
 
     # ---- one step ------------------------------------------------------------------------
     def forward(self, ctx):

@@ -12,21 +12,44 @@ from dataclasses import dataclass, field
 from typing import Any, Mapping
 
 
+ROLES = ("norm", "mixer", "feed_forward")
+
+
 @dataclass(frozen=True)
 class PartSpec:
     kind: str                               # key in the part registry of its role
     params: Mapping[str, Any] = field(default_factory=dict)
     name: str = ""                          # weight-name prefix inside its parent ("ln1", "attn")
+    role: str = ""                          # inside a layer: "norm" | "mixer" | "feed_forward"; if empty,
+                                            # taken from the part's name in the layer (see LayerSpec)
 
 
 @dataclass(frozen=True)
 class LayerSpec:
+    """A layer is a bag of named parts and the name of the arrangement that wires them.  What
+    names an arrangement expects is the arrangement's business (``pre_norm`` wants ``norm1``,
+    ``mixer``, ``norm2``, ``feed_forward``); a layer with one norm, without a feed-forward or
+    with two mixers is another arrangement over another bag, not another schema."""
+
     prefix: str                             # weight-name prefix of the layer ("blocks.0.")
-    mixer: PartSpec
-    feed_forward: PartSpec
-    norm1: PartSpec
-    norm2: PartSpec
+    parts: Mapping[str, PartSpec]           # name in the layer -> part
     arrangement: str = "pre_norm"           # key in the block-arrangement registry
+
+    def role_of(self, name: str) -> str:
+        role = self.parts[name].role
+        if not role:
+            role = next((r for r in ROLES if name == r or name.startswith(r)), "")
+        if role not in ROLES:
+            raise ValueError(f"layer {self.prefix!r}: part {name!r} has no role; set PartSpec.role to "
+                             f"one of {ROLES} or name it after its role")
+        return role
+
+
+def pre_norm_layer(prefix: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec,
+                   feed_forward: PartSpec) -> LayerSpec:
+    """The usual block: ``x += mixer(norm1(x)); x += feed_forward(norm2(x))``."""
+    return LayerSpec(prefix, {"norm1": norm1, "mixer": mixer, "norm2": norm2,
+                              "feed_forward": feed_forward}, "pre_norm")
 
 
 @dataclass(frozen=True)

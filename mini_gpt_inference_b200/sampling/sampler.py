@@ -27,6 +27,28 @@ class Sampler:
         self.vocab_limit = vocab_limit
         self._seed_source = np.random.SeedSequence(base_seed)
         self._rng = np.random.default_rng(self._seed_source)
+        # Two pinned staging buffers for the per-row parameters, used in turn: the copy to the
+        # device is asynchronous, so the host does not wait for the step that is still running.
+        self._staging = [None, None]
+        self._copied = [None, None]
+        self._turn = 0
+
+    def _to_device(self, packed: np.ndarray) -> torch.Tensor:
+        if self.device.type != "cuda":
+            return torch.from_numpy(packed).to(self.device)
+        slot, self._turn = self._turn, self._turn ^ 1
+        if self._copied[slot] is not None:
+            self._copied[slot].synchronize()              # the copy before last has left this buffer
+        need = packed.size
+        if self._staging[slot] is None or self._staging[slot].numel() < need:
+            self._staging[slot] = torch.empty(max(need, 6 * 64), dtype=torch.int32, pin_memory=True)
+        flat = self._staging[slot][:need]
+        flat.numpy()[:] = packed.reshape(-1)
+        dev = flat.to(self.device, non_blocking=True).view(packed.shape)
+        if self._copied[slot] is None:
+            self._copied[slot] = torch.cuda.Event()
+        self._copied[slot].record()
+        return dev
 
     def fresh_seed(self) -> int:
         """A seed for a request that gave none."""
@@ -57,7 +79,7 @@ class Sampler:
         packed[3] = _as_i32([s & _MASK32 for s in seeds])
         packed[4] = _as_i32([(s >> 32) & _MASK32 for s in seeds])
         packed[5] = _as_i32([n & _MASK32 for n in draw_numbers])
-        dev = torch.from_numpy(packed).to(self.device, non_blocking=False)
+        dev = self._to_device(packed)
         use_k = any(p.top_k is not None and p.top_k < vocab for p in params)
         use_p = any(p.top_p is not None and p.top_p < 1.0 for p in params)
         extra = {} if out is None else {"out": out}

@@ -30,11 +30,12 @@ _WRAPPER_PREFIXES = ("module.", "_orig_mod.")
 class WeightsError(RuntimeError):
     """The checkpoint does not fit the model.  Carries the three lists."""
 
-    def __init__(self, message: str, missing=(), unexpected=(), wrong_shape=()) -> None:
+    def __init__(self, message: str, missing=(), unexpected=(), wrong_shape=(), wrong_dtype=()) -> None:
         super().__init__(message)
         self.missing = list(missing)
         self.unexpected = list(unexpected)
         self.wrong_shape = list(wrong_shape)
+        self.wrong_dtype = list(wrong_dtype)
 
 
 def strip_wrapper_prefixes(tensors: Mapping[str, torch.Tensor]) -> dict[str, torch.Tensor]:
@@ -45,16 +46,16 @@ def strip_wrapper_prefixes(tensors: Mapping[str, torch.Tensor]) -> dict[str, tor
     return out
 
 
-def _keep_storage_dtype(name: str, t: torch.Tensor, role: str) -> torch.Tensor:
+_INTEGER_DTYPES = (torch.int8, torch.uint8, torch.int16, torch.int32, torch.int64)
+
+
+def _keep_storage_dtype(t: torch.Tensor, role: str) -> torch.Tensor | str:
+    """The tensor as it is kept (bfloat16 stays bfloat16, 32-bit stays 32-bit, integer tables
+    become int32), or a string that says what was expected if its stored dtype is none of these:
+    nothing is converted silently."""
     if role == "table":
-        if t.dtype.is_floating_point:
-            raise WeightsError(f"tensor {name!r} must be an integer table, is {t.dtype}")
-        return t.to(torch.int32)
-    if t.dtype in (torch.bfloat16, torch.float32):
-        return t
-    if t.dtype in (torch.float16, torch.float64):
-        return t.to(torch.float32)
-    raise WeightsError(f"tensor {name!r} has dtype {t.dtype}; expected a floating tensor")
+        return t.to(torch.int32) if t.dtype in _INTEGER_DTYPES else "an integer table"
+    return t if t.dtype in (torch.bfloat16, torch.float32) else "bfloat16 or float32"
 
 
 def check_and_bind(tensors: Mapping[str, torch.Tensor],
@@ -62,7 +63,7 @@ def check_and_bind(tensors: Mapping[str, torch.Tensor],
                    ) -> dict[str, torch.Tensor]:
     """Match ``tensors`` against ``expected``; raise one WeightsError naming every fault."""
     tensors = strip_wrapper_prefixes(tensors)
-    missing, unexpected, wrong_shape, unequal = [], [], [], []
+    missing, unexpected, wrong_shape, wrong_dtype, unequal = [], [], [], [], []
     bound: dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
         if name not in tensors:
@@ -79,11 +80,15 @@ def check_and_bind(tensors: Mapping[str, torch.Tensor],
                     other.to(torch.float32), t.to(torch.float32)):
                 unequal.append(f"{name} differs from {spec.optional_alias_of} (they are tied)")
             continue
-        bound[name] = _keep_storage_dtype(name, t, spec.role)
+        kept = _keep_storage_dtype(t, spec.role)
+        if isinstance(kept, str):
+            wrong_dtype.append(f"{name}: checkpoint {str(t.dtype).replace('torch.', '')}, model wants {kept}")
+            continue
+        bound[name] = kept
     for name in tensors:
         if name not in expected:
             unexpected.append(name)
-    if missing or unexpected or wrong_shape or unequal:
+    if missing or unexpected or wrong_shape or wrong_dtype or unequal:
         parts = [f"{where} does not match the model:"]
         if missing:
             parts.append(f"  missing ({len(missing)}): " + ", ".join(missing))
@@ -91,9 +96,11 @@ def check_and_bind(tensors: Mapping[str, torch.Tensor],
             parts.append(f"  unexpected ({len(unexpected)}): " + ", ".join(unexpected))
         if wrong_shape:
             parts.append(f"  wrong shape ({len(wrong_shape)}): " + "; ".join(wrong_shape))
+        if wrong_dtype:
+            parts.append(f"  wrong dtype ({len(wrong_dtype)}): " + "; ".join(wrong_dtype))
         if unequal:
             parts.append("  tied tensors differ: " + "; ".join(unequal))
-        raise WeightsError("\n".join(parts), missing, unexpected, wrong_shape + unequal)
+        raise WeightsError("\n".join(parts), missing, unexpected, wrong_shape + unequal, wrong_dtype)
     return bound
 
 

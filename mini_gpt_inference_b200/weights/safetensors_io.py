@@ -44,17 +44,38 @@ def read_header(path: str | Path) -> tuple[dict, int]:
             header = json.loads(f.read(n))
         except (json.JSONDecodeError, UnicodeDecodeError) as exc:
             raise SafetensorsError(f"{path}: header is not JSON: {exc}") from exc
+    if not isinstance(header, dict):
+        raise SafetensorsError(f"{path}: header is not a JSON object")
     header.pop("__metadata__", None)
+    spans = []
     for name, info in header.items():
-        begin, end = info["data_offsets"]
-        if info["dtype"] not in _DTYPES:
-            raise SafetensorsError(f"{path}: tensor {name!r} has unsupported dtype {info['dtype']}")
+        if not isinstance(info, dict):
+            raise SafetensorsError(f"{path}: entry {name!r} of the header is not an object")
+        dtype, shape, offsets = info.get("dtype"), info.get("shape"), info.get("data_offsets")
+        if not isinstance(dtype, str) or dtype not in _DTYPES:
+            raise SafetensorsError(f"{path}: tensor {name!r} has unsupported dtype {dtype!r}")
+
+        def is_int(v):
+            return isinstance(v, int) and not isinstance(v, bool)
+
+        if not isinstance(shape, list) or not all(is_int(d) and d >= 0 for d in shape):
+            raise SafetensorsError(f"{path}: tensor {name!r} has a malformed shape {shape!r}")
+        if (not isinstance(offsets, list) or len(offsets) != 2 or not all(is_int(v) for v in offsets)
+                or not 0 <= offsets[0] <= offsets[1]):
+            raise SafetensorsError(f"{path}: tensor {name!r} has malformed data_offsets {offsets!r}")
+        begin, end = offsets
         count = 1
-        for d in info["shape"]:
+        for d in shape:
             count *= d
-        width = torch.empty((), dtype=_DTYPES[info["dtype"]]).element_size()
-        if end - begin != count * width or 8 + n + end > size or begin < 0:
+        width = torch.empty((), dtype=_DTYPES[dtype]).element_size()
+        if end - begin != count * width or 8 + n + end > size:
             raise SafetensorsError(f"{path}: tensor {name!r} has inconsistent offsets")
+        if end > begin:
+            spans.append((begin, end, name))
+    spans.sort()
+    for (_, end_a, a), (begin_b, _, b) in zip(spans, spans[1:]):
+        if begin_b < end_a:
+            raise SafetensorsError(f"{path}: tensors {a!r} and {b!r} overlap in the file")
     return header, 8 + n
 
 

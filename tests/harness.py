@@ -56,16 +56,17 @@ def tokens_for(cfg, length: int, seed: int) -> list[int]:
     return torch.randint(0, cfg.vocab_size, (length,), generator=gen).tolist()
 
 
-def plain_logits(cfg, tensors, tokens) -> torch.Tensor:
+def plain_logits(cfg, tensors, tokens, rows=None) -> torch.Tensor:
     return plain_gpt.forward_logits(tokens, tensors, cfg.n_layer, cfg.n_head,
-                                    cfg.layer_norm_epsilon)
+                                    cfg.layer_norm_epsilon, rows=rows)
 
 
-def gpu_runner(cfg, tensors, dtype: str, page_tokens: int, num_pages: int, max_requests: int = 8):
+def gpu_runner(cfg, tensors, dtype: str, page_tokens: int, num_pages: int, max_requests: int = 8,
+               ops=None):
     from mini_gpt_inference_b200.kernels.ops import default_ops
 
     loaded = load_model(config=cfg, tensors=tensors, dtype=dtype, device="cuda:0")
-    return make_runner(loaded, default_ops("cuda:0"), page_tokens, num_pages, max_requests)
+    return make_runner(loaded, ops or default_ops("cuda:0"), page_tokens, num_pages, max_requests)
 
 
 def first_mismatch(got: torch.Tensor, want: torch.Tensor, tol: float):

@@ -89,14 +89,18 @@ def block(x: torch.Tensor, w: dict, prefix: str, n_head: int, eps: float) -> tor
 
 
 def forward_logits(tokens, w: dict, n_layer: int, n_head: int, eps: float = 1e-5,
-                   dtype=torch.float64) -> torch.Tensor:
+                   dtype=torch.float64, rows=None) -> torch.Tensor:
     """Logits at every position of one whole sequence: embed, blocks in order, final
     LayerNorm, tied head without bias (src/minigpt_infer/reference.py:105-114,
-    src/minigpt_infer/model.py:128-130, 183-187)."""
+    src/minigpt_infer/model.py:128-130, 183-187).  ``rows``: only these positions meet the
+    head (the whole sequence still runs through the blocks); with a vocabulary of tens of
+    thousands the head is most of the work."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     x = embed(tokens, w, dtype)
     for i in range(n_layer):
         x = block(x, w, f"blocks.{i}.", n_head, eps)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long)]
     x = layer_norm(x, w["ln_f.weight"], w.get("ln_f.bias"), eps)
     return x @ w["tok_emb.weight"].to(dtype).T
 

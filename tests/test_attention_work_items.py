@@ -8,7 +8,7 @@ import random
 
 import pytest
 
-from mini_gpt_inference_b200.parts.context import KEY_CHUNK, QUERY_TILE, query_tiles
+from mini_gpt_inference_b200.kernels.attention_plan import KEY_CHUNK, QUERY_TILE, query_tiles
 
 
 def _check(q_lens, ctx_befores, slots=None):

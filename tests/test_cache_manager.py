@@ -128,10 +128,39 @@ def test_every_change_of_a_table_shows_in_its_version():
     assert again.serial != a.serial
 
 
-def test_random_orders_lose_nothing():
+def test_groups_have_page_geometries_of_their_own():
+    """A group takes the manager's page size and pool unless its spec names others; a windowed
+    group is sized for what its requests can hold at once when the step size is known."""
+    specs = [PagedKVSpec(2, 16), PagedKVSpec(2, 16, page_tokens=16), PagedKVSpec(2, 16, window=10),
+             PagedKVSpec(1, 8, page_tokens=2, num_pages=7)]
+    m = CacheManager(specs, page_tokens=4, num_pages=32, max_requests=3, window_slack_tokens=6)
+    # default; same tokens in larger pages; window 10 + 6 per step -> 4 + 2 pages per request slot; as named
+    assert [(g.page_tokens, g.num_pages) for g in m.groups] == [(4, 32), (16, 8), (4, 18), (2, 7)]
+    assert [m.max_pages_per_request(40, g) for g in range(4)] == [10, 3, 10, 20]
+    m.admit("a")
+    assert m.pages_needed("a", 13) == [4, 1, 4, 7]
+    assert m.tokens_that_fit("a") == 14                          # the smallest pool decides: 7 pages of 2
+    assert m.reserve("a", 13) and m.get("a").capacity == 14
+    m.advance("a", 13)
+    assert not m.reserve("a", 15) and m.get("a").capacity == 14  # group 3 is full: nothing was taken anywhere
+    assert [len(t) for t in m.get("a").tables] == [4, 1, 4, 7]
+    assert m.slot_of("a", 1, 13 - 1) == m.block_table("a", 1)[0] * 16 + 12
+    assert m.slot_of("a", 3, 5) == m.block_table("a", 3)[2] * 2 + 1
+    assert m.can_ever_hold(14) and not m.can_ever_hold(15)
+    m.check()
+    m.release("a")
+    assert all(g.pool.num_free == g.num_pages for g in m.groups)
+    # without a known step size a windowed group keeps the default pool
+    assert CacheManager(specs[2:3], 4, 32, 3).groups[0].num_pages == 32
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_random_orders_lose_nothing(mixed):
     rng = random.Random(0)
-    m = CacheManager([PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=10), FixedStateSpec((3,))],
-                     page_tokens=4, num_pages=24, max_requests=5)
+    specs = [PagedKVSpec(2, 8), PagedKVSpec(2, 8, window=10), FixedStateSpec((3,))]
+    if mixed:
+        specs += [PagedKVSpec(2, 8, page_tokens=8, num_pages=14), PagedKVSpec(1, 8, window=5, page_tokens=2)]
+    m = CacheManager(specs, page_tokens=4, num_pages=24, max_requests=5)
     live: dict[str, int] = {}
     counter = 0
     for _ in range(3000):
@@ -160,7 +189,8 @@ def test_random_orders_lose_nothing():
     for rid in list(live):
         m.release(rid)
     m.check()
-    assert all(g.pool.num_free == 24 for g in m.groups) and m.slots.num_free == 5
+    assert all(g.pool.num_free == g.num_pages for g in m.groups) and m.slots.num_free == 5
+    assert [g.num_pages for g in m.groups] == ([24, 24, 14, 48] if mixed else [24, 24])
     assert m.stats()["internal_fragmentation_slots"] == 0
 
 

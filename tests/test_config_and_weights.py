@@ -193,5 +193,36 @@ def test_malformed_safetensors_files_give_clear_errors(tmp_path):
     attempt(struct.pack("<Q", 5) + b"hello", "not JSON")
     attempt(with_header({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 16]}}, b"\0" * 8), "offsets")
     attempt(with_header({"a": {"dtype": "F32", "shape": [4], "data_offsets": [0, 8]}}, b"\0" * 8), "offsets")
-    attempt(with_header({"a": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 8]}}, b"\0" * 8), "offsets")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [-1], "data_offsets": [0, 8]}}, b"\0" * 8), "shape")
     attempt(with_header({"a": {"dtype": "Q7", "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 8), "unsupported dtype")
+    # a header whose structure is wrong is reported as such, whatever Python would have raised
+    attempt(with_header({"a": {"dtype": "F32", "shape": [2]}}, b"\0" * 8), "data_offsets")
+    attempt(with_header({"a": [1, 2]}, b"\0" * 8), "not an object")
+    attempt(struct.pack("<Q", 2) + b"[]", "not a JSON object")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [-2, -1], "data_offsets": [0, 8]}}, b"\0" * 8), "shape")
+    attempt(with_header({"a": {"dtype": "F32", "shape": "2", "data_offsets": [0, 8]}}, b"\0" * 8), "shape")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [2], "data_offsets": [8, 0]}}, b"\0" * 8), "data_offsets")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8.0]}}, b"\0" * 8), "data_offsets")
+    attempt(with_header({"a": {"dtype": 7, "shape": [2], "data_offsets": [0, 8]}}, b"\0" * 8), "unsupported dtype")
+    attempt(with_header({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 8]},
+                         "b": {"dtype": "F32", "shape": [1], "data_offsets": [4, 8]}}, b"\0" * 8), "overlap")
+
+
+def test_loader_reports_wrong_dtypes_with_the_rest():
+    """Storage is kept as it is (bfloat16, 32-bit); a tensor stored as anything else is not
+    converted behind the user's back but named, in the same error as the other faults."""
+    cfg = tiny_config("A")
+    m = _model(cfg)
+    tensors = random_tensors(m, 3)
+    tensors["blocks.0.mlp.fc.weight"] = tensors["blocks.0.mlp.fc.weight"].to(torch.float16)
+    tensors["ln_f.weight"] = tensors["ln_f.weight"].to(torch.float64)
+    tensors["tok_emb.weight"] = tensors["tok_emb.weight"].to(torch.int32)
+    del tensors["ln_f.bias"]
+    with pytest.raises(WeightsError) as err:
+        check_and_bind(tensors, m.tensor_specs())
+    e = err.value
+    assert e.missing == ["ln_f.bias"] and len(e.wrong_dtype) == 3
+    text = str(e)
+    for piece in ("wrong dtype (3)", "blocks.0.mlp.fc.weight: checkpoint float16", "ln_f.weight: checkpoint float64",
+                  "tok_emb.weight: checkpoint int32", "bfloat16 or float32", "missing (1)"):
+        assert piece in text, text

@@ -156,3 +156,43 @@ def test_overlapped_decoding_gives_the_same_answers_one_step_late(dtype):
             assert engine.num_overlapped_steps == 0
         answers.append({k: v for k, v in results.items() if k != "e"})
     assert answers[0] == answers[1]
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_a_kernel_that_gave_up_stops_generation(overlap):
+    """A kernel whose bounded wait ran out leaves a code in the status word and skips its work.
+    The engine reads that word with every step's ids: generation raises instead of returning
+    tokens sampled from invalid logits, the word is cleared, and the engine works afterwards."""
+    from mini_gpt_inference_b200.kernels.library import KernelLibraryError
+
+    cfg, tensors, engine = engine_for("A", "bfloat16", block_size=8, num_blocks=32, max_batch_size=2,
+                                      overlap_decode=overlap)
+    prompt = tokens_for(cfg, 5, 3)
+    params = SamplingParams(max_tokens=6, temperature=0.0)
+    good = engine.generate([prompt], params)[0]["token_ids"]
+    engine.runner.ops.status.fill_(3)                       # what such a kernel would have written
+    with pytest.raises(KernelLibraryError, match="gave up waiting"):
+        engine.generate([prompt], params)
+    assert int(engine.runner.ops.status.item()) == 0
+    # a fresh engine on the same kernel set is unaffected
+    _, _, again = engine_for("A", "bfloat16", block_size=8, num_blocks=32, max_batch_size=2,
+                             overlap_decode=overlap)
+    assert again.generate([prompt], params)[0]["token_ids"] == good
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_batch_of_seven_with_portions_of_13_and_forced_preemption(dtype):
+    """The second tiny configuration as the task's list words it (MLP 384, eps 1e-5, pages of 8):
+    prompts of 1 to 100 tokens, seven running at a time, prompt portions of at most 13 tokens, and a
+    pool too small for seven long requests, so that some give way and are recomputed."""
+    cfg, tensors, engine = engine_for("C", dtype, sharp=False, block_size=8, num_blocks=44, max_batch_size=7,
+                                      max_num_batched_tokens=32, max_prefill_chunk=13)
+    lengths = [100, 1, 57, 13, 88, 26, 14, 2, 71, 39]
+    prompts = [tokens_for(cfg, n, 90 + i) for i, n in enumerate(lengths)]
+    outs = engine.generate(prompts, SamplingParams(max_tokens=14, temperature=0.0))
+    assert engine.scheduler.num_preemptions > 0
+    for prompt, out in zip(prompts, outs):
+        assert len(out["token_ids"]) == 14
+        assert_greedy(cfg, tensors, prompt, out["token_ids"], TOLERANCE[dtype])
+    assert engine.stats()["allocated_blocks"] == 0
+    engine.runner.manager.check()

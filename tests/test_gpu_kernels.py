@@ -378,14 +378,17 @@ def _attention_case(ops, dtype, n_head, n_kv_head, head_dim, page_tokens, window
             positions.append(p)
     cache = SimpleNamespace(k_pages=k_pages.to(dtype).cuda(), v_pages=v_pages.to(dtype).cuda(),
                             group=0, page_tokens=page_tokens, window=window or None, writes=False)
-    from mini_gpt_inference_b200.parts.context import query_tiles
+    from mini_gpt_inference_b200.parts.context import HostBatch, StepPlan
 
-    work = query_tiles(q_lens, [n - ql for n, ql in zip(lengths, q_lens)])
+    # the host half of the tiled prompt attention, as the attention mixer asks for it
+    plan = StepPlan()
+    ops.plan_prompt_attention(HostBatch(q_lens, [n - ql for n, ql in zip(lengths, q_lens)], [0] * len(q_lens),
+                                        dtype), plan, n_head, n_kv_head, head_dim)
     ctx = SimpleNamespace(block_tables=[tables.cuda()],
                           token_request=torch.tensor(token_request, dtype=torch.int32).cuda(),
                           positions=torch.tensor(positions, dtype=torch.int32).cuda(),
                           decode_only=all(q == 1 for q in q_lens), max_ctx_after=max(lengths),
-                          attn_work=torch.tensor(work, dtype=torch.int32).cuda())
+                          extra={k: torch.from_numpy(v).cuda() for k, v in plan.arrays.items()})
     qkv = torch.stack(qkv_rows).to(dtype).cuda()
     before = ops.launches
     got = ops.paged_attention(qkv, n_head, n_kv_head, head_dim, scale, cache, ctx)
@@ -470,6 +473,30 @@ def test_paged_attention_split_over_keys(ops, n_head, n_kv_head, head_dim, page_
     finally:
         ops.use_split_attention = True
     assert (general - got).abs().max() <= _tol(torch.bfloat16, 1.0)
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,rows", [
+    (8, 8, 64, 64, 64),        # the 50M model's batch of 64: 64 x 8 x 9 blocks
+    (24, 2, 64, 16, 48),       # 12 query heads per kv head: two tiles of eight heads per CTA
+    (40, 2, 32, 8, 200),       # 20 heads per kv head: two CTAs per kv head, the second not full
+    (4, 4, 128, 32, 40)])
+def test_split_attention_of_many_rows_merges_in_a_second_kernel(ops, n_head, n_kv_head, head_dim,
+                                                                  page_tokens, rows):
+    """A grid of several waves leaves its partial rows in scratch and a second kernel merges them.
+    Every row's context is long enough for three or more key blocks that all hold keys, and the
+    lengths differ from row to row, so that a block merged twice, dropped, or taken from the
+    neighbour's scratch shows."""
+    block = ops.lib.mg_attention_split_keys(head_dim)
+    lengths = [2 * block + 37 + (11 * i) % (2 * block + 150) for i in range(rows)]
+    assert min(lengths) > 2 * block
+    got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, head_dim, page_tokens, 0,
+                                lengths, [1] * rows, seed=11)
+    assert _attention_case.kernels == 2, "the merge was expected to run as a kernel of its own"
+    ops.check_status()
+    assert not torch.isnan(got).any()
+    assert (got - want).abs().max() <= _tol(torch.bfloat16, 1.0)
+    # the counters stay zero for the next launch, whichever kernel merged
+    assert int(ops._counters(1).abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -20,7 +20,8 @@ from mini_gpt_inference_b200.engine.build import load_model, make_runner
 from mini_gpt_inference_b200.engine.runner import StepEntry
 from mini_gpt_inference_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, LayerCall, LayerSpec,
                                            Mixer, ModelSpec, PartSpec, PositionEncoding,
-                                           StepContext, TensorSpec, register_mixer,
+                                           StepContext, TensorSpec, pre_norm_layer,
+                                           register_arrangement, register_mixer,
                                            register_position_encoding)
 from mini_gpt_inference_b200.parts.base import (EMBEDDINGS, HEADS, POSITION_ENCODINGS, FeedForward,
                                                 register_feed_forward)
@@ -235,6 +236,17 @@ class SignFlipPositions(PositionEncoding):
         qkv[:, : (n_head + n_kv_head) * head_dim] *= sign
 
 
+@register_arrangement("toy_parallel")
+def toy_parallel(ctx, layer, cache, residual32):
+    """One norm feeds both branches: ``y = norm(x); x += mixer(y) + feed_forward(y)``."""
+    y = layer.norm.forward(ctx, residual32)
+    layer.mixer.forward(ctx, cache, y, residual32)
+    layer.feed_forward.forward(ctx, y, residual32)
+
+
+toy_parallel.requires = ("norm", "mixer", "feed_forward")
+
+
 @dataclass(frozen=True)
 class ToyConfig:
     vocab_size: int
@@ -246,28 +258,103 @@ class ToyConfig:
         return cls(raw["vocab_size"], raw["width"])
 
 
+TOY_WINDOW = 6
+
+
 @register_model("ToyStateLM", config_class=ToyConfig)
 def describe_toy(cfg: ToyConfig) -> ModelSpec:
-    norm = PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "n1")
-    norm2 = PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "n2")
+    def norm(name):
+        return PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, name)
+
     ff = PartSpec("dense_mlp", {"width": cfg.width, "inner": 2 * cfg.width, "bias": False}, "ff")
-    attn = PartSpec("causal_attention", {"width": cfg.width, "n_head": 2, "n_kv_head": 1,
-                                         "head_dim": 16, "bias": False, "window": 6}, "attn")
-    layers = (LayerSpec("l0.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"), ff, norm, norm2),
-              LayerSpec("l1.", attn, ff, norm, norm2),
-              LayerSpec("l2.", PartSpec("toy_running_mean", {"width": cfg.width}, "mix"),
-                        PartSpec("toy_top1_experts", {"width": cfg.width, "inner": 24, "experts": 3}, "moe"),
-                        norm, norm2))
+    mean = PartSpec("toy_running_mean", {"width": cfg.width}, "mix")
+    windowed = PartSpec("causal_attention", {"width": cfg.width, "n_head": 2, "n_kv_head": 1,
+                                             "head_dim": 16, "bias": False, "window": TOY_WINDOW}, "attn")
+    # all keys, in pages of 8 from a pool of its own size: a second cache group beside the windowed one
+    full = PartSpec("causal_attention", {"width": cfg.width, "n_head": 4, "n_kv_head": 2, "head_dim": 16,
+                                         "bias": False, "cache_page_tokens": 8, "cache_pages": 9}, "attn")
+    layers = (pre_norm_layer("l0.", norm("n1"), mean, norm("n2"), ff),
+              pre_norm_layer("l1.", norm("n1"), windowed, norm("n2"), ff),
+              pre_norm_layer("l2.", norm("n1"), mean, norm("n2"),
+                             PartSpec("toy_top1_experts", {"width": cfg.width, "inner": 24, "experts": 3}, "moe")),
+              LayerSpec("l3.", {"norm": norm("n"), "mixer": full, "feed_forward": ff}, "toy_parallel"))
     return ModelSpec(
         architecture="ToyStateLM", width=cfg.width, vocab_size=cfg.vocab_size,
         embedding=PartSpec("token_embedding", {"vocab_size": cfg.vocab_size, "width": cfg.width}, "emb"),
         position=PartSpec("toy_sign_flip", {}, ""),
         layers=layers,
         # layer 1 runs twice; its second run reads the cache its first run wrote
-        layer_order=(LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2), LayerCall(1, 1, writes_cache=False)),
-        final_norm=PartSpec("layernorm", {"width": cfg.width, "eps": 1e-5, "bias": False}, "nf"),
+        layer_order=(LayerCall(0, 0), LayerCall(1, 1), LayerCall(2, 2), LayerCall(3, 3),
+                     LayerCall(1, 1, writes_cache=False)),
+        final_norm=norm("nf"),
         head=PartSpec("tied_head", {"vocab_size": cfg.vocab_size, "width": cfg.width,
                                     "tied_to": "emb.weight"}, "head"))
+
+
+# ---- the toy model once more, whole sequences, no cache, plain torch in 64-bit -----------------
+def plain_toy_logits(tokens, w, margins=None):
+    """Logits of one whole sequence through the toy architecture, sharing nothing with the parts
+    above but the formulas in their docstrings.  ``margins``: a list that receives, per token, the
+    gap between the two largest router logits (a small gap means that rounding may pick another
+    expert)."""
+    w = {k: v.double() for k, v in w.items()}
+    T = len(tokens)
+    x = w["emb.weight"][torch.tensor(tokens)]
+    counts = torch.arange(1, T + 1, dtype=torch.float64)[:, None]
+    pos = torch.arange(T)
+    flip = (1 - 2 * (pos % 2)).double()[:, None]
+
+    def ln(v, name):
+        return plain_gpt.layer_norm(v, w[name + ".weight"], None, 1e-5)
+
+    def running_mean(y, prefix):
+        return w[prefix + "mix.gain"] * y.cumsum(0) / counts
+
+    def qkv_of(y, prefix, n_head, n_kv):
+        qkv = y @ w[prefix + "attn.qkv.weight"].T
+        q = (qkv[:, : n_head * 16] * flip).reshape(T, n_head, 16)
+        k = (qkv[:, n_head * 16: (n_head + n_kv) * 16] * flip).reshape(T, n_kv, 16)
+        v = qkv[:, (n_head + n_kv) * 16:].reshape(T, n_kv, 16)
+        return q, k, v
+
+    def attend(q, k, v, prefix, window):
+        n_head, n_kv = q.shape[1], k.shape[1]
+        allowed = pos[None, :] <= pos[:, None]
+        if window is not None:
+            allowed &= pos[None, :] > pos[:, None] - window
+        out = torch.zeros(T, n_head, 16, dtype=torch.float64)
+        for h in range(n_head):
+            s = (q[:, h] @ k[:, h // (n_head // n_kv)].T) / 4.0
+            out[:, h] = torch.softmax(s.masked_fill(~allowed, float("-inf")), -1) @ v[:, h // (n_head // n_kv)]
+        return out.reshape(T, -1) @ w[prefix + "attn.proj.weight"].T
+
+    def dense(y, prefix):
+        return plain_gpt.gelu_tanh(y @ w[prefix + "ff.fc.weight"].T) @ w[prefix + "ff.proj.weight"].T
+
+    def experts(y, prefix):
+        logits = y @ w[prefix + "moe.router.weight"].T
+        if margins is not None:
+            top = logits.sort(-1, descending=True).values
+            margins.extend((top[:, 0] - top[:, 1]).tolist())
+        out = torch.zeros_like(y)
+        for t, e in enumerate(logits.argmax(-1).tolist()):
+            out[t] = plain_gpt.gelu_tanh(y[t] @ w[prefix + f"moe.e{e}.fc.weight"].T) @ w[prefix + f"moe.e{e}.proj.weight"].T
+        return out
+
+    x = x + running_mean(ln(x, "l0.n1"), "l0.")
+    x = x + dense(ln(x, "l0.n2"), "l0.")
+    q, k1, v1 = qkv_of(ln(x, "l1.n1"), "l1.", 2, 1)            # keys and values of layer 1's first run
+    x = x + attend(q, k1, v1, "l1.", TOY_WINDOW)
+    x = x + dense(ln(x, "l1.n2"), "l1.")
+    x = x + running_mean(ln(x, "l2.n1"), "l2.")
+    x = x + experts(ln(x, "l2.n2"), "l2.")
+    y = ln(x, "l3.n")                                           # one norm, two branches
+    q, k, v = qkv_of(y, "l3.", 4, 2)
+    x = x + attend(q, k, v, "l3.", None) + dense(y, "l3.")
+    q, _, _ = qkv_of(ln(x, "l1.n1"), "l1.", 2, 1)               # second run: new queries, the old cache
+    x = x + attend(q, k1, v1, "l1.", TOY_WINDOW)
+    x = x + dense(ln(x, "l1.n2"), "l1.")
+    return ln(x, "nf") @ w["emb.weight"].T
 
 
 def test_toy_mixer_alone_matches_its_formula(ops):
@@ -307,6 +394,11 @@ def test_toy_routed_feed_forward_alone_matches_its_formula(ops, dtype):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_toy_architecture_is_registered_built_and_stepped(ops, dtype):
+    """Built from the registries alone, stepped whole and in portions with two requests side by
+    side, and compared with the plain computation above: a mixer with state of its own (twice), a
+    windowed attention layer that runs twice against one cache, a routed feed-forward, a layer
+    with one norm and two branches, and two paged cache groups with different page sizes and
+    pool sizes."""
     from mini_gpt_inference_b200.config import lookup
     from mini_gpt_inference_b200.parts import DecoderModel
 
@@ -315,15 +407,25 @@ def test_toy_architecture_is_registered_built_and_stepped(ops, dtype):
     model = DecoderModel(family.describe(cfg))
     specs = model.cache_specs()
     assert isinstance(specs[0], FixedStateSpec) and isinstance(specs[2], FixedStateSpec)
-    tensors = random_tensors(model, 3, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
+    # (a seed whose router logits have no near-ties on the two sequences below)
+    tensors = random_tensors(model, 22, torch.bfloat16 if dtype == "bfloat16" else torch.float32)
     loaded = load_model(config=cfg, tensors=tensors, dtype=dtype, device=DEV)
     runner = make_runner(loaded, ops, page_tokens=4, num_pages=12, max_requests=3)
-    assert len(runner.manager.groups) == 1 and sorted(runner.manager.state_layers) == [0, 2]
+    groups = runner.manager.groups
+    assert [(g.page_tokens, g.num_pages, g.layers) for g in groups] == [(4, 12, [1]), (8, 9, [3])]
+    assert sorted(runner.manager.state_layers) == [0, 2]
     g = torch.Generator().manual_seed(1)
     a = torch.randint(0, 97, (30,), generator=g).tolist()
     b = torch.randint(0, 97, (21,), generator=g).tolist()
+    margins = []
+    want_a, want_b = plain_toy_logits(a, tensors, margins), plain_toy_logits(b, tensors, margins)
+    # routing is an argmax: the comparison is meaningful where rounding cannot flip it
+    assert min(margins) > (1e-4 if dtype == "float32" else 2e-2), "choose weights with clearer routing"
+    tol = 2e-5 if dtype == "float32" else 3e-2
     whole_a = runner.step([StepEntry("a", a, list(range(30)))])
     whole_b = runner.step([StepEntry("b", b, list(range(21)))])
+    assert (whole_a.double().cpu() - want_a).abs().max() <= tol
+    assert (whole_b.double().cpu() - want_b).abs().max() <= tol
     runner.finish("a")
     runner.finish("b")
     # the same two requests in portions, side by side, in fresh slots and pages
@@ -335,11 +437,16 @@ def test_toy_architecture_is_registered_built_and_stepped(ops, dtype):
         got_b.append(out[na:])
         pa, pb = pa + na, pb + nb
         runner.manager.check()
-    tol = 2e-5 if dtype == "float32" else 3e-2
-    assert (torch.cat(got_a) - whole_a).abs().max() <= tol
-    assert (torch.cat(got_b) - whole_b).abs().max() <= tol
-    # the window (6) let pages go back early: 30 tokens never held more than 3 pages of 4
-    assert runner.manager.groups[0].pool.num_used <= 6
+    assert (torch.cat(got_a).double().cpu() - want_a).abs().max() <= tol
+    assert (torch.cat(got_b).double().cpu() - want_b).abs().max() <= tol
+    # the window (6) let pages go back early: 30 tokens never held more than 3 pages of 4 there;
+    # the other group keeps every key: 30 + 21 tokens in pages of 8
+    assert groups[0].pool.num_used <= 6 and groups[1].pool.num_used == 4 + 3
+    # a slot that held state is given to a newcomer, which must start from zero: release one
+    # request and recompute it beside the other
     runner.finish("a2")
+    again = runner.step([StepEntry("a3", a[:17], list(range(17)))])
+    assert (again.double().cpu() - want_a[:17]).abs().max() <= tol
+    runner.finish("a3")
     runner.finish("b2")
     assert runner.manager.stats()["allocated_blocks"] == 0

@@ -14,7 +14,8 @@ from mini_gpt_inference_b200.engine.runner import StepEntry
 
 pytestmark = pytest.mark.gpu
 
-CASES = list(itertools.product("AB", ["float32", "bfloat16"], [False, True]))
+CASES = (list(itertools.product("AB", ["float32", "bfloat16"], [False, True]))
+         + [("C", "float32", False), ("C", "bfloat16", False)])
 IDS = [f"{w}-{d}-{'sharp' if s else 'soft'}" for w, d, s in CASES]
 
 
@@ -198,3 +199,80 @@ def test_step_errors_are_clear():
     with pytest.raises(CacheFullError):
         runner.step([StepEntry("y", [1] * 20, [])])
     runner.manager.check()
+
+
+@pytest.mark.parametrize("which,dtype", list(itertools.product("ABC", ["float32", "bfloat16"])))
+def test_released_request_is_recomputed_to_the_same_logits(which, dtype):
+    """Preemption by recomputation, seen from the step function: a request that has run through its
+    prompt and a few single tokens gives everything back, other requests take its pages, and it
+    comes again from position 0 with prompt and generated tokens as one prompt in portions of 13
+    beside the others' decoding.  Its logits, first pass and second, are the plain ones at every
+    position (the reference checks tokens only, tests/test_paged.py:107-143)."""
+    cfg = tiny_config(which)
+    pt = PAGE_TOKENS[which]
+    n = cfg.n_positions
+    cfg, tensors, runner, tol = _setup(which, dtype, False, num_pages=2 * (-(-n // pt)) + 2)
+    victim, other, late = tokens_for(cfg, n - 5, 31), tokens_for(cfg, n // 2, 32), tokens_for(cfg, n // 3, 33)
+    want = {k: plain_logits(cfg, tensors, v) for k, v in (("v", victim), ("o", other), ("l", late))}
+    for pages in runner.storage.k + runner.storage.v:
+        pages.fill_(float("nan"))
+    # first pass: most of the prompt, then single tokens beside another request
+    first = n // 2
+    got = [runner.step([StepEntry("v", victim[:first], list(range(first))), StepEntry("o", other[:7], [])])[:first]]
+    pos_o = 7
+    for t in range(first, first + 6):
+        out = runner.step([StepEntry("v", victim[t: t + 1], [0]), StepEntry("o", other[pos_o: pos_o + 1], [0])])
+        got.append(out[:1])
+        assert_close(out[1:], want["o"][pos_o: pos_o + 1], tol, "the other request, first pass")
+        pos_o += 1
+    assert_close(torch.cat(got), want["v"][: first + 6], tol, "first pass of the request")
+    # it gives way; a newcomer takes pages (some of them the ones just freed)
+    held = [p for p in runner.manager.block_table("v", 0) if p >= 0]
+    runner.finish("v")
+    for pages in runner.storage.k + runner.storage.v:
+        pages[:, torch.tensor(held, device="cuda")] = float("nan")
+    out = runner.step([StepEntry("l", late, list(range(len(late)))), StepEntry("o", other[pos_o: pos_o + 1], [0])])
+    assert_close(out[: len(late)], want["l"], tol, "the newcomer")
+    pos_o += 1
+    assert set(held) & {p for p in runner.manager.block_table("l", 0) if p >= 0}, "pages were expected to be reused"
+    runner.finish("l")
+    # second pass: from position 0, portions of 13, the other request decoding beside it
+    pos, again = 0, []
+    while pos < len(victim):
+        m = min(13, len(victim) - pos)
+        entries = [StepEntry("v", victim[pos: pos + m], list(range(m)))]
+        if pos_o < len(other):
+            entries.append(StepEntry("o", other[pos_o: pos_o + 1], [0]))
+        out = runner.step(entries)
+        again.append(out[:m])
+        if len(entries) == 2:
+            assert_close(out[m:], want["o"][pos_o: pos_o + 1], tol, "the other request, second pass")
+            pos_o += 1
+        pos += m
+    again = torch.cat(again)
+    assert not torch.isnan(again).any()
+    assert_close(again, want["v"], tol, "the request recomputed")
+    if dtype == "float32":
+        assert torch.equal(again[: first + 6], torch.cat(got)), "recomputation differs from the first pass"
+    runner.manager.check()
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_engine_usable():
+    """A kernel waits, with the wait that all tensor-core and bulk-copy kernels share, on a barrier
+    that nobody completes; after a few hundred tries it gives up, leaves its code in the status
+    word and returns.  The host sees it, the word is cleared, and the next step is right."""
+    from mini_gpt_inference_b200.kernels.library import KernelLibraryError
+
+    cfg, tensors, runner, tol = _setup("A", "bfloat16", False)
+    ops = runner.ops
+    ops.check_status()                                   # clean before
+    ops.wait_probe(300)
+    with pytest.raises(KernelLibraryError, match="gave up waiting \\(code 90\\)"):
+        ops.check_status()
+    ops.check_status()                                   # cleared by the report
+    with pytest.raises(KernelLibraryError, match="limit"):
+        ops.wait_probe(0)
+    tokens = tokens_for(cfg, 40, 2)
+    got = runner.step([StepEntry("r", tokens, list(range(40)))])
+    assert_close(got, plain_logits(cfg, tensors, tokens), tol, "a step after the probe")
+    ops.check_status()

@@ -128,6 +128,57 @@ def test_replay_four_ways(tmp_path, which, dtype):
         assert (mixed[k].double() - want[k]).abs().max() <= tol, f"mixed {k}"
 
 
+@pytest.mark.parametrize("which,dtype", [("A", "float32"), ("B", "bfloat16"), ("C", "float32"), ("C", "bfloat16")])
+def test_replay_with_a_request_released_half_way_and_recomputed(tmp_path, which, dtype):
+    """Preemption by recomputation inside a mixed replay: request v runs through half of its tokens
+    beside two others, is ended (its pages go back and are taken by a newcomer), and comes again
+    under the same id from its first token, in portions of 13 beside the others' single tokens.
+    Logits at every position of both passes are compared (the reference's preemption test compares
+    generated tokens, tests/test_paged.py:107-143)."""
+    model_dir, cfg, tensors = make_model_dir(tmp_path, which, 23, dtype)
+    tol = TOLERANCE[dtype]
+    n = cfg.n_positions
+    reqs = {"v": tokens_for(cfg, n - 3, 81), "o1": tokens_for(cfg, n // 2 + 5, 82), "o2": tokens_for(cfg, 37, 83),
+            "late": tokens_for(cfg, n // 2, 84)}
+    want = {k: plain_logits(cfg, tensors, t) for k, t in reqs.items()}
+    pos = dict.fromkeys(reqs, 0)
+    steps = []
+
+    def step(parts, end=()):
+        entries = []
+        for rid, m in parts:
+            m = min(m, len(reqs[rid]) - pos[rid])
+            if m > 0:
+                entries.append({"id": rid, "tokens": reqs[rid][pos[rid]: pos[rid] + m], "want": list(range(m))})
+                pos[rid] += m
+        steps.append({"step": len(steps), "entries": entries, "end": list(end)})
+
+    half = (n - 3) // 2
+    step([("v", half - 4), ("o1", 9), ("o2", 2)])
+    for _ in range(4):
+        step([("v", 1), ("o1", 1), ("o2", 3)])
+    first_pass = len(steps)
+    step([("o1", 1), ("o2", 1)], end=["v"])                    # v gives everything back
+    pos["v"] = 0
+    step([("late", n // 2), ("o1", 1)])                        # a newcomer takes the freed pages
+    step([("o2", 50)], end=["late", "o2"])
+    while pos["v"] < len(reqs["v"]) or pos["o1"] < len(reqs["o1"]):
+        step([("v", 13), ("o1", 1)])
+    steps[-1]["end"] = ["v", "o1"]
+    live_most = sum(64 * ((len(reqs[k]) + 63) // 64) for k in ("v", "o1", "o2"))
+    run_trace(model_dir, dtype, tmp_path / "preempt", live_most, steps, page_tokens=8)
+    first = collect(tmp_path / "preempt", steps[:first_pass], cfg.vocab_size)
+    rest = collect(tmp_path / "preempt", steps[first_pass:], cfg.vocab_size)
+    assert (first["v"].double() - want["v"][:half]).abs().max() <= tol, "first pass of v"
+    assert (rest["v"].double() - want["v"]).abs().max() <= tol, "v recomputed"
+    if dtype == "float32":
+        assert torch.equal(rest["v"][:half], first["v"]), "recomputation differs from the first pass"
+    for k in ("o1", "o2"):
+        both = torch.cat([first[k], rest[k]])
+        assert (both.double() - want[k]).abs().max() <= tol, k
+    assert (rest["late"].double() - want["late"]).abs().max() <= tol, "late"
+
+
 def test_trace_run_reports_bad_input(tmp_path):
     model_dir, cfg, _ = make_model_dir(tmp_path, "A", 3, "float32")
     cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(model_dir), "--dtype", "float32",

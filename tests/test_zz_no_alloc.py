@@ -66,6 +66,13 @@ def test_no_alloc_argmax_matches_the_existing_entry_point_twice_in_a_row():
             want = _existing(lib, logits, limit)
             torch.cuda.synchronize()
             assert torch.equal(out, want), (rows, vocab, limit)
+            # and to a reference that is no kernel of this library: the largest value among the
+            # ids below the limit, the lowest index on ties
+            upto = limit if limit > 0 else vocab
+            host = logits[:, :upto].cpu()
+            top = host.max(dim=1, keepdim=True).values
+            lowest = (host == top).int().argmax(dim=1).to(torch.int32)
+            assert torch.equal(out.cpu(), lowest), (rows, vocab, limit)
         upto = limit if limit > 0 else vocab
         if upto == vocab:
             assert out[0] == vocab - 1                    # the planted winner of the second call
