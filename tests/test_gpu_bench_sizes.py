@@ -89,7 +89,7 @@ def test_prompt_in_portions_across_key_chunks(setup):
     tiles (128) and key chunks (512): logits of each portion's first and last token."""
     cfg, oracle, runner, dtype, tol = setup
     tokens = oracle.bases[1]
-    sizes = [511, 2, 127, 129, 255, 64, 448, 3, 380, 130]
+    sizes = [511, 2, 127, 129, 255, 64, 448, 3, 380, 129]
     assert sum(sizes) <= 2048
     pos, places, outs = 0, [], []
     for n in sizes:

@@ -477,9 +477,9 @@ def test_paged_attention_split_over_keys(ops, n_head, n_kv_head, head_dim, page_
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,rows", [
     (8, 8, 64, 64, 64),        # the 50M model's batch of 64: 64 x 8 x 9 blocks
-    (24, 2, 64, 16, 48),       # 12 query heads per kv head: two tiles of eight heads per CTA
+    (24, 2, 64, 16, 170),      # 12 query heads per kv head: two tiles of eight heads per CTA
     (40, 2, 32, 8, 200),       # 20 heads per kv head: two CTAs per kv head, the second not full
-    (4, 4, 128, 32, 40)])
+    (4, 4, 128, 32, 70)])
 def test_split_attention_of_many_rows_merges_in_a_second_kernel(ops, n_head, n_kv_head, head_dim,
                                                                   page_tokens, rows):
     """A grid of several waves leaves its partial rows in scratch and a second kernel merges them.
