@@ -168,3 +168,39 @@ static inline cudaError_t mg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     }
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
+
+// ---- phase stamps (tracing builds only) ----------------------------------------------------------
+// With -DMG_STAMPS a kernel file keeps a small device array of clock readings: thread 0 of each CTA
+// records, at MG_STAMP(name, 0), the global nanosecond timer (one clock for all SMs and kernels) in
+// slot 0 and its SM's cycle counter in slot 1, and at every other MG_STAMP(name, slot) the cycle
+// counter (cheap to read, so the stamps hardly disturb what they measure; slot 1 is reserved).  An
+// exported mg_<name>_stamps() copies the array to the host: where a kernel's time goes, and how long
+// the hand-over between two kernels takes.
+// In ordinary builds the macros expand to nothing.
+#ifdef MG_STAMPS
+#define MG_STAMP_SLOTS 12
+#define MG_STAMP_CTAS 1024
+#define MG_STAMP_DECLARE(name)                                                                      \
+    static __device__ long long name##_stamp_buf[MG_STAMP_CTAS * MG_STAMP_SLOTS];                   \
+    MG_API int mg_##name##_stamps(long long* host, int ctas) {                                      \
+        if (ctas > MG_STAMP_CTAS) ctas = MG_STAMP_CTAS;                                             \
+        return cudaMemcpyFromSymbol(host, name##_stamp_buf, sizeof(long long) * ctas * MG_STAMP_SLOTS) == cudaSuccess \
+                   ? MG_OK : MG_ERR_CUDA;                                                           \
+    }
+#define MG_STAMP(name, slot)                                                                        \
+    do {                                                                                            \
+        if (threadIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < MG_STAMP_CTAS) {  \
+            long long t_;                                                                           \
+            if ((slot) == 0) {                                                                      \
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                              \
+                name##_stamp_buf[blockIdx.x * MG_STAMP_SLOTS] = t_;                                 \
+                name##_stamp_buf[blockIdx.x * MG_STAMP_SLOTS + 1] = clock64();                      \
+            } else {                                                                                \
+                name##_stamp_buf[blockIdx.x * MG_STAMP_SLOTS + (slot)] = clock64();                 \
+            }                                                                                       \
+        }                                                                                           \
+    } while (0)
+#else
+#define MG_STAMP_DECLARE(name)
+#define MG_STAMP(name, slot) do {} while (0)
+#endif

@@ -227,3 +227,30 @@ MG_API int mg_copy_ints(int* dst, const int* src, int n, void* stream) {
     MG_CHECK_LAUNCH("copy_ints");
     return MG_OK;
 }
+
+
+namespace {
+__global__ void zero_fill_kernel(uint4* __restrict__ dst, long long n16, uint8_t* __restrict__ tail, int tail_bytes) {
+    pdl_trigger();
+    pdl_wait();                                                  // the buffer may still be in use by the kernel in front
+    const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = z;
+    if (blockIdx.x == 0 && (int)threadIdx.x < tail_bytes) tail[threadIdx.x] = 0;
+}
+}  // namespace
+
+// dst[0 .. bytes) = 0 (dst 16-byte aligned).
+MG_API int mg_zero_fill(void* dst, long long bytes, void* stream) {
+    if (bytes <= 0) return MG_OK;
+    MG_REQUIRE(dst != nullptr && ((uintptr_t)dst & 15) == 0, "zero fill: the buffer must be 16-byte aligned");
+    const long long n16 = bytes / 16;
+    const int tail = (int)(bytes - n16 * 16);
+    long long blocks = (n16 + 255) / 256;
+    if (blocks < 1) blocks = 1;
+    if (blocks > 1184) blocks = 1184;
+    const cudaError_t le = mg_launch(zero_fill_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, true,
+                                     (uint4*)dst, n16, (uint8_t*)dst + n16 * 16, tail);
+    if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "zero_fill: %s", cudaGetErrorString(le));
+    MG_CHECK_LAUNCH("zero_fill");
+    return MG_OK;
+}

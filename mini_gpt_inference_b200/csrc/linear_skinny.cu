@@ -26,6 +26,8 @@
 // activations must fit the shared memory; other sizes are refused (the tensor-core GEMM takes them).
 #include "linear_epilogue.cuh"
 
+MG_STAMP_DECLARE(skinny)
+
 namespace {
 
 constexpr int MAX_M = 16;
@@ -77,6 +79,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     int best_i = 0x7fffffff;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    MG_STAMP(skinny, 0);
 
     const int ks = a.k_splits;
     const int tiles_per_round = WARPS / ks;
@@ -126,8 +129,10 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         }
     }
     // Weights and bias do not depend on the kernel before this one; everything below does.
+    MG_STAMP(skinny, 2);
     pdl_trigger();
     pdl_wait();
+    MG_STAMP(skinny, 3);
     if (ln) __syncthreads();
 
     // ---- stage the activations (with the LayerNorm prologue if asked) as bfloat16 ----
@@ -181,6 +186,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
         }
     }
     __syncthreads();
+    MG_STAMP(skinny, 4);
 
     const uint8_t* xrow0 = xs + (size_t)g * xstride;
     const uint8_t* xrow1 = xs + (size_t)(g + 8) * xstride;
@@ -229,6 +235,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             if (MT == 16) *reinterpret_cast<float2*>(mine + (g + 8) * TILE_N + 2 * t) = make_float2(c[2], c[3]);
         }
         __syncthreads();
+        MG_STAMP(skinny, 5);
         // ---- epilogue: one thread per (tile of the round, token, row) ----
         for (int e = tid; e < tiles_per_round * MT * TILE_N; e += THREADS) {
             const int ti = e / (MT * TILE_N), rem = e - ti * (MT * TILE_N);
@@ -268,6 +275,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             }
         }
     }
+    MG_STAMP(skinny, 7);
     if constexpr (AMAX) {
         if (tid < a.M) {
             a.amax_v[(size_t)tid * gridDim.x + blockIdx.x] = best_v;

@@ -24,6 +24,11 @@ CSRC = Path(__file__).resolve().parent.parent / "csrc"
 LIB_NAME = "libminigpt_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
+# MINIGPT_B200_STAMPS=1 builds a tracing variant (in a folder of its own) whose kernels record
+# time stamps at their phases (MG_STAMP in common.cuh); the ordinary build has none of it.
+STAMPS = os.environ.get("MINIGPT_B200_STAMPS", "") not in ("", "0")
+if STAMPS:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DMG_STAMPS"] + os.environ.get("MINIGPT_B200_STAMPS_FLAGS", "").split()
 
 
 class BuildError(RuntimeError):
@@ -52,7 +57,7 @@ def _stamp() -> str:
 
 
 def _build_dir() -> Path:
-    d = CSRC / "_build"
+    d = CSRC / ("_build_stamps" if STAMPS else "_build")
     try:
         d.mkdir(parents=True, exist_ok=True)
         probe = d / f".write_probe_{os.getpid()}"

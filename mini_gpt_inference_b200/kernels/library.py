@@ -44,6 +44,8 @@ _SIGNATURES = {
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_wait_probe": [_I, _P, _P],
+    "mg_mlp_fused": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
+    "mg_zero_fill": [_P, ctypes.c_longlong, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
@@ -87,6 +89,8 @@ def load(verbose: bool = True):
     lib.mg_attention_split_keys.restype = c_int
     lib.mg_attention_split_launches.argtypes = [c_int, c_int, c_int, c_int]
     lib.mg_attention_split_launches.restype = c_int
+    lib.mg_mlp_pack_elements.argtypes = [c_int, c_int]
+    lib.mg_mlp_pack_elements.restype = ctypes.c_longlong
     lib.mg_attention_split_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
     lib.mg_attention_split_scratch_floats.restype = ctypes.c_longlong
     _lib = lib

@@ -85,6 +85,9 @@ class CudaOps:
         self._counter_buf = None
         self._retired_counters = []
         self._sm_count = None
+        self.use_fused_mlp = True
+        self._packed = {}          # data pointer of a matrix -> (the matrix, its copy packed for a kernel)
+        self._ring = None          # (tensor that holds the residual stream, zeroed buffer, spare buffer)
 
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
@@ -373,6 +376,75 @@ class CudaOps:
             raise KernelLibraryError("linear_residual: residual has the wrong shape")
         self._linear(x, weight, bias, EPILOGUES["residual"], None, residual32)
 
+    # ---- the whole feed-forward in one kernel (small batches) ---------------------------------------
+    FUSED_MLP_ROWS = 16
+
+    def _residual_ring(self, residual32):
+        """Two more buffers like ``residual32`` that take turns with it as the residual stream
+        (see ``mlp_residual``): ``(next, spare)``, ``next`` all zeros.  They are remembered by the
+        tensor that currently holds the stream, so a chain of calls in one step allocates and
+        zeroes once."""
+        entry = self._ring
+        if entry is not None and entry[0] is residual32:
+            return entry[1], entry[2]
+        nxt = torch.empty_like(residual32)
+        spare = torch.empty_like(residual32)
+        self._run(self.lib.mg_zero_fill(_ptr(nxt), nxt.numel() * 4, self._stream()), "zero fill")
+        return nxt, spare
+
+    def _packed_proj(self, weight):
+        """The second matrix of a feed-forward, [C, F], copied once into the order in which the
+        fused kernel's lanes read it (``mg_mlp_pack_elements`` in mlp_fused.cu): a layout change
+        made when a matrix is first seen, not a computation of the step."""
+        key = weight.data_ptr()
+        hit = self._packed.get(key)
+        if hit is not None and hit[0] is weight:
+            return hit[1]
+        c, f = weight.shape
+        groups = (f + 15) // 16
+        padded = weight
+        if groups * 16 != f:
+            padded = torch.zeros((c, groups * 16), dtype=weight.dtype, device=weight.device)
+            padded[:, :f] = weight
+        packed = padded.view(c // 8, 8, groups, 4, 4).permute(2, 0, 1, 3, 4).contiguous()
+        assert packed.numel() == self.lib.mg_mlp_pack_elements(c, f)
+        self._packed[key] = (weight, packed)
+        return packed
+
+    def mlp_residual(self, y, fc_weight, fc_bias, proj_weight, proj_bias, activation, residual32, act_dtype):
+        """``residual32 + proj(act(fc(y)))``.  Returns the tensor that holds the sum: ``residual32``
+        itself (added in place by two projection kernels), or, where the whole feed-forward runs as
+        one kernel (bfloat16, up to 16 tokens, ``y`` a deferred LayerNorm of ``residual32``),
+        another tensor: that kernel cannot write where its CTAs still read, so the residual
+        stream moves between three buffers that take turns."""
+        deferred = y if isinstance(y, DeferredNorm) else None
+        m = residual32.shape[0]
+        if (self.use_fused_mlp and deferred is not None and deferred.rows is None and deferred.x32 is residual32
+                and activation == "gelu_tanh" and fc_weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
+                and deferred.dtype == torch.bfloat16 and 0 < m <= self.FUSED_MLP_ROWS):
+            self._want(residual32, torch.float32, "residual", 2)
+            self._want(fc_weight, torch.bfloat16, "fc weight", 2)
+            self._want(proj_weight, torch.bfloat16, "proj weight", 2)
+            c, f = residual32.shape[1], fc_weight.shape[0]
+            if fc_weight.shape != (f, c) or proj_weight.shape != (c, f):
+                raise KernelLibraryError("feed-forward: the two matrices do not fit the width")
+            for b, n, name in ((fc_bias, f, "fc bias"), (proj_bias, c, "proj bias")):
+                if b is not None and self._want(b, torch.float32, name, 1).numel() != n:
+                    raise KernelLibraryError(f"feed-forward: {name} has the wrong length")
+            nxt, spare = self._residual_ring(residual32)
+            code = self.lib.mg_mlp_fused(_ptr(residual32), _ptr(nxt), _ptr(spare), _ptr(deferred.gain),
+                                         _ptr(deferred.shift), deferred.eps, _ptr(fc_weight), _ptr(fc_bias),
+                                         _ptr(self._packed_proj(proj_weight)), _ptr(proj_bias), m, c, f,
+                                         self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "feed-forward (fused)")
+                self._ring = (nxt, spare, residual32)          # nxt holds the stream; spare is zero
+                return nxt
+            self._ring = None
+        h = self.linear(y, fc_weight, fc_bias, activation, act_dtype)
+        self.linear_residual(h, proj_weight, proj_bias, residual32)
+        return residual32
+
     def logits(self, y, tok_emb, greedy_out=None, vocab_limit=None):
         """Logits in 32-bit.  With ``greedy_out`` (int32 ``[rows]``): the argmax of every row (ids at
         or above ``vocab_limit`` excluded) is left there as well; returns ``(logits, taken)`` then,
@@ -400,6 +472,7 @@ class CudaOps:
                                    cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
 
     SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
+
     PREFILL_TC_HEAD_DIMS = (64,)
 
     def _attention_tiles_name(self, n_head: int) -> str:

@@ -15,10 +15,11 @@ Interfaces (what a new part must provide):
                     ``max_positions`` (None if unbounded)
 * Mixer:            built with ``position=`` (the model's position encoding),
                     ``cache_spec()`` (what the layer keeps per request, or None),
-                    ``forward(ctx, cache, y, residual32)``  adds its output to residual32
-* FeedForward:      ``forward(ctx, y, residual32)``         adds its output to residual32
-* Block arrangement: a function ``run(ctx, layer, cache, residual32)`` that wires
-                    norm1/mixer/norm2/feed_forward.
+                    ``forward(ctx, cache, y, residual32)``  adds its output to residual32 in place
+                    and returns None, or returns another tensor that holds the sum
+* FeedForward:      ``forward(ctx, y, residual32)``         the same
+* Block arrangement: a function ``run(ctx, layer, cache, residual32)`` that wires the layer's
+                    named parts and returns the tensor that holds the stream (None: in place).
 """
 
 from __future__ import annotations

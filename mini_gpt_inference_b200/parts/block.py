@@ -3,6 +3,10 @@
 A block arrangement is a function ``run(ctx, layer, cache, residual32)`` registered under a name;
 it finds the layer's parts by the names it expects (``layer.norm1`` ...) and says which names
 those are in ``requires``, so that a layer that lacks one is refused when the model is built.
+Mixers and feed-forwards add their output to the 32-bit residual stream: in place (they return
+nothing), or into another tensor that they return (a kernel that fuses the whole part cannot
+always write where it reads); an arrangement hands the stream on with ``stream_after`` and
+returns the tensor that holds it at the end (or nothing, if that is the one it was given).
 ``pre_norm``: ``x += mixer(norm1(x)); x += ff(norm2(x))`` (src/minigpt_infer/model.py:112-115).
 """
 
@@ -52,9 +56,16 @@ def _normed(ctx, norm, consumer, residual32):
     return run(ctx, residual32)
 
 
-def pre_norm(ctx, layer: Layer, cache, residual32) -> None:
-    layer.mixer.forward(ctx, cache, _normed(ctx, layer.norm1, layer.mixer, residual32), residual32)
-    layer.feed_forward.forward(ctx, _normed(ctx, layer.norm2, layer.feed_forward, residual32), residual32)
+def stream_after(returned, residual32):
+    """The tensor that holds the residual stream after a part ran: what the part returned, or, if
+    it returned nothing, the tensor it was given (it added in place)."""
+    return residual32 if returned is None else returned
+
+
+def pre_norm(ctx, layer: Layer, cache, residual32):
+    x = residual32
+    x = stream_after(layer.mixer.forward(ctx, cache, _normed(ctx, layer.norm1, layer.mixer, x), x), x)
+    return stream_after(layer.feed_forward.forward(ctx, _normed(ctx, layer.norm2, layer.feed_forward, x), x), x)
 
 
 pre_norm.requires = ("norm1", "mixer", "norm2", "feed_forward")

@@ -40,6 +40,12 @@ class DenseMLP(FeedForward):
 
     accepts_deferred_norm = True
 
-    def forward(self, ctx, y, residual32) -> None:
+    def forward(self, ctx, y, residual32):
+        whole = getattr(ctx.ops, "mlp_residual", None)
+        if whole is not None:
+            # the kernel set may run both projections as one kernel; it returns where the sum lies
+            return whole(y, self.fc_weight, self.fc_bias, self.proj_weight, self.proj_bias, self.activation,
+                         residual32, ctx.act_dtype)
         h = ctx.ops.linear(y, self.fc_weight, self.fc_bias, self.activation, ctx.act_dtype)
         ctx.ops.linear_residual(h, self.proj_weight, self.proj_bias, residual32)
+        return None

@@ -12,7 +12,7 @@ from typing import Any, Mapping
 
 from .base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS,
                    POSITION_ENCODINGS)
-from .block import Layer
+from .block import Layer, stream_after
 from .spec import ModelSpec, TensorSpec
 
 
@@ -70,7 +70,7 @@ class DecoderModel:
         x = self.embedding.forward(ctx, self.position)
         for call in self.layer_order:
             layer = self.layers[call.layer]
-            layer.run(ctx, layer, ctx.cache_view(call.cache_layer, call.writes_cache), x)
+            x = stream_after(layer.run(ctx, layer, ctx.cache_view(call.cache_layer, call.writes_cache), x), x)
         if ctx.logit_rows.numel() == 0:
             return None
         if getattr(self.head, "accepts_deferred_norm", False):

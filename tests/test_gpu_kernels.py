@@ -134,6 +134,56 @@ def test_small_batch_projection_with_fused_norm(ops, m, n, k):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m,c,f,bias", [(1, 512, 2048, True), (8, 512, 2048, True), (16, 512, 2048, True),
+                                        (9, 512, 2048, False), (5, 96, 200, False), (3, 64, 256, True),
+                                        (11, 768, 3072, True), (8, 1600, 6400, True), (2, 192, 520, True),
+                                        (7, 40, 24, True), (16, 1024, 72, False)])
+def test_whole_feed_forward_in_one_kernel(ops, m, c, f, bias):
+    """LayerNorm, fc, tanh-GELU and proj of up to 16 tokens as one kernel that adds partial products
+    of slices of the inner dimension into a zeroed buffer: against the formula (with the same
+    roundings to bfloat16 as the two-kernel path) and against that path; three times in a row, so
+    that the three buffers have taken every role."""
+    x = randn(m, c, seed=41, scale=2.0) + 0.3
+    gain, shift = randn(c, seed=42) + 1.0, (randn(c, seed=43) if bias else None)
+    w1 = randn(f, c, dtype=torch.bfloat16, seed=44, scale=1 / math.sqrt(c))
+    w2 = randn(c, f, dtype=torch.bfloat16, seed=45, scale=1 / math.sqrt(f))
+    b1, b2 = (randn(f, seed=46), randn(c, seed=47)) if bias else (None, None)
+
+    def formula(xin):
+        y = F.layer_norm(xin.double(), (c,), gain.double(), None if shift is None else shift.double(), 1e-5)
+        h = y.to(torch.bfloat16).double() @ w1.double().T + (b1.double() if bias else 0)
+        h = plain_gpt.gelu_tanh(h).to(torch.bfloat16).double()
+        return xin.double() + h @ w2.double().T + (b2.double() if bias else 0)
+
+    before = ops.launches
+    first = ops.mlp_residual(ops.defer_layernorm(x, gain, shift, 1e-5, torch.bfloat16), w1, b1, w2, b2,
+                             "gelu_tanh", x, torch.bfloat16)
+    assert first is not x, "the fused kernel was expected to run and hand back another buffer"
+    assert ops.launches == before + 2                      # the zero fill of the first call, and the kernel
+    want = formula(x)
+    scale = max(1.0, float(want.abs().max()))
+    assert (first.double() - want).abs().max() <= 2e-2 * scale   # a hidden value at a bfloat16 rounding edge
+    second = ops.mlp_residual(ops.defer_layernorm(first, gain, shift, 1e-5, torch.bfloat16), w1, b1, w2, b2,
+                              "gelu_tanh", first, torch.bfloat16)
+    assert ops.launches == before + 3 and second is not first and second is not x
+    assert (second.double() - formula(first)).abs().max() <= 2e-2 * scale
+    third = ops.mlp_residual(ops.defer_layernorm(second, gain, shift, 1e-5, torch.bfloat16), w1, b1, w2, b2,
+                             "gelu_tanh", second, torch.bfloat16)
+    assert third is x and ops.launches == before + 4         # the first buffer's turn again
+    assert (third.double() - formula(second)).abs().max() <= 2e-2 * scale
+    # the two-kernel path from the same input
+    x2 = second.clone()
+    ops.use_fused_mlp = False
+    try:
+        apart = ops.mlp_residual(ops.defer_layernorm(x2, gain, shift, 1e-5, torch.bfloat16), w1, b1, w2, b2,
+                                 "gelu_tanh", x2, torch.bfloat16)
+    finally:
+        ops.use_fused_mlp = True
+    assert apart is x2
+    assert (apart - third).abs().max() <= 1e-2 * scale
+    ops.check_status()
+
+
 @pytest.mark.parametrize("m", [17, 24, 32, 33, 50, 64])
 @pytest.mark.parametrize("n,k", [(1536, 512), (512, 2048), (509, 96), (200, 200), (77, 40), (2048, 4096)])
 def test_mid_batch_projection_over_a_cluster(ops, m, n, k):

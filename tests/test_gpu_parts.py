@@ -25,6 +25,7 @@ from mini_gpt_inference_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, LayerCa
                                            register_position_encoding)
 from mini_gpt_inference_b200.parts.base import (EMBEDDINGS, HEADS, POSITION_ENCODINGS, FeedForward,
                                                 register_feed_forward)
+from mini_gpt_inference_b200.parts.block import stream_after
 from mini_gpt_inference_b200.weights import random_tensors
 
 pytestmark = pytest.mark.gpu
@@ -113,7 +114,7 @@ def test_dense_mlp_part(ops, dtype):
     y = (torch.randn(9, 40, generator=torch.Generator().manual_seed(4))).to(dtype)
     residual = torch.randn(9, 40, generator=torch.Generator().manual_seed(5))
     res_dev = residual.to(DEV)
-    part.forward(make_ctx(ops, dtype, [9]), y.to(DEV), res_dev)
+    res_dev = stream_after(part.forward(make_ctx(ops, dtype, [9]), y.to(DEV), res_dev), res_dev)
     want = residual.double() + plain_gpt.mlp(y.double(), {k: v.double() for k, v in w.items()}, "ff.")
     assert rel_err(res_dev, want) <= REL[dtype]
 
@@ -240,8 +241,8 @@ class SignFlipPositions(PositionEncoding):
 def toy_parallel(ctx, layer, cache, residual32):
     """One norm feeds both branches: ``y = norm(x); x += mixer(y) + feed_forward(y)``."""
     y = layer.norm.forward(ctx, residual32)
-    layer.mixer.forward(ctx, cache, y, residual32)
-    layer.feed_forward.forward(ctx, y, residual32)
+    x = stream_after(layer.mixer.forward(ctx, cache, y, residual32), residual32)
+    return stream_after(layer.feed_forward.forward(ctx, y, x), x)
 
 
 toy_parallel.requires = ("norm", "mixer", "feed_forward")

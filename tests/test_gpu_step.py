@@ -154,7 +154,14 @@ def test_prompt_steps_of_a_repeated_shape_are_replayed(which, dtype):
                 r.finish("b")
     assert runner.shape_graph_replays >= 3 and eager.shape_graph_replays == 0
     for mine, theirs in zip(outs[0::2], outs[1::2]):
-        assert torch.equal(mine, theirs), "a replayed step differs from the same launches run eagerly"
+        if dtype == "float32":
+            assert torch.equal(mine, theirs), "a replayed step differs from the same launches run eagerly"
+        else:
+            # the fused feed-forward of small steps adds its partial sums in whatever order they
+            # arrive, so 32-bit sums differ in their last bits from run to run, and now and then such
+            # a difference moves an activation to the neighbouring bfloat16 value (0.4% of it): the
+            # same launches agree far inside the tolerance against the plain logits, not bit for bit
+            assert (mine - theirs).abs().max() <= tol / 8, "a replayed step differs from the same launches run eagerly"
     runner.manager.check()
 
 
