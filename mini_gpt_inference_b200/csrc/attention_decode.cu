@@ -175,7 +175,12 @@ attention_merge_kernel(const int* __restrict__ positions, const float* __restric
 }
 
 // partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
-template <int D, int NT>   // NT: tiles of 8 query heads per CTA (1 or 2)
+// VSTREAM: the values are not kept beside the keys.  Their rows are only asked into the L2 cache
+// before the wait and copied into the keys' place once the scores are done, so a CTA holds half
+// the shared memory and twice as many CTAs are on the GPU at once: for grids that would otherwise
+// need a second round of CTAs (whose loads start only when the first round ends), at the price of
+// one trip to L2 on every CTA's way.
+template <int D, int NT, bool VSTREAM>   // NT: tiles of 8 query heads per CTA (1 or 2)
 __global__ void __launch_bounds__(THREADS)
 attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_pages,
                        const bf16* __restrict__ v_pages, const int* __restrict__ block_table,
@@ -194,7 +199,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     static_assert(KW % 16 == 0, "a warp takes whole k steps of keys");
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* k_tile = smem;                                            // [SPLIT][D] bf16, swizzled
-    uint8_t* v_tile = smem + SPLIT * ROWB;
+    uint8_t* v_tile = VSTREAM ? smem : smem + SPLIT * ROWB;            // VSTREAM: the values come where the keys were
     int* grow = reinterpret_cast<int*>(v_tile + SPLIT * ROWB);         // [SPLIT] cache row of each key
     bf16* q_tiles = reinterpret_cast<bf16*>(grow + SPLIT);             // [WARPS][rows][QSTRIDE]: a copy per warp
     __shared__ int is_last;
@@ -245,17 +250,22 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
 #pragma unroll 4
         for (int i = lane; i < KW * CPR; i += 32) {
             const int r = warp * KW + i / CPR, c = i % CPR;
+            if (VSTREAM && which == 1) {
+                // only towards L2 for now: one request per 128-byte line of the row
+                if (r < old_count && (c * 16) % 128 == 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(pages + (size_t)grow[r] * D + c * 8));
+                continue;
+            }
             uint8_t* dst = tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16);
             if (r < old_count) cp_async16(smem_u32(dst), pages + (size_t)grow[r] * D + c * 8);
             else if (r >= count) *reinterpret_cast<uint4*>(dst) = zero4;            // keeps 0 * garbage out of O
         }
-        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (!(VSTREAM && which == 1)) asm volatile("cp.async.commit_group;" ::: "memory");
     }
     pdl_wait();
     // ---- what the kernel in front wrote: the newest row (to the warp that owns it) and the
     // queries (a copy for every warp, so that no warp waits for another before the end) ----
     if (holds_newest && warp == (count - 1) / KW) {
-        for (int i = lane; i < 2 * CPR; i += 32) {
+        for (int i = lane; i < (VSTREAM ? 1 : 2) * CPR; i += 32) {     // (streamed values are copied later, the newest with them)
             const int which = i / CPR, c = i - which * CPR, r = count - 1;
             const uint4 v = *reinterpret_cast<const uint4*>((which == 0 ? k_pages : v_pages) + (size_t)grow[r] * D + c * 8);
             *reinterpret_cast<uint4*>((which == 0 ? k_tile : v_tile) + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16)) = v;
@@ -270,7 +280,8 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
                 *reinterpret_cast<const uint4*>(qkv + (size_t)token * qkv_width + (size_t)(h0 + row) * D + c * 8);
         }
     }
-    asm volatile("cp.async.wait_group 1;" ::: "memory");               // this lane's keys have landed
+    if (VSTREAM) asm volatile("cp.async.wait_group 0;" ::: "memory");
+    else asm volatile("cp.async.wait_group 1;" ::: "memory");          // this lane's keys have landed
     __syncwarp();                                                       // the warp's keys, its newest row, its queries
 
     // ---- scores, keys as rows: S[key, head] = k . q over this warp's KW keys ----
@@ -346,6 +357,17 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     }
 
     // ---- values, dims as rows: O[dim, head] = sum over keys of v[key, dim] * p[key, head] ----
+    if (VSTREAM) {
+        // the warp's keys are used up: its value rows (from L2 by now, the newest included) take their place
+        __syncwarp();
+        for (int i = lane; i < KW * CPR; i += 32) {
+            const int r = warp * KW + i / CPR, c = i % CPR;
+            uint8_t* dst = v_tile + r * ROWB + ((c ^ ((r / RPL) % SWZ)) * 16);
+            if (r < count) cp_async16(smem_u32(dst), v_pages + (size_t)grow[r] * D + c * 8);
+            else *reinterpret_cast<uint4*>(dst) = zero4;                // keeps 0 * garbage out of O
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
     float o[NT][D / 16][4];
@@ -444,6 +466,16 @@ inline bool merges_inside(int n_tokens, int n_head, int n_kv_head, int max_split
     return max_splits == 1 || (long long)n_tokens * n_kv_head * head_tiles * max_splits <= MERGE_INSIDE_CTAS;
 }
 
+int device_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    return sms;
+}
+
 template <int D>
 int launch(const void* qkv, const void* k_pages, const void* v_pages, const int* block_table,
            const int* token_request, const int* positions, void* out, float* part_out, float* part_ml,
@@ -452,30 +484,44 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
     const int group = n_head / n_kv_head;
     const int head_tiles = (group + HEAD_ROWS - 1) / HEAD_ROWS;
     const int nh_max = group < HEAD_ROWS ? group : HEAD_ROWS;
-    const size_t smem = (size_t)2 * split_keys(D) * D * sizeof(bf16) + (size_t)WARPS * nh_max * (D + 8) * sizeof(bf16) +
-                        (size_t)split_keys(D) * sizeof(int) + (size_t)WARPS * nh_max * (D + 2) * sizeof(float);
+    const size_t rest = (size_t)WARPS * nh_max * (D + 8) * sizeof(bf16) + (size_t)split_keys(D) * sizeof(int) +
+                        (size_t)WARPS * nh_max * (D + 2) * sizeof(float);
+    const size_t tile = (size_t)split_keys(D) * D * sizeof(bf16);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_split_kernel<D, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(attention_split_kernel<D, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaError_t e = cudaSuccess;
+        for (auto fn : {attention_split_kernel<D, 1, false>, attention_split_kernel<D, 2, false>,
+                        attention_split_kernel<D, 1, true>, attention_split_kernel<D, 2, true>})
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention (split): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     dim3 grid(n_tokens, n_kv_head * head_tiles, max_splits);
+    const long long ctas = (long long)n_tokens * n_kv_head * head_tiles * max_splits;
+    // Keys and values side by side if the whole grid is on the GPU at once that way (or if not even
+    // half the shared memory per CTA would achieve it); else the values are streamed after the keys.
+    auto resident = [&](bool streamed) -> long long {
+        int per_sm = 0;
+        const size_t bytes = (streamed ? tile : 2 * tile) + rest;
+        const cudaError_t e =
+            nh_max <= 8 ? (streamed ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_kernel<D, 1, true>, THREADS, bytes)
+                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_kernel<D, 1, false>, THREADS, bytes))
+                        : (streamed ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_kernel<D, 2, true>, THREADS, bytes)
+                                    : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_kernel<D, 2, false>, THREADS, bytes));
+        return e == cudaSuccess ? (long long)per_sm * device_sms() : 0;
+    };
+    const bool vstream = ctas > resident(false) && ctas <= resident(true);
+    const size_t smem = (vstream ? tile : 2 * tile) + rest;
     // A grid of several waves (six CTAs fit an SM) merges in a second kernel, so that its CTAs do
     // not hold their shared memory while a counter answers; a small grid merges inside, which
     // saves a launch.
     const int merge_inside = merges_inside(n_tokens, n_head, n_kv_head, max_splits) ? 1 : 0;
-    cudaError_t le =
-        nh_max <= 8 ? mg_launch(attention_split_kernel<D, 1>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
-                                (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-                                (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                                window, max_splits, scale * 1.4426950408889634f, head_tiles, merge_inside)
-                    : mg_launch(attention_split_kernel<D, 2>, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv,
-                                (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-                                (bf16*)out, part_out, part_ml, counters, n_head, n_kv_head, page_tokens, max_pages,
-                                window, max_splits, scale * 1.4426950408889634f, head_tiles, merge_inside);
+    auto kernel = nh_max <= 8 ? (vstream ? attention_split_kernel<D, 1, true> : attention_split_kernel<D, 1, false>)
+                              : (vstream ? attention_split_kernel<D, 2, true> : attention_split_kernel<D, 2, false>);
+    cudaError_t le = mg_launch(kernel, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv, (const bf16*)k_pages,
+                               (const bf16*)v_pages, block_table, token_request, positions, (bf16*)out, part_out, part_ml,
+                               counters, n_head, n_kv_head, page_tokens, max_pages, window, max_splits,
+                               scale * 1.4426950408889634f, head_tiles, merge_inside);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     if (!merge_inside) {

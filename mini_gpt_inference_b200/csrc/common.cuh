@@ -127,6 +127,15 @@ __device__ __forceinline__ float gelu_tanh(float u) {
     return 0.5f * u * (1.0f + tanhf(k * (u + 0.044715f * u * u * u)));
 }
 
+// tanh-GELU with the hardware's tanh (one instruction, relative error about 2^-11): for results that
+// are rounded to bfloat16 (2^-8) right away, where the exact tanhf costs twenty times the instructions.
+__device__ __forceinline__ float gelu_tanh_fast(float u) {
+    const float k = 0.7978845608028654f;  // sqrt(2/pi)
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(k * (u + 0.044715f * u * u * u)));
+    return 0.5f * u * (1.0f + th);
+}
+
 // 2^x as one instruction of the special-function unit (two units in the last place; results
 // below the smallest normal number become zero).  For softmax weights, whose argument is <= 0 and
 // whose result is rounded to bfloat16 or summed in 32-bit right away.

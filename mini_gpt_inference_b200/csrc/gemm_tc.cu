@@ -31,6 +31,8 @@
 
 #include "blackwell.cuh"
 
+MG_STAMP_DECLARE(gemm)
+
 #define EPI_STORE 0
 #define EPI_GELU 1
 #define EPI_RESIDUAL 2
@@ -101,6 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
     }
 
+    MG_STAMP(gemm, 0);
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(smem_u32(&bars->full[s]), 1);
@@ -117,24 +120,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const uint32_t tmem_base = bars->tmem_base;
     // Barriers, tensor memory and the bias are set up while the kernel in front drains; its
     // results (the activations, the residual stream) are touched only from here on.
+    MG_STAMP(gemm, 2);
     pdl_trigger();
+    // The weights do not come from the kernel in front: their tiles of the first round of stages are
+    // asked for before the wait (tokens x weights: the q operand; weights x tokens: the p operand).
+    const int early = num_kb < stages ? num_kb : stages;
+    if (tid == 0) {
+        for (int kb = 0; kb < early; ++kb) {
+            const uint32_t full = smem_u32(&bars->full[kb]);
+            mbar_expect_tx(full, STAGE_BYTES);
+            uint8_t* stage = smem + (size_t)kb * STAGE_BYTES;
+            if (SWAP) tma_load_2d(smem_u32(stage), &map_p, full, kb * BLOCK_K, p0);
+            else tma_load_2d(smem_u32(stage + P_TILE_BYTES), &map_q, full, kb * BLOCK_K, q0);
+        }
+    }
     pdl_wait();
+    MG_STAMP(gemm, 3);
 
     if (tid == 0) {
         // ---- producer: TMA loads into the ring of stages ----
         for (int kb = 0; kb < num_kb; ++kb) {
             const int s = kb % stages;
+            const uint32_t full = smem_u32(&bars->full[s]);
+            uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
+            if (kb < early) {                             // the weights' tile is on its way already
+                if (SWAP) tma_load_2d(smem_u32(stage + P_TILE_BYTES), &map_q, full, kb * BLOCK_K, q0);
+                else tma_load_2d(smem_u32(stage), &map_p, full, kb * BLOCK_K, p0);
+                continue;
+            }
             if (!mbar_wait(smem_u32(&bars->empty[s]), ((kb / stages) & 1) ^ 1)) {
                 atomicExch(status, 1);
                 bars->failed = 1;
                 break;
             }
-            const uint32_t full = smem_u32(&bars->full[s]);
             mbar_expect_tx(full, STAGE_BYTES);
-            uint8_t* stage = smem + (size_t)s * STAGE_BYTES;
             tma_load_2d(smem_u32(stage), &map_p, full, kb * BLOCK_K, p0);
             tma_load_2d(smem_u32(stage + P_TILE_BYTES), &map_q, full, kb * BLOCK_K, q0);
         }
+        MG_STAMP(gemm, 4);
     } else if (tid == 32) {
         // ---- issuer: tcgen05.mma over the stages, accumulator in TMEM ----
         constexpr uint32_t idesc = instr_desc_bf16(TILE_P, BN);
@@ -169,6 +192,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     good = good && (*(volatile uint32_t*)&bars->failed == 0);
     good = __all_sync(0xffffffffu, good);               // tcgen05.ld needs the whole warp
     tc_fence_after();
+    MG_STAMP(gemm, 5);
     if (good) {
         const int p = p0 + warp * 32 + lane;             // this thread's row of D
         // first element of the token's cache row for kv head 0: [page][kv head][offset in page][feature]
@@ -179,13 +203,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         }
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
         constexpr int CHUNK = BN < 32 ? BN : 32;
-#pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CHUNK) {
-            if (q0 + c0 >= rows_q) break;                 // uniform over the CTA
-            uint32_t r[32];
-            if (CHUNK == 32) tmem_load_32(lane_addr + (uint32_t)c0, r);
-            else tmem_load_16(lane_addr + (uint32_t)c0, r);
-            tmem_wait_ld();
+        // one chunk of the accumulator (this thread's row, CHUNK columns from c0) through the epilogue
+        auto finish_chunk = [&](const uint32_t (&r)[32], const int c0) {
             if (p < rows_p) {
                 if (!SWAP) {
                     // p is a token, q runs over features: contiguous in the output row
@@ -204,8 +223,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                             v[j + 3] = __uint_as_float(r[j + 3]) + b4.w;
                         }
                         if (epilogue == EPI_GELU) {
+                            // results that become bfloat16 take the hardware tanh; 32-bit results the exact one
+                            if (out_bf16) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                                for (int j = 0; j < 32; ++j) v[j] = gelu_tanh_fast(v[j]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) v[j] = gelu_tanh(v[j]);
+                            }
                         }
                         if (epilogue == EPI_RESIDUAL) {
                             // all loads first, then the adds and stores: a load after a store to the
@@ -306,13 +331,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                     }
                 }
             }
+        };
+        // Two register buffers take turns: while one chunk goes through the epilogue the next one is
+        // on its way from tensor memory.
+        uint32_t ra[32], rb[32];
+        auto fetch = [&](uint32_t (&r)[32], const int c0) {
+            if (CHUNK == 32) tmem_load_32(lane_addr + (uint32_t)c0, r);
+            else tmem_load_16(lane_addr + (uint32_t)c0, r);
+        };
+        fetch(ra, 0);
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 2 * CHUNK) {
+            if (q0 + c0 >= rows_q) break;                 // uniform over the CTA
+            tmem_wait_ld();
+            const bool second = c0 + CHUNK < BN && q0 + c0 + CHUNK < rows_q;
+            if (second) fetch(rb, c0 + CHUNK);
+            finish_chunk(ra, c0);
+            if (second) {
+                tmem_wait_ld();
+                if (c0 + 2 * CHUNK < BN && q0 + c0 + 2 * CHUNK < rows_q) fetch(ra, c0 + 2 * CHUNK);
+                finish_chunk(rb, c0 + CHUNK);
+            }
         }
     } else if (tid == 0) {
         // something timed out: give copies that may still be in flight a moment to land
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
     }
+    MG_STAMP(gemm, 6);
     tc_fence_before();
     __syncthreads();
+    MG_STAMP(gemm, 7);
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
