@@ -23,7 +23,7 @@
 //
 // The order in which the CTAs' partial sums meet is not fixed, so the 32-bit result can differ
 // in its last bits from run to run; the two-kernel path (and the true 32-bit path) stay
-// reproducible.  Sizes: up to 16 tokens, width a multiple of 8, inner width a multiple of 8.
+// reproducible.  Sizes: up to 16 tokens, width a multiple of 8 up to 512, inner width a multiple of 8.
 #include "linear_epilogue.cuh"
 
 MG_STAMP_DECLARE(mlp)
@@ -33,8 +33,13 @@ namespace {
 constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int FS = 16;               // inner units per CTA (two mma tiles of 8)
-constexpr int KPW = 2;               // k blocks (of 32) of fc.weight a lane holds at once
-constexpr int NTW = 8;               // tiles of 8 output columns of proj.weight a lane holds at once
+// A lane holds KPW k blocks (of 32) of fc.weight and NTW tiles of 8 output columns of proj.weight,
+// all requested before the dependency wait: widths up to 512.  Wider models are left to the two
+// streaming projections (measured at widths 768 and 1600: deeper register rings or a second round
+// of loads after the wait cost more than the kernel saves).
+constexpr int KPW = 2;
+constexpr int NTW = 8;
+constexpr int MAX_WIDTH = 32 * WARPS * KPW;
 constexpr int XPAD = 64;             // bytes between activation rows beyond C bf16 (no bank conflicts)
 constexpr int HSTRIDE = FS + 8;      // bf16 per row of the hidden tile (rows 16 bytes apart in the banks)
 
@@ -325,8 +330,9 @@ size_t mlp_smem(int mt, int C) {
 
 }  // namespace
 
-// Most tokens the fused feed-forward takes.
+// Most tokens and the largest width the fused feed-forward takes.
 MG_API int mg_mlp_fused_max_rows() { return 16; }
+MG_API int mg_mlp_fused_max_width() { return MAX_WIDTH; }
 
 // The kernel reads proj.weight [C, F] from a copy in the order its lanes use it: with G = ceil(F / 16)
 // CTAs and C / 8 column tiles, element (((cta * C/8 + tile) * 8 + g) * 4 + t) * 4 + u of the copy is
@@ -347,24 +353,24 @@ MG_API int mg_mlp_fused(const float* x, float* out, float* spare, const float* g
     MG_REQUIRE(x != out && x != spare && out != spare, "feed-forward: x, out and spare must be three buffers");
     const int mt = M <= 8 ? 8 : 16;
     const size_t smem = mlp_smem(mt, C);
-    if (M > 16 || C % 8 != 0 || F % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w1 & 15) || ((uintptr_t)w2_packed & 15) ||
+    if (M > 16 || C > MAX_WIDTH || C % 8 != 0 || F % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w1 & 15) || ((uintptr_t)w2_packed & 15) ||
         ((uintptr_t)x & 15) || ((uintptr_t)out & 15) || ((uintptr_t)spare & 15) || ((uintptr_t)gain & 15) ||
         (shift && ((uintptr_t)shift & 15)) || (b2 && ((uintptr_t)b2 & 15)))
-        return mg_set_error(MG_ERR_UNSUPPORTED, "feed-forward (fused): needs M <= 16, widths that are multiples of 8, aligned operands");
+        return mg_set_error(MG_ERR_UNSUPPORTED, "feed-forward (fused): needs M <= 16, width <= 512, widths that are multiples of 8, aligned operands");
     MlpArgs a;
     a.x = x; a.out = out; a.spare = spare; a.gain = gain; a.shift = shift; a.eps = eps;
     a.w1 = (const bf16*)w1; a.b1 = b1; a.w2p = (const bf16*)w2_packed; a.b2 = b2; a.M = M; a.C = C; a.F = F;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(mlp_fused_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(mlp_fused_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        cudaError_t e = cudaSuccess;
+        for (auto fn : {mlp_fused_kernel<8>, mlp_fused_kernel<16>})
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "feed-forward (fused): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
     const int grid = (F + FS - 1) / FS;
     cudaStream_t s = (cudaStream_t)stream;
-    const cudaError_t le = mt == 8 ? mg_launch(mlp_fused_kernel<8>, dim3(grid), dim3(THREADS), smem, s, true, a)
-                                   : mg_launch(mlp_fused_kernel<16>, dim3(grid), dim3(THREADS), smem, s, true, a);
+    const cudaError_t le = mg_launch(mt == 8 ? mlp_fused_kernel<8> : mlp_fused_kernel<16>, dim3(grid), dim3(THREADS), smem, s, true, a);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "mlp_fused: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("mlp_fused");
     return MG_OK;

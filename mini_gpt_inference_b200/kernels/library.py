@@ -44,6 +44,7 @@ _SIGNATURES = {
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
     "mg_wait_probe": [_I, _P, _P],
+    "mg_mlp_fused_max_width": [],
     "mg_mlp_fused": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
     "mg_zero_fill": [_P, ctypes.c_longlong, _P],
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],

@@ -421,7 +421,9 @@ class CudaOps:
         m = residual32.shape[0]
         if (self.use_fused_mlp and deferred is not None and deferred.rows is None and deferred.x32 is residual32
                 and activation == "gelu_tanh" and fc_weight.dtype == torch.bfloat16 and act_dtype == torch.bfloat16
-                and deferred.dtype == torch.bfloat16 and 0 < m <= self.FUSED_MLP_ROWS):
+                and deferred.dtype == torch.bfloat16 and 0 < m <= self.FUSED_MLP_ROWS
+                and residual32.shape[1] <= self.lib.mg_mlp_fused_max_width() and residual32.shape[1] % 8 == 0
+                and fc_weight.shape[0] % 8 == 0):
             self._want(residual32, torch.float32, "residual", 2)
             self._want(fc_weight, torch.bfloat16, "fc weight", 2)
             self._want(proj_weight, torch.bfloat16, "proj weight", 2)
