@@ -43,6 +43,23 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_
     return false;
 }
 
+// The same by polling (mbarrier.test_wait never suspends the thread): for waits that are usually
+// short and sit on a kernel's critical path; `limit` polls of some tens of cycles each.
+__device__ __forceinline__ bool mbar_poll(uint32_t bar, uint32_t parity, uint32_t limit = 8 * MBAR_SPIN_LIMIT) {
+    for (uint32_t i = 0; i < limit; ++i) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // The same for a whole warp: true only if every lane saw the phase complete, so that what follows
 // (warp-wide tcgen05 instructions, votes) is reached by all lanes or by none.
 __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, uint32_t limit = MBAR_SPIN_LIMIT) {
@@ -55,6 +72,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
         ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y)
+        : "memory");
+}
+
+// The same for a 3-D tile (x innermost; the rule on x holds as above).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+        ::"r"(dst), "l"((uint64_t)map), "r"(bar), "r"(x), "r"(y), "r"(z)
         : "memory");
 }
 

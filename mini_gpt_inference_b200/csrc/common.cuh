@@ -209,7 +209,19 @@ static inline cudaError_t mg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
             }                                                                                       \
         }                                                                                           \
     } while (0)
+// the same from whichever single thread calls it (slots other than 0 and 1)
+#define MG_STAMP_HERE(name, slot)                                                                   \
+    do {                                                                                            \
+        if (blockIdx.y == 0 && blockIdx.z == 0 && blockIdx.x < MG_STAMP_CTAS)                       \
+            name##_stamp_buf[blockIdx.x * MG_STAMP_SLOTS + (slot)] = clock64();                     \
+    } while (0)
+#define MG_STAMP_HERE_LANE0(name, slot)                                                             \
+    do {                                                                                            \
+        if ((threadIdx.x & 31) == 0) MG_STAMP_HERE(name, slot);                                     \
+    } while (0)
 #else
 #define MG_STAMP_DECLARE(name)
 #define MG_STAMP(name, slot) do {} while (0)
+#define MG_STAMP_HERE(name, slot) do {} while (0)
+#define MG_STAMP_HERE_LANE0(name, slot) do {} while (0)
 #endif

@@ -30,6 +30,7 @@
 #include <unordered_map>
 
 #include "blackwell.cuh"
+#include "tensor_map.cuh"
 
 MG_STAMP_DECLARE(gemm)
 
@@ -365,60 +366,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
 }
 
 // ---- host side -----------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr;
-    int rows, k, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && k == o.k && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& m) const {
-        size_t h = std::hash<const void*>()(m.ptr);
-        h = h * 1000003u ^ (size_t)m.rows;
-        h = h * 1000003u ^ (size_t)m.k;
-        return h * 1000003u ^ (size_t)m.box_rows;
-    }
-};
-
-// Tensor map of a row-major [rows, k] bfloat16 matrix, boxes of box_rows x 64, 128-byte swizzle.
-int tensor_map(const void* ptr, int rows, int k, int box_rows, CUtensorMap* out) {
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    MapKey key{ptr, rows, k, box_rows};
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return MG_OK; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return mg_set_error(MG_ERR_CUDA, "linear: cuTensorMapEncodeTiled is not available from this driver");
-    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BLOCK_K, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return mg_set_error(MG_ERR_CUDA, "linear: cuTensorMapEncodeTiled failed (%d)", (int)r);
-    if (cache.size() > 8192) cache.clear();
-    cache.emplace(key, *out);
-    return MG_OK;
-}
-
 template <int BN, bool SWAP>
 int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const float* bias, void* out,
            float* residual, int ld_out, int epilogue, int out_bf16, const KvSink& sink, int* status,

@@ -73,6 +73,7 @@ class CudaOps:
         self.use_skinny = True
         self.use_cluster = True
         self.use_stream = True
+        self.use_wide = True
         # The streaming kernel also takes any matrix of at least `stream_min_bytes` (None: only tall
         # ones, the head), with rows cut into up to `stream_max_chunks` K chunks.  At width 1600
         # (5 chunks, row copies of 640 bytes) it is a little faster than the small-batch kernel; at
@@ -266,9 +267,34 @@ class CudaOps:
             raise KernelLibraryError(
                 f"linear: shapes do not fit: x {tuple(x.shape)}, w {tuple(weight.shape)}")
         out_bf16 = self._is_bf16(out) if out is not None else 0
-        if (self.use_stream and weight.dtype == torch.bfloat16 and 0 < m <= STREAM_ROWS and k % 8 == 0
-                and (n >= STREAM_MIN_ROWS
-                     or (self.stream_min_bytes is not None and 2 * n * k >= self.stream_min_bytes))):
+        large = n >= STREAM_MIN_ROWS or (self.stream_min_bytes is not None and 2 * n * k >= self.stream_min_bytes)
+        if self.use_wide and weight.dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0 and large:
+            # a matrix of many megabytes: tiles of 64 rows by TMA through a deep ring, started before
+            # the dependency wait
+            if deferred is not None:
+                args = [None, _ptr(deferred.x32), _ptr(deferred.rows), _ptr(deferred.gain),
+                        _ptr(deferred.shift), deferred.eps]
+            else:
+                self._want(x, weight.dtype, "linear input", 2)
+                args = [_ptr(x), None, None, None, None, 0.0]
+            amax, parts = [None, None, 0], 0
+            if greedy is not None:
+                ids_out, limit = greedy
+                parts = self.lib.mg_linear_wide_parts(m, n, k, 1 if deferred is not None else 0)
+                part_v = torch.empty((m * parts,), dtype=torch.float32, device=self.device)
+                part_i = torch.empty((m * parts,), dtype=torch.int32, device=self.device)
+                amax = [_ptr(part_v), _ptr(part_i), int(limit or 0)]
+            code = self.lib.mg_linear_wide(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
+                                           m, n, k, epilogue, out_bf16, *self._sink_args(kv_sink), *amax,
+                                           _ptr(self.status), self._stream())
+            if code != library.UNSUPPORTED:
+                self._run(code, "linear (large matrix)")
+                if greedy is not None:
+                    self._run(self.lib.mg_argmax_merge(_ptr(part_v), _ptr(part_i), _ptr(ids_out), m, parts,
+                                                       self._stream()), "argmax (merge)")
+                    self.greedy_taken = True
+                return kv_sink is not None
+        if (self.use_stream and weight.dtype == torch.bfloat16 and 0 < m <= STREAM_ROWS and k % 8 == 0 and large):
             # a tall matrix (the head) or one of many megabytes: one CTA per SM streams it through
             # shared memory
             if deferred is not None and m > SKINNY_ROWS:

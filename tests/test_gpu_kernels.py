@@ -265,12 +265,14 @@ def test_streaming_projection_of_a_wide_matrix_takes_up_to_64_rows(ops, m):
     want = x.double() @ w.double().T + b.double()
     was = ops_module.STREAM_ROWS
     ops_module.STREAM_ROWS = 64
+    ops.use_wide = False                                     # (the kernel of tiled copies takes 16 rows; this one is meant)
     try:
         ids = torch.full((m,), -1, dtype=torch.int32, device="cuda")
         got = ops.linear(x, w, b, "none", torch.float32)
         logits, taken = ops.logits(x, w, ids, 9000)
     finally:
         ops_module.STREAM_ROWS = was
+        ops.use_wide = True
     assert taken
     assert (got.double() - want).abs().max() <= 2e-4
     masked = logits.clone()
@@ -279,12 +281,15 @@ def test_streaming_projection_of_a_wide_matrix_takes_up_to_64_rows(ops, m):
     ops.check_status()
 
 
+@pytest.mark.parametrize("wide", [True, False], ids=["tiles", "rows"])
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
-@pytest.mark.parametrize("n,k", [(640, 1600), (203, 6400), (9001, 1608), (77, 3080)])
-def test_streamed_projection_of_long_rows(ops, m, n, k):
-    """Rows too long for whole-row stages go through the streaming kernel in K chunks (a tile's
-    sums stay in registers from chunk to chunk), with the LayerNorm prologue on rows of any length:
-    one launch, and the same numbers as the separate kernels."""
+@pytest.mark.parametrize("n,k", [(640, 1600), (203, 6400), (9001, 1608), (77, 3080), (4800, 1600), (1600, 6400)])
+def test_streamed_projection_of_long_rows(ops, m, n, k, wide):
+    """Large matrices are streamed: as boxes of whole rows by TMA through a ring (rows of a multiple
+    of 64 and up to 2048 values; longer ones only for the residual epilogue, K cut over CTAs whose
+    partial sums are added in L2), or, where that kernel refuses, row by row in K chunks (a tile's
+    sums stay in registers from chunk to chunk); with the LayerNorm prologue: one launch, and the
+    same numbers as the separate kernels."""
     x32 = randn(m + 3, k, seed=81, scale=2.0) + 0.5
     rows = torch.tensor([(3 * i + 1) % (m + 3) for i in range(m)], dtype=torch.int32).cuda()
     gain, shift = randn(k, seed=82) + 1.0, randn(k, seed=83)
@@ -292,10 +297,13 @@ def test_streamed_projection_of_long_rows(ops, m, n, k):
     b = randn(n, seed=85)
     want = torch.nn.functional.layer_norm(x32[rows.long()].double(), (k,), gain.double(), shift.double(), 1e-5)
     want = want.to(torch.bfloat16).double() @ w.double().T + b.double()
-    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster)
+    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster, ops.use_wide)
     ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = 0, 1 << 20, False, False
+    ops.use_wide = wide
     # 16 rows of 6400 values leave no room for stages beside them: refused, other kernels take it
     fits = (8 if m <= 8 else 16) * (2 * k + 64) + 8 * k + 8 * 4 * 8 * (2 * 64 + 64) <= 226 * 1024
+    if wide:
+        fits = fits or k <= 2048                              # the tiled kernel stages rows of up to 2048 values
     try:
         before = ops.launches
         fused = ops.linear(ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16, rows), w, b, "none",
@@ -307,10 +315,10 @@ def test_streamed_projection_of_long_rows(ops, m, n, k):
         res = randn(m, n, seed=86)
         keep = res.clone()
         ops.linear_residual(y, w, b, res)
-        ops.use_stream = False
+        ops.use_stream = ops.use_wide = False
         apart = ops.linear(y, w, b, "none", torch.float32)
     finally:
-        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = flags
+        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster, ops.use_wide = flags
         ops.use_stream = True
     assert (fused.double() - want).abs().max() <= 2e-2       # bf16 rounding of the normalised rows
     assert (fused - streamed).abs().max() <= 2e-5             # the fused norm rounds as the stand-alone kernel
@@ -320,8 +328,37 @@ def test_streamed_projection_of_long_rows(ops, m, n, k):
     ops.check_status()
 
 
+@pytest.mark.parametrize("m,vocab,k,limit", [(1, 50304, 512, None), (8, 50257, 1600, 50000), (16, 9001, 192, 9000),
+                                             (3, 777, 64, None), (13, 50257, 768, None)])
+def test_large_matrix_kernel_takes_the_greedy_choice_on_its_way(ops, m, vocab, k, limit):
+    """The head through the kernel of tiled copies: 32-bit logits, and the first stage of the greedy
+    argmax in its epilogue (lowest index among equal maxima, ids at or above the limit excluded)."""
+    x = randn(m, k, dtype=torch.bfloat16, seed=75)
+    w = randn(vocab, k, dtype=torch.bfloat16, seed=76, scale=1 / math.sqrt(k))
+    w[vocab // 2] = w[7]                                     # a tie between two rows
+    flags = (ops.stream_min_bytes, ops.use_stream, ops.use_skinny)
+    ops.stream_min_bytes, ops.use_stream, ops.use_skinny = 0, False, False
+    try:
+        ids = torch.full((m,), -1, dtype=torch.int32, device="cuda")
+        before = ops.launches
+        logits, taken = ops.logits(x, w, ids, limit)
+        assert taken and ops.launches == before + 2          # the projection and the merge of its candidates
+    finally:
+        ops.stream_min_bytes, ops.use_stream, ops.use_skinny = flags
+    want = x.double() @ w.double().T
+    assert (logits.double() - want).abs().max() <= 2e-5
+    masked = logits.clone()
+    if limit is not None:
+        masked[:, limit:] = -float("inf")
+    best = masked.max(-1).values
+    first = (masked == best[:, None]).float().argmax(-1)     # lowest index among equal maxima
+    assert torch.equal(ids.long(), first)
+    ops.check_status()
+
+
+@pytest.mark.parametrize("wide", [True, False], ids=["tiles", "rows"])
 @pytest.mark.parametrize("m", [1, 8, 16])
-def test_streamed_qkv_projection_writes_keys_and_values(ops, m):
+def test_streamed_qkv_projection_writes_keys_and_values(ops, m, wide):
     """A QKV matrix of many megabytes is streamed as well; the epilogue of the streaming kernel
     copies key and value features to their cache rows like the other projection kernels."""
     n_head, n_kv, d, pt, k = 5, 5, 64, 16, 1600
@@ -337,14 +374,14 @@ def test_streamed_qkv_projection_writes_keys_and_values(ops, m):
     cache = SimpleNamespace(k_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
                             v_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
                             page_tokens=pt, writes=True)
-    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster)
-    ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = 0, 1 << 20, False, False
+    flags = (ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster, ops.use_wide)
+    ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster, ops.use_wide = 0, 1 << 20, False, False, wide
     try:
         before = ops.launches
         qkv = ops.linear_qkv(x, w, b, n_head, n_kv, d, cache, slots, torch.bfloat16)
         assert ops.launches == before + 1, "projection and page write were expected in one streaming kernel"
     finally:
-        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster = flags
+        ops.stream_min_bytes, ops.stream_max_chunks, ops.use_skinny, ops.use_cluster, ops.use_wide = flags
     kk = qkv[:, n_head * d: (n_head + n_kv) * d].reshape(m, n_kv, d)
     vv = qkv[:, (n_head + n_kv) * d:].reshape(m, n_kv, d)
     want_k, want_v = torch.zeros_like(cache.k_pages), torch.zeros_like(cache.v_pages)
