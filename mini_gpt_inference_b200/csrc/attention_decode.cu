@@ -35,6 +35,27 @@
 
 #include "common.cuh"
 
+MG_STAMP_DECLARE(attn)
+#ifdef MG_STAMPS
+// (the grid is three-dimensional here: stamps go by the CTA's linear index, thread 0 of each CTA)
+#define MG_STAMP_ATTN(slot)                                                                                  \
+    do {                                                                                                     \
+        const unsigned cta_ = (blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;                \
+        if (threadIdx.x == 0 && cta_ < MG_STAMP_CTAS) {                                                      \
+            if ((slot) == 0) {                                                                               \
+                long long t_;                                                                                \
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                       \
+                attn_stamp_buf[cta_ * MG_STAMP_SLOTS] = t_;                                                  \
+                attn_stamp_buf[cta_ * MG_STAMP_SLOTS + 1] = clock64();                                       \
+            } else {                                                                                         \
+                attn_stamp_buf[cta_ * MG_STAMP_SLOTS + (slot)] = clock64();                                  \
+            }                                                                                                \
+        }                                                                                                    \
+    } while (0)
+#else
+#define MG_STAMP_ATTN(slot) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int THREADS = 128;
@@ -213,6 +234,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     float* wpart = reinterpret_cast<float*>(q_tiles + WARPS * nh_rows * QSTRIDE);   // [WARPS][nh][OSTRIDE]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
+    MG_STAMP_ATTN(0);
     pdl_trigger();
     const int request = token_request[token];                          // asked for together with the position:
     const int p = positions[token];                                    // one trip to memory, not two
@@ -241,6 +263,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         }
     }
     __syncwarp();
+    MG_STAMP_ATTN(2);
     // ---- every warp asks for its own rows: all keys first, then all values ----
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
@@ -261,7 +284,9 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         }
         if (!(VSTREAM && which == 1)) asm volatile("cp.async.commit_group;" ::: "memory");
     }
+    MG_STAMP_ATTN(3);
     pdl_wait();
+    MG_STAMP_ATTN(4);
     // ---- what the kernel in front wrote: the newest row (to the warp that owns it) and the
     // queries (a copy for every warp, so that no warp waits for another before the end) ----
     if (holds_newest && warp == (count - 1) / KW) {
@@ -283,6 +308,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     if (VSTREAM) asm volatile("cp.async.wait_group 0;" ::: "memory");
     else asm volatile("cp.async.wait_group 1;" ::: "memory");          // this lane's keys have landed
     __syncwarp();                                                       // the warp's keys, its newest row, its queries
+    MG_STAMP_ATTN(5);
 
     // ---- scores, keys as rows: S[key, head] = k . q over this warp's KW keys ----
     // B operand: the queries, head nt * 8 + g in column g (heads past the group are zero columns)
@@ -356,6 +382,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
             for (int o = 4; o < 32; o <<= 1) sum[nt][i] += __shfl_xor_sync(0xffffffffu, sum[nt][i], o);
     }
 
+    MG_STAMP_ATTN(6);
     // ---- values, dims as rows: O[dim, head] = sum over keys of v[key, dim] * p[key, head] ----
     if (VSTREAM) {
         // the warp's keys are used up: its value rows (from L2 by now, the newest included) take their place
@@ -391,6 +418,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
                 for (int nt = 0; nt < NT; ++nt) mma_bf16(o[nt][dm], a, pb[nt][kk][0], pb[nt][kk][1]);
             }
     }
+    MG_STAMP_ATTN(7);
     // ---- the four warps' results meet in shared memory ----
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
@@ -436,6 +464,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
             }
         }
     }
+    MG_STAMP_ATTN(8);
     if (splits == 1 || !merge_inside) return;
     // ---- the CTA that finishes last merges the blocks of this (token, kv head) ----
     // The barrier orders every thread's partial writes before thread 0's release on the counter;
@@ -455,6 +484,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     float* weights = reinterpret_cast<float*>(k_tile) + warp * WCAP;
     for (int row = warp; row < nh; row += WARPS)
         merge_row<D>(part_out, part_ml, (pair0 + row) * max_splits, splits, weights, WCAP, out + (pair0 + row) * D, lane);
+    MG_STAMP_ATTN(9);
 }
 
 // Whether the CTA that finishes last merges the key blocks of its row (one launch), or a second

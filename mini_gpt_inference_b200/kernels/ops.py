@@ -74,11 +74,14 @@ class CudaOps:
         self.use_cluster = True
         self.use_stream = True
         self.use_wide = True
-        # The streaming kernel also takes any matrix of at least `stream_min_bytes` (None: only tall
-        # ones, the head), with rows cut into up to `stream_max_chunks` K chunks.  At width 1600
-        # (5 chunks, row copies of 640 bytes) it is a little faster than the small-batch kernel; at
-        # 6400 (67 chunks, copies of 192 bytes) it was measured far slower, hence the limit.
-        self.stream_min_bytes = 8 << 20
+        # The large-matrix kernels also take any matrix of at least `stream_min_bytes` (None: only tall
+        # ones, the head).  Measured with 8 tokens: a 5.1 MB matrix (1600 x 1600) is faster through
+        # the kernel of tiled copies than through the small-batch kernel, matrices of 4.7 MB (3072 x
+        # 768 and its transpose) are slower by a tenth; the boundary sits between them.  Where that
+        # kernel refuses, the row-streaming kernel takes over, with rows cut into up to
+        # `stream_max_chunks` K chunks (at 6400 columns, 67 chunks of 192 bytes, it was measured far
+        # slower than the small-batch kernel, hence the limit).
+        self.stream_min_bytes = 5_000_000
         self.stream_max_chunks = 8
         self.greedy_taken = False
         self.use_dependent_launch = True
