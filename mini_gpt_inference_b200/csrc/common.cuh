@@ -121,6 +121,27 @@ __device__ __forceinline__ void layernorm_row_chunked(const float* src, int widt
     }
 }
 
+// LayerNorm gain and shift (shift may be null: zeros) from global to shared memory by all `threads`
+// threads of a CTA: a thread asks for all its values (of up to two rounds) before it stores the
+// first, so that they cost one trip to memory, not one per value.  n4: floats / 4; 16-byte aligned.
+__device__ __forceinline__ void stage_gain_shift(float* gain_s, float* shift_s, const float* gain, const float* shift,
+                                                 int n4, int tid, int threads) {
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i0 = tid; i0 < n4; i0 += 2 * threads) {
+        const int i1 = i0 + threads;
+        const float4 g0 = reinterpret_cast<const float4*>(gain)[i0];
+        const float4 s0 = shift ? reinterpret_cast<const float4*>(shift)[i0] : zero;
+        const float4 g1 = i1 < n4 ? reinterpret_cast<const float4*>(gain)[i1] : zero;
+        const float4 s1 = (i1 < n4 && shift) ? reinterpret_cast<const float4*>(shift)[i1] : zero;
+        reinterpret_cast<float4*>(gain_s)[i0] = g0;
+        reinterpret_cast<float4*>(shift_s)[i0] = s0;
+        if (i1 < n4) {
+            reinterpret_cast<float4*>(gain_s)[i1] = g1;
+            reinterpret_cast<float4*>(shift_s)[i1] = s1;
+        }
+    }
+}
+
 // tanh-GELU evaluated in 32-bit: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))).
 __device__ __forceinline__ float gelu_tanh(float u) {
     const float k = 0.7978845608028654f;  // sqrt(2/pi)

@@ -122,11 +122,7 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
     const bool ln = a.x32 != nullptr;
     const bool ln_fast = ln && K % 128 == 0 && K <= 1024;                 // the row fits a warp's registers
     if (ln) {
-        for (int i = tid; i < K / 4; i += THREADS) {
-            reinterpret_cast<float4*>(gain_s)[i] = reinterpret_cast<const float4*>(a.gain)[i];
-            reinterpret_cast<float4*>(shift_s)[i] =
-                a.shift ? reinterpret_cast<const float4*>(a.shift)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        stage_gain_shift(gain_s, shift_s, a.gain, a.shift, K / 4, tid, THREADS);
     }
     // Weights and bias do not depend on the kernel before this one; everything below does.
     MG_STAMP(skinny, 2);
@@ -178,11 +174,23 @@ __global__ void __launch_bounds__(THREADS) linear_skinny_kernel(const SkinnyArgs
             layernorm_row_chunked<bf16>(src, K, gain_s, a.shift ? shift_s : nullptr, a.eps, reinterpret_cast<bf16*>(dst), lane);
         }
     } else {
-        const int chunks8 = K / 8;
-        for (int i = tid; i < a.M * chunks8; i += THREADS) {
-            const int m = i / chunks8, c = i - m * chunks8;
-            *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + c * 16) =
-                *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + c * 8);
+        // (a thread asks for four pieces before it stores the first: one trip to L2 for 4 x THREADS pieces)
+        const int chunks8 = K / 8, total = a.M * chunks8;
+        for (int i0 = tid; i0 < total; i0 += 4 * THREADS) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * THREADS;
+                if (i < total) v[u] = *reinterpret_cast<const uint4*>(a.x + (size_t)i * 8);   // (row m, piece c) is piece m * chunks8 + c
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * THREADS;
+                if (i < total) {
+                    const int m = i / chunks8, c = i - m * chunks8;
+                    *reinterpret_cast<uint4*>(xs + (size_t)m * xstride + c * 16) = v[u];
+                }
+            }
         }
     }
     __syncthreads();

@@ -117,11 +117,7 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
     const bool ln = a.x32 != nullptr;
     const bool ln_fast = ln && K % 128 == 0 && K <= 1024;                 // the row fits a warp's registers
     if (ln) {
-        for (int i = tid; i < K / 4; i += THREADS) {
-            reinterpret_cast<float4*>(gain_s)[i] = reinterpret_cast<const float4*>(a.gain)[i];
-            reinterpret_cast<float4*>(shift_s)[i] =
-                a.shift ? reinterpret_cast<const float4*>(a.shift)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+        stage_gain_shift(gain_s, shift_s, a.gain, a.shift, K / 4, tid, THREADS);
     }
     pdl_trigger();
     pdl_wait();
