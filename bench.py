@@ -47,12 +47,14 @@ sys.path.insert(0, str(ROOT))
 SIZES = {
     "50m": dict(vocab_size=50304, n_positions=2048, n_layer=8, n_head=8, n_embd=512, n_inner=2048,
                 bias=True, layer_norm_epsilon=1e-5),
+    "50m-long": dict(vocab_size=50304, n_positions=16384, n_layer=8, n_head=8, n_embd=512, n_inner=2048,
+                     bias=True, layer_norm_epsilon=1e-5),
     "gpt2-small": dict(vocab_size=50257, n_positions=1024, n_layer=12, n_head=12, n_embd=768,
                        n_inner=3072, bias=True, layer_norm_epsilon=1e-5),
     "gpt2-xl": dict(vocab_size=50257, n_positions=1024, n_layer=48, n_head=25, n_embd=1600,
                     n_inner=6400, bias=True, layer_norm_epsilon=1e-5),
 }
-MODEL_NAMES = {"50m": "gpt2-style-50M", "gpt2-small": "gpt2-small-sizes", "gpt2-xl": "gpt2-xl-sizes"}
+MODEL_NAMES = {"50m": "gpt2-style-50M", "50m-long": "gpt2-style-50M with a position table of 16384", "gpt2-small": "gpt2-small-sizes", "gpt2-xl": "gpt2-xl-sizes"}
 MODEL = SIZES["50m"]
 BASELINE_T4_DECODE_B8 = 1671.8      # tok/s, Tesla T4 fp16, context 8..40 (docs/BENCHMARKS.md:622)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -67,8 +69,9 @@ def parse_args():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--sizes", choices=sorted(SIZES), default="50m",
-                    help="layer sizes: the 50M model (default) or the same architecture at the "
-                         "layer sizes of GPT-2 small / GPT-2 XL")
+                    help="layer sizes: the 50M model (default), the same with a position table of 16384 "
+                         "(for contexts beyond 2048: give --context), or the same architecture at "
+                         "the layer sizes of GPT-2 small / GPT-2 XL")
     ap.add_argument("--context", type=int, default=None, help="default: the position table's length")
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the configuration has (both numbers are reported)")
@@ -432,6 +435,7 @@ def check_decode_logits(args) -> dict:
 
 
 def run_ours(args) -> dict:
+    global MODEL
     import torch
 
     pk, peak_source = peaks()
@@ -517,6 +521,20 @@ def run_ours(args) -> dict:
             _, pre32, _, _ = prefill_once(args32, reps=3)
             points["prefill_fp32_tok_s"] = round(PREFILL_TOKENS / (pre32 * 1e-3), 1)
             build_engine.cache.pop((args.sizes, args.layers, "float32"), None)     # give the memory back
+        if args.sizes == "50m" and args.dtype == "bfloat16":
+            # the same layers with a position table of 16384: the cache's share of a step grows eightfold
+            keep, MODEL = MODEL, SIZES["50m-long"]
+            try:
+                args_long = argparse.Namespace(**{**vars(args), "sizes": "50m-long", "context": 16384})
+                cfg_long, t, _, ctx_long, _ = device_decode(args_long, args.batch, min(args.steps, 32), 4,
+                                                            min_seconds=0.0, max_windows=2)
+                ms_long = statistics.median(t)
+                points[f"decode_b{args.batch}_ctx16384"] = round(args.batch / (ms_long * 1e-3), 1)
+                points[f"decode_b{args.batch}_ctx16384_roofline_frac"] = round(
+                    roofline_of(cfg_long, args.batch, ctx_long, ms_long)[1] / pk["hbm_gbs"], 4)
+                build_engine.cache.pop(("50m-long", args.layers, "bfloat16"), None)    # give the memory back
+            finally:
+                MODEL = keep
         serve = serve_mixed(args)
         points["serve_64_requests_tok_s"] = serve["value"]
         line["points"] = points

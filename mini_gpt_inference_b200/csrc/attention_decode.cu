@@ -105,18 +105,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// One warp merges the key blocks of one (token, head): the weights of the blocks go to `weights`
-// (shared memory, room for `cap` of them; blocks beyond are weighed again when used), then each
-// lane adds up its dims over the blocks in order, eight loads in flight.
+// The four warps of a CTA merge the key blocks of one (token, head).  Up to 16 blocks: warp 0 alone,
+// everything it needs asked for at once (one trip to memory).  More: every warp finds the row's
+// maximum, takes a quarter of the blocks (contiguous, in order; eight blocks' values and weights in
+// flight per lane), and the quarters' sums meet in `scratch` (shared memory, WARPS * (D + 1) floats)
+// and are added in warp order.  How the blocks are shared depends on their number only, so a token's
+// result does not depend on the batch.  Every thread of the CTA must call it (it has two barriers).
 template <int D>
 __device__ __forceinline__ void merge_row(const float* __restrict__ part_out, const float* __restrict__ part_ml,
-                                          size_t base, int splits, float* weights, int cap, bf16* __restrict__ out_row,
-                                          int lane) {
+                                          size_t base, int splits, float* scratch, bf16* __restrict__ out_row,
+                                          int warp, int lane) {
+    constexpr int DPL = (D + 31) / 32;                                  // dims per lane: lane, lane + 32, ..
     if constexpr (D >= 32 && D <= 128) {
         if (splits <= 16) {
+            if (warp != 0) return;                                      // (uniform: no barrier on this path)
             // Few blocks: maxima, sums and every partial value this lane needs are asked for at
             // once (one trip to memory instead of two); lane s holds the weight of block s.
-            constexpr int DPL = D / 32;
             const float2 ml = lane < splits ? __ldcg(reinterpret_cast<const float2*>(part_ml) + base + lane)
                                             : make_float2(-INFINITY, 0.f);
             float x[16][DPL];
@@ -145,32 +149,50 @@ __device__ __forceinline__ void merge_row(const float* __restrict__ part_out, co
     float M = -INFINITY;
     for (int sidx = lane; sidx < splits; sidx += 32) M = fmaxf(M, __ldcg(&part_ml[(base + sidx) * 2]));
     M = warp_max(M);
-    float denom = 0.f;
-    for (int sidx = lane; sidx < splits; sidx += 32) {
-        const float w = exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
-        if (sidx < cap) weights[sidx] = w;
-        denom += w * __ldcg(&part_ml[(base + sidx) * 2 + 1]);
-    }
-    denom = warp_sum(denom);
-    __syncwarp();
-    const float inv = 1.0f / denom;
-    for (int d = lane; d < D; d += 32) {
-        float v = 0.f;
-        for (int s0 = 0; s0 < splits; s0 += 8) {
-            float x[8];
+    const int per = (splits + WARPS - 1) / WARPS;
+    const int b0 = warp * per, b1 = min(splits, b0 + per);
+    float v[DPL], den = 0.f;
 #pragma unroll
-            for (int u = 0; u < 8; ++u) x[u] = (s0 + u < splits) ? __ldcg(&part_out[(base + s0 + u) * D + d]) : 0.f;
+    for (int j = 0; j < DPL; ++j) v[j] = 0.f;
+    for (int s0 = b0; s0 < b1; s0 += 8) {
+        float x[8][DPL];
+        float2 ml[8];
 #pragma unroll
-            for (int u = 0; u < 8; ++u)
-                if (s0 + u < splits) {
-                    const int sidx = s0 + u;
-                    const float w = sidx < cap ? weights[sidx] : exp2f(__ldcg(&part_ml[(base + sidx) * 2]) - M);
-                    v = fmaf(w, x[u], v);
-                }
+        for (int u = 0; u < 8; ++u) {
+            const bool in = s0 + u < b1;
+            ml[u] = in ? __ldcg(reinterpret_cast<const float2*>(part_ml) + base + s0 + u) : make_float2(-INFINITY, 0.f);
+#pragma unroll
+            for (int j = 0; j < DPL; ++j)
+                x[u][j] = (in && lane + 32 * j < D) ? __ldcg(&part_out[(base + s0 + u) * D + lane + 32 * j]) : 0.f;
         }
-        out_row[d] = __float2bfloat16_rn(v * inv);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {                                     // blocks in order
+            const float w = s0 + u < b1 ? exp2f(ml[u].x - M) : 0.f;
+            den = fmaf(w, ml[u].y, den);
+#pragma unroll
+            for (int j = 0; j < DPL; ++j) v[j] = fmaf(w, x[u][j], v[j]);
+        }
     }
-    __syncwarp();
+    __syncthreads();                                                    // `scratch` may still be in use (the row before)
+#pragma unroll
+    for (int j = 0; j < DPL; ++j)
+        if (lane + 32 * j < D) scratch[warp * (D + 1) + lane + 32 * j] = v[j];
+    if (lane == 0) scratch[warp * (D + 1) + D] = den;
+    __syncthreads();
+    if (warp == 0) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) total += scratch[w * (D + 1) + D];        // warps in order
+        const float inv = 1.0f / total;
+#pragma unroll
+        for (int j = 0; j < DPL; ++j)
+            if (lane + 32 * j < D) {
+                float y = 0.f;
+#pragma unroll
+                for (int w = 0; w < WARPS; ++w) y += scratch[w * (D + 1) + lane + 32 * j];
+                out_row[lane + 32 * j] = __float2bfloat16_rn(y * inv);
+            }
+    }
 }
 
 // The merge as a kernel of its own, for grids of many waves: the attention CTAs then leave as soon
@@ -181,18 +203,17 @@ attention_merge_kernel(const int* __restrict__ positions, const float* __restric
                        const float* __restrict__ part_ml, bf16* __restrict__ out, int n_head, int window,
                        int max_splits) {
     constexpr int SPLIT = split_keys(D);
-    __shared__ float weights[WARPS][256];
-    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int head = blockIdx.y * WARPS + warp;
+    __shared__ float scratch[WARPS * (D + 1)];
+    const int token = blockIdx.x, head = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int p = positions[token];
     pdl_trigger();
     pdl_wait();                                                        // the partial rows come from the kernel in front
-    if (p < 0 || head >= n_head) return;
+    if (p < 0) return;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int splits = (p - lo) / SPLIT + 1;
     if (splits == 1) return;                                            // the attention kernel wrote the row itself
     const size_t pair = (size_t)token * n_head + head;
-    merge_row<D>(part_out, part_ml, pair * max_splits, splits, weights[warp], 256, out + pair * D, lane);
+    merge_row<D>(part_out, part_ml, pair * max_splits, splits, scratch, out + pair * D, warp, lane);
 }
 
 // partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
@@ -479,11 +500,10 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     }
     __syncthreads();
     if (!is_last) return;
-    // A warp per head; the weights of the blocks go to shared memory (the key tile is free now).
-    constexpr int WCAP = KW * ROWB / 4;
-    float* weights = reinterpret_cast<float*>(k_tile) + warp * WCAP;
-    for (int row = warp; row < nh; row += WARPS)
-        merge_row<D>(part_out, part_ml, (pair0 + row) * max_splits, splits, weights, WCAP, out + (pair0 + row) * D, lane);
+    // The heads one after the other, all four warps on each (the key tile is free now: scratch).
+    for (int row = 0; row < nh; ++row)
+        merge_row<D>(part_out, part_ml, (pair0 + row) * max_splits, splits, reinterpret_cast<float*>(k_tile),
+                     out + (pair0 + row) * D, warp, lane);
     MG_STAMP_ATTN(9);
 }
 
@@ -555,7 +575,7 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     if (!merge_inside) {
-        le = mg_launch(attention_merge_kernel<D>, dim3(n_tokens, (n_head + WARPS - 1) / WARPS), dim3(THREADS), 0, s, true,
+        le = mg_launch(attention_merge_kernel<D>, dim3(n_tokens, n_head), dim3(THREADS), 0, s, true,
                        positions, (const float*)part_out, (const float*)part_ml, (bf16*)out, n_head, window, max_splits);
         if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_merge: %s", cudaGetErrorString(le));
         MG_CHECK_LAUNCH("attention_merge");

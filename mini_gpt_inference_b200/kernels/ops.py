@@ -91,6 +91,7 @@ class CudaOps:
         self._sm_count = None
         self.use_fused_mlp = True
         self._packed = {}          # data pointer of a matrix -> (the matrix, its copy packed for a kernel)
+        self._tile_lists = {}      # (rows, contexts, slots) of a step -> the prompt attention's work list
         self._ring = None          # (tensor that holds the residual stream, zeroed buffer, spare buffer)
 
     # ---- helpers --------------------------------------------------------------------------
@@ -524,8 +525,16 @@ class CudaOps:
             import numpy as np
 
             slots = int(name.rsplit("/", 1)[1])
-            work = query_tiles(batch.q_len, batch.ctx_before, slots)
-            plan.arrays[name] = np.asarray(work, dtype=np.int32).reshape(-1, 5)
+            # (steps of a shape that came before take their list from a small table)
+            key = (tuple(batch.q_len), tuple(batch.ctx_before), slots)
+            work = self._tile_lists.get(key)
+            if work is None:
+                work = np.asarray(query_tiles(batch.q_len, batch.ctx_before, slots), dtype=np.int32).reshape(-1, 5)
+                work.setflags(write=False)
+                if len(self._tile_lists) >= 64:
+                    self._tile_lists.pop(next(iter(self._tile_lists)))
+                self._tile_lists[key] = work
+            plan.arrays[name] = work
             plan.signature.append(("attention_merge", batch.max_ctx_after > KEY_CHUNK))
 
     def paged_attention(self, qkv, n_head, n_kv_head, head_dim, scale, cache, ctx):
