@@ -219,9 +219,9 @@ attention_merge_kernel(const int* __restrict__ positions, const float* __restric
 // partial layout: out [token][head][split][D], ml [token][head][split][2]; counters [token][kv head tile]
 // VSTREAM: the values are not kept beside the keys.  Their rows are only asked into the L2 cache
 // before the wait and copied into the keys' place once the scores are done, so a CTA holds half
-// the shared memory and twice as many CTAs are on the GPU at once: for grids that would otherwise
-// need a second round of CTAs (whose loads start only when the first round ends), at the price of
-// one trip to L2 on every CTA's way.
+// the shared memory and twice as many CTAs are on the GPU at once: for grids that need fewer rounds
+// of CTAs that way (a round's loads start only when the round before ends), at the price of one
+// trip to L2 on every CTA's way.
 template <int D, int NT, bool VSTREAM>   // NT: tiles of 8 query heads per CTA (1 or 2)
 __global__ void __launch_bounds__(THREADS)
 attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_pages,
@@ -560,7 +560,9 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
                                     : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attention_split_kernel<D, 2, false>, THREADS, bytes));
         return e == cudaSuccess ? (long long)per_sm * device_sms() : 0;
     };
-    const bool vstream = ctas > resident(false) && ctas <= resident(true);
+    // the values are streamed after the keys wherever that saves a round of CTAs
+    const long long beside = resident(false), after = resident(true);
+    const bool vstream = beside > 0 && after > 0 && (ctas + after - 1) / after < (ctas + beside - 1) / beside;
     const size_t smem = (vstream ? tile : 2 * tile) + rest;
     // A grid of several waves (six CTAs fit an SM) merges in a second kernel, so that its CTAs do
     // not hold their shared memory while a counter answers; a small grid merges inside, which

@@ -1,4 +1,4 @@
-// Projection of a few dozen tokens (decoding at batch 17 to 64): out[m, n] = x[m, :] . w[n, :].
+// Projection of a few dozen tokens (decoding at batch 17 to 128): out[m, n] = x[m, :] . w[n, :].
 //
 // At this size a projection is still a stream over the weights, but the activations are no
 // longer small: 64 tokens of width 2048 are 256 KB, too much for every CTA to stage whole, and a
@@ -22,11 +22,10 @@ namespace cg = cooperative_groups;
 
 namespace {
 
-constexpr int MAX_M = 64;
+constexpr int MAX_M = 128;
 constexpr int TILE_N = 8;            // weight rows per warp
 constexpr int WARPS = 8;             // tiles per cluster
 constexpr int THREADS = WARPS * 32;
-constexpr int PRE = 8;               // k blocks (of 32) whose weights a lane holds at once
 
 struct ClusterArgs {
     const bf16* x;                   // [M, K]
@@ -38,9 +37,12 @@ struct ClusterArgs {
     int xstride;                     // bytes between staged activation rows
 };
 
-template <int MG>   // groups of 16 tokens held: 2 or 4
-__global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterArgs a) {
+template <int MG>   // groups of 16 tokens held: 2, 4, 6 or 8
+__global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const ClusterArgs a) {
     constexpr int MT = MG * 16;
+    // k blocks (of 32) whose weights a lane holds at once: fewer where the sums take more registers,
+    // so that two CTAs still share an SM
+    constexpr int PRE = MG <= 4 ? 8 : 4;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int ranks = a.ranks;
@@ -167,7 +169,7 @@ __global__ void __launch_bounds__(THREADS) linear_cluster_kernel(const ClusterAr
 MG_API int mg_linear_cluster_max_rows() { return MAX_M; }
 
 // x: [M, K] bf16; w: [N, K] bf16; epilogues and the key/value sink as mg_linear_skinny.
-// Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 64, K % 8 != 0, operands that are not
+// Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 128, K % 8 != 0, operands that are not
 // 16-byte aligned or a slice of activations beyond the shared memory.
 MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, void* out, float* residual, int M, int N,
                              int K, int epilogue, int out_bf16, void* k_pages, void* v_pages, const int* slots,
@@ -184,10 +186,10 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
     const int per_rank = (kblocks + ranks - 1) / ranks;
     const int slice_bytes = per_rank * 64;
     const int xstride = slice_bytes + (slice_bytes % 128 == 0 ? 64 : 0);               // rows 64 bytes apart mod 128
-    const int mg = M <= 32 ? 2 : 4;
+    const int mg = M <= 32 ? 2 : M <= 64 ? 4 : M <= 96 ? 6 : 8;
     const size_t smem = (size_t)mg * 16 * xstride + (size_t)WARPS * mg * 16 * TILE_N * sizeof(float);
     if (M > MAX_M || K % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15))
-        return mg_set_error(MG_ERR_UNSUPPORTED, "linear (cluster): needs M <= 64, K %% 8 == 0, aligned operands");
+        return mg_set_error(MG_ERR_UNSUPPORTED, "linear (cluster): needs M <= 128, K %% 8 == 0, aligned operands");
     ClusterArgs a;
     a.x = (const bf16*)x; a.w = (const bf16*)w; a.K = K; a.ranks = ranks; a.per_rank = per_rank; a.xstride = xstride;
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
@@ -198,6 +200,8 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(linear_cluster_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear (cluster): cannot raise shared memory: %s", cudaGetErrorString(e));
         configured = true;
     }
@@ -220,8 +224,10 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
         cfg.numAttrs = 2;
     }
     cfg.attrs = attr;
-    const cudaError_t le = mg == 2 ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<2>, a)
-                                   : cudaLaunchKernelEx(&cfg, linear_cluster_kernel<4>, a);
+    const cudaError_t le = mg == 2   ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<2>, a)
+                           : mg == 4 ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<4>, a)
+                           : mg == 6 ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<6>, a)
+                                     : cudaLaunchKernelEx(&cfg, linear_cluster_kernel<8>, a);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear_cluster: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("linear_cluster");
     return MG_OK;

@@ -627,6 +627,10 @@ WidePlan wide_plan(int M, int N, int K, bool can_slice, bool prologue) {
             if (q.groups < 1) continue;
             const int rounds = (q.row_boxes + q.groups - 1) / q.groups;
             q.solo = (p.slice_k / KB) * (mt / 8) <= SOLO_BLOCKS;
+            // (rows of fewer than 16 blocks whose fragments do not fit a warp are left to the other
+            // kernels: shared by eight warps, a box of so few blocks costs more in hand-overs than in
+            // bytes; measured at K = 512 with 16 tokens: 38 us against 20 us of the row-streaming kernel)
+            if (!q.solo && p.slice_k / KB < 16) continue;
             const size_t sums = q.solo ? 0 : (size_t)2 * CONSUMERS * mt * rows * sizeof(float);
             if (fixed + sums + 2 * stage_bytes > budget) continue;
             q.stages = (int)((budget - fixed - sums) / stage_bytes);

@@ -16,7 +16,7 @@ from .library import KernelLibraryError, check
 
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
-CLUSTER_ROWS = 64        # most tokens the mid-batch (K split over a cluster) projection kernel takes
+CLUSTER_ROWS = 128       # most tokens the mid-batch (K split over a cluster) projection kernel takes
 STREAM_MIN_ROWS = 8192   # a matrix this tall (the head) goes through the streaming kernel ...
 STREAM_ROWS = 16         # ... for up to this many tokens (it takes 64; beyond 16 the tensor-core GEMM measured faster)
 

@@ -329,7 +329,7 @@ def test_streamed_projection_of_long_rows(ops, m, n, k, wide):
 
 
 @pytest.mark.parametrize("m,vocab,k,limit", [(1, 50304, 512, None), (8, 50257, 1600, 50000), (16, 9001, 192, 9000),
-                                             (3, 777, 64, None), (13, 50257, 768, None)])
+                                             (3, 777, 64, None), (13, 50257, 1024, None)])
 def test_large_matrix_kernel_takes_the_greedy_choice_on_its_way(ops, m, vocab, k, limit):
     """The head through the kernel of tiled copies: 32-bit logits, and the first stage of the greedy
     argmax in its epilogue (lowest index among equal maxima, ids at or above the limit excluded)."""
