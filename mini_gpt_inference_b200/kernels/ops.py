@@ -530,11 +530,10 @@ class CudaOps:
             work = self._tile_lists.get(key)
             if work is None:
                 work = np.asarray(query_tiles(batch.q_len, batch.ctx_before, slots), dtype=np.int32).reshape(-1, 5)
-                work.setflags(write=False)
                 if len(self._tile_lists) >= 64:
                     self._tile_lists.pop(next(iter(self._tile_lists)))
                 self._tile_lists[key] = work
-            plan.arrays[name] = work
+            plan.arrays[name] = work.copy()                  # (the table's copy stays as it is)
             plan.signature.append(("attention_merge", batch.max_ctx_after > KEY_CHUNK))
 
     def paged_attention(self, qkv, n_head, n_kv_head, head_dim, scale, cache, ctx):
