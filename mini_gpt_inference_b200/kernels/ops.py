@@ -17,6 +17,7 @@ from .library import KernelLibraryError, check
 EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
 CLUSTER_ROWS = 128       # most tokens the mid-batch (K split over a cluster) projection kernel takes
+CLUSTER_WIDE_MAX_BYTES = 3 << 20   # ... and the largest matrix it is given for more than 64 tokens
 STREAM_MIN_ROWS = 8192   # a matrix this tall (the head) goes through the streaming kernel ...
 STREAM_ROWS = 16         # ... for up to this many tokens (it takes 64; beyond 16 the tensor-core GEMM measured faster)
 
@@ -357,8 +358,10 @@ class CudaOps:
         self._want(x, weight.dtype, "linear input", 2)
         # (a matrix of thousands of 8-row tiles, the head, is left to the tensor-core GEMM: every one
         # of its clusters would stage the activations and meet at a barrier for a few KB of weights)
+        # (and beyond 64 tokens it keeps only matrices of up to 3 MB: measured with 96 and 128 tokens, it
+        # is faster than the tensor-core GEMM at 512 x 2048, slower from 3 x 768 x 768 elements on)
         if (x.dtype == torch.bfloat16 and self.use_cluster and 0 < m <= CLUSTER_ROWS and k % 8 == 0
-                and n <= 8192):
+                and n <= 8192 and (m <= 64 or 2 * n * k <= CLUSTER_WIDE_MAX_BYTES)):
             sink = self._sink_args(kv_sink)
             code = self.lib.mg_linear_cluster(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                               m, n, k, epilogue, out_bf16, *sink, self._stream())
