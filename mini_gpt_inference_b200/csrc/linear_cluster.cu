@@ -88,11 +88,24 @@ __global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const Cluste
     {
         const int pieces = (b_end - b_begin) * 4;                                  // 16-byte pieces per row
         const int k0 = b_begin * 32;
-        for (int i = tid; i < M * pieces; i += THREADS) {
-            const int m = i / pieces, pc = i - m * pieces;
-            const int k = k0 + pc * 8;
-            *reinterpret_cast<uint4*>(xs + (size_t)m * a.xstride + pc * 16) =
-                k < K ? *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + k) : zero4;
+        // (a thread asks for four pieces before it stores the first: one trip to L2 for 4 x THREADS pieces)
+        for (int i0 = tid; i0 < M * pieces; i0 += 4 * THREADS) {
+            uint4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * THREADS;
+                const int m = i / pieces, pc = i - m * pieces;
+                const int k = k0 + pc * 8;
+                v[u] = (i < M * pieces && k < K) ? *reinterpret_cast<const uint4*>(a.x + (size_t)m * K + k) : zero4;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * THREADS;
+                if (i < M * pieces) {
+                    const int m = i / pieces, pc = i - m * pieces;
+                    *reinterpret_cast<uint4*>(xs + (size_t)m * a.xstride + pc * 16) = v[u];
+                }
+            }
         }
     }
     __syncthreads();
