@@ -87,6 +87,8 @@ struct WideArgs {
     float* amax_v;                   // greedy choice on the way: [token][CTA * 2 + finisher], SOLO: [token][CTA * 8 + warp]
     int* amax_i;
     int amax_limit;
+    const uint8_t* next_w;           // weights of the projection that is expected to run next (may be null) ..
+    int next_lines;                  // .. and their size in 128-byte lines: asked into L2 behind this kernel's own
     int* status;
 };
 
@@ -223,6 +225,15 @@ __global__ void __launch_bounds__(THREADS, 1) linear_wide_kernel(const __grid_co
         asm volatile("bar.sync 2, %0;" ::"n"((CONSUMERS + 1) * 32) : "memory");   // the activations are asked for
         if (lane >= a.early && lane < fill) issue(lane);
         __syncwarp();
+        // ---- the weights that the next projection will want: this CTA's share of them is asked into
+        // L2 now, behind its own copies (requests are served in order: they do not delay these), and
+        // travels while this kernel sums, writes and hands over (nothing comes back to the SM) ----
+        if (a.next_w != nullptr && lane > 0) {
+            const int per_cta = (a.next_lines + gridDim.x - 1) / gridDim.x;
+            const int line0 = blockIdx.x * per_cta;
+            for (int l = lane - 1; l < per_cta && line0 + l < a.next_lines; l += 31)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(a.next_w + (size_t)(line0 + l) * 128));
+        }
         if (lane == 0) {
             MG_STAMP_HERE(wide, 9);                                             // the ring is full
             for (int n = stages; n < my_boxes; ++n) {
@@ -693,7 +704,10 @@ MG_API int mg_linear_wide_parts(int M, int N, int K, int prologue) {
 }
 
 // As mg_linear_skinny (same operands, prologue, epilogues and greedy choice), for matrices of many
-// megabytes and up to 16 tokens.  Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 16,
+// megabytes and up to 16 tokens.  next_w / next_lines: optionally the start and the size (in 128-byte
+// lines) of memory that the caller expects to be read next (the weights of the projection behind this
+// one): the kernel asks it into the L2 cache once its own copies are out; it must be readable, nothing
+// else is assumed about it.  Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 16,
 // K % 64 != 0, operands that are not 16-byte aligned, or rows whose activations do not fit the shared
 // memory beside a ring of at least three stages (K beyond 2048 without the residual epilogue, or with
 // the prologue).
@@ -701,9 +715,11 @@ MG_API int mg_linear_wide(const void* x, const float* x32, const int* row_index,
                           const float* shift, float eps, const void* w, const float* bias, void* out,
                           float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
                           void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
-                          int page_tokens, float* amax_v, int* amax_i, int amax_limit, int* status, void* stream) {
+                          int page_tokens, float* amax_v, int* amax_i, int amax_limit, const void* next_w,
+                          int next_lines, int* status, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0 && status != nullptr, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
+    MG_REQUIRE(next_lines >= 0 && (next_w != nullptr || next_lines == 0), "linear: bad hint");
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
     MG_REQUIRE(amax_v == nullptr || (amax_i != nullptr && epilogue == EPI_STORE && !out_bf16),
@@ -732,6 +748,7 @@ MG_API int mg_linear_wide(const void* x, const float* x32, const int* row_index,
     if (a.early < 1) a.early = 1;
     if (a.early > p.stages) a.early = p.stages;
     a.amax_v = amax_v; a.amax_i = amax_i; a.amax_limit = (amax_limit <= 0 || amax_limit > N) ? N : amax_limit;
+    a.next_w = next_lines > 0 ? (const uint8_t*)next_w : nullptr; a.next_lines = next_lines;
     a.status = status;
     const int grid = p.groups * p.k_slices;
     cudaStream_t s = (cudaStream_t)stream;

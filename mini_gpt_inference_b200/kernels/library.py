@@ -33,7 +33,7 @@ _SIGNATURES = {
                          _I, _I, _I, _I, _P, _P, _I, _I, _P, _P],
     "mg_linear_stream_parts": [_I],
     "mg_linear_wide": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
-                       _I, _I, _I, _I, _P, _P, _I, _P, _P],
+                       _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "mg_linear_wide_parts": [_I, _I, _I, _I],
     "mg_argmax_merge": [_P, _P, _P, _I, _I, _P],
     "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],

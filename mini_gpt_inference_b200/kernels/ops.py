@@ -8,6 +8,8 @@ computes anything on this path.
 
 from __future__ import annotations
 
+import weakref
+
 import torch
 
 from . import library
@@ -18,6 +20,7 @@ EPILOGUES = {"none": 0, "gelu_tanh": 1, "residual": 2}
 SKINNY_ROWS = 16         # most tokens the small-batch projection kernel takes
 CLUSTER_ROWS = 128       # most tokens the mid-batch (K split over a cluster) projection kernel takes
 CLUSTER_WIDE_MAX_BYTES = 3 << 20   # ... and the largest matrix it is given for more than 64 tokens
+PREFETCH_MAX_BYTES = 32 << 20   # most of a following matrix that a streaming projection asks into L2
 STREAM_MIN_ROWS = 8192   # a matrix this tall (the head) goes through the streaming kernel ...
 STREAM_ROWS = 16         # ... for up to this many tokens (it takes 64; beyond 16 the tensor-core GEMM measured faster)
 
@@ -91,6 +94,11 @@ class CudaOps:
         self._retired_counters = []
         self._sm_count = None
         self.use_fused_mlp = True
+        # A streaming projection asks the weights of the projection that followed it the last time into
+        # L2 once its own are on their way (learned from the order of the calls: a step repeats it).
+        self.use_weight_prefetch = True
+        self._last_weight = None   # data pointer of the matrix of the last projection
+        self._next_weight = {}     # data pointer of a matrix -> weak reference to the matrix that came next
         self._packed = {}          # data pointer of a matrix -> (the matrix, its copy packed for a kernel)
         self._tile_lists = {}      # (rows, contexts, slots) of a step -> the prompt attention's work list
         self._ring = None          # (tensor that holds the residual stream, zeroed buffer, spare buffer)
@@ -266,6 +274,10 @@ class CudaOps:
         m, k = x.shape
         n = weight.shape[0]
         self._want(weight, None, "linear weight", 2)
+        # which matrix followed which the last time: what a streaming kernel asks into L2 on its way
+        if self._last_weight is not None:
+            self._next_weight[self._last_weight] = weakref.ref(weight)
+        self._last_weight = weight.data_ptr()
         if bias is not None:
             self._want(bias, torch.float32, "linear bias", 1)
         if weight.shape[1] != k or (bias is not None and bias.numel() != n):
@@ -289,9 +301,14 @@ class CudaOps:
                 part_v = torch.empty((m * parts,), dtype=torch.float32, device=self.device)
                 part_i = torch.empty((m * parts,), dtype=torch.int32, device=self.device)
                 amax = [_ptr(part_v), _ptr(part_i), int(limit or 0)]
+            follower = self._next_weight.get(weight.data_ptr())
+            follower = follower() if follower is not None and self.use_weight_prefetch else None
+            ahead = [None, 0]
+            if follower is not None and follower.is_cuda and follower.data_ptr() % 128 == 0:
+                ahead = [_ptr(follower), min(follower.numel() * follower.element_size(), PREFETCH_MAX_BYTES) // 128]
             code = self.lib.mg_linear_wide(*args, _ptr(weight), _ptr(bias), _ptr(out), _ptr(residual),
                                            m, n, k, epilogue, out_bf16, *self._sink_args(kv_sink), *amax,
-                                           _ptr(self.status), self._stream())
+                                           *ahead, _ptr(self.status), self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "linear (large matrix)")
                 if greedy is not None:

@@ -356,6 +356,30 @@ def test_large_matrix_kernel_takes_the_greedy_choice_on_its_way(ops, m, vocab, k
     ops.check_status()
 
 
+def test_large_matrix_kernel_asks_for_the_matrix_that_followed_it_last_time(ops):
+    """The kernel for large matrices asks the weights of the projection that came next the last
+    time into L2 (a hint learned from the order of the calls): results do not change with it, and
+    a matrix that is gone is not asked for."""
+    import gc
+
+    m, n, k = 8, 4800, 1600
+    x = randn(m, k, dtype=torch.bfloat16, seed=95)
+    w1 = randn(n, k, dtype=torch.bfloat16, seed=96, scale=1 / math.sqrt(k))
+    w2 = randn(n, k, dtype=torch.bfloat16, seed=97, scale=1 / math.sqrt(k))
+    want1 = x.double() @ w1.double().T
+    first = ops.linear(x, w1, None, "none", torch.float32)                # nothing is known to follow w1 yet
+    ops.linear(x, w2, None, "none", torch.float32)
+    assert ops._next_weight[w1.data_ptr()]() is w2
+    again = ops.linear(x, w1, None, "none", torch.float32)                # asks for w2 on its way
+    assert torch.equal(first, again) and (first.double() - want1).abs().max() <= 2e-5
+    del w2
+    gc.collect()
+    assert ops._next_weight[w1.data_ptr()]() is None
+    once_more = ops.linear(x, w1, None, "none", torch.float32)            # the follower is gone: no hint
+    assert torch.equal(first, once_more)
+    ops.check_status()
+
+
 @pytest.mark.parametrize("wide", [True, False], ids=["tiles", "rows"])
 @pytest.mark.parametrize("m", [1, 8, 16])
 def test_streamed_qkv_projection_writes_keys_and_values(ops, m, wide):
