@@ -147,17 +147,28 @@ __global__ void __launch_bounds__(THREADS, 1) linear_stream_kernel(const StreamA
                         sq += (dx * dx + dy * dy) + (dz * dz + dw * dw);
                     }
                 const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + a.eps);
+                // gain and shift of four chunks are read before the four results are stored: a store to
+                // shared memory keeps the loads from shared memory behind it in their place
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    if (i < n4) {
-                        const int c = (lane + 32 * i) * 4;
-                        const float4 gn = *reinterpret_cast<const float4*>(gain_s + c);
-                        const float4 sh = *reinterpret_cast<const float4*>(shift_s + c);
-                        uint2 y;
-                        y.x = pack_bf16((v[i].x - mean) * rstd * gn.x + sh.x, (v[i].y - mean) * rstd * gn.y + sh.y);
-                        y.y = pack_bf16((v[i].z - mean) * rstd * gn.z + sh.z, (v[i].w - mean) * rstd * gn.w + sh.w);
-                        *reinterpret_cast<uint2*>(dst + c * 2) = y;
-                    }
+                for (int i0 = 0; i0 < 8; i0 += 4) {
+                    float4 gn[4], sh[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (i0 + u < n4) {
+                            const int c = (lane + 32 * (i0 + u)) * 4;
+                            gn[u] = *reinterpret_cast<const float4*>(gain_s + c);
+                            sh[u] = *reinterpret_cast<const float4*>(shift_s + c);
+                        }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        if (i0 + u < n4) {
+                            const int i = i0 + u, c = (lane + 32 * i) * 4;
+                            uint2 y;
+                            y.x = pack_bf16((v[i].x - mean) * rstd * gn[u].x + sh[u].x, (v[i].y - mean) * rstd * gn[u].y + sh[u].y);
+                            y.y = pack_bf16((v[i].z - mean) * rstd * gn[u].z + sh[u].z, (v[i].w - mean) * rstd * gn[u].w + sh[u].w);
+                            *reinterpret_cast<uint2*>(dst + c * 2) = y;
+                        }
+                }
                 continue;
             }
             // longer or odd rows: three passes in chunks (K is a multiple of 8 here), gain and shift from shared memory
