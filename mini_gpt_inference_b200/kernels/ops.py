@@ -286,8 +286,8 @@ class CudaOps:
         out_bf16 = self._is_bf16(out) if out is not None else 0
         large = n >= STREAM_MIN_ROWS or (self.stream_min_bytes is not None and 2 * n * k >= self.stream_min_bytes)
         if self.use_wide and weight.dtype == torch.bfloat16 and 0 < m <= SKINNY_ROWS and k % 8 == 0 and large:
-            # a matrix of many megabytes: tiles of 64 rows by TMA through a deep ring, started before
-            # the dependency wait
+            # a matrix of many megabytes: whole rows as TMA boxes through a ring of stages, the first of
+            # them asked for before the dependency wait
             if deferred is not None:
                 args = [None, _ptr(deferred.x32), _ptr(deferred.rows), _ptr(deferred.gain),
                         _ptr(deferred.shift), deferred.eps]
