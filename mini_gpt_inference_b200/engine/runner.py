@@ -83,7 +83,7 @@ class _ShapeGraph:
 
 
 class ModelRunner:
-    GRAPH_ROWS = (1, 2, 4, 8, 16, 32, 64, 96, 128, 192, 256)
+    GRAPH_ROWS = (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256)
     SHAPE_GRAPHS = 16              # most captured prompt-step shapes kept at a time
 
     def __init__(self, model: DecoderModel, manager: CacheManager, storage: CacheStorage,
