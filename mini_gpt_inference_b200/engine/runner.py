@@ -385,7 +385,7 @@ class ModelRunner:
         state = _DecodeGraph(rows, offsets, meta, staging, ctx)
         self._fill_graph_inputs(state, [])                # all rows are padding: nothing is written
         meta.copy_(staging)
-        self.model.forward(ctx)                           # warm-up outside the capture
+        self._forward(ctx)                           # warm-up outside the capture
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
         launches = getattr(self.ops, "launches", 0)
@@ -402,7 +402,7 @@ class ModelRunner:
                 # on its way if it can, else by the argmax kernels
                 ctx.greedy_out, ctx.greedy_vocab_limit = self.sampled_ids[:rows], self.greedy_vocab_limit
                 ctx.greedy_taken = False
-                state.logits = self.model.forward(ctx)
+                state.logits = self._forward(ctx)
                 if not ctx.greedy_taken:
                     self.ops.argmax(state.logits, self.greedy_vocab_limit, out=self.sampled_ids[:rows])
         finally:
@@ -511,7 +511,7 @@ class ModelRunner:
         packed = self._pack(entries, arrays)
         decode_only = all(n == 1 for n in packed.q_len)
         if not self.use_cuda_graphs or decode_only:
-            return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
+            return self._forward(self._context(self._to_device(packed.buf, packed.total), packed))
         # what the launches of a step depend on besides the device-side integers
         key = (tuple(packed.q_len), packed.wanted, tuple(packed.extra), packed.signature)
         state = self._shape_graphs.get(key)
@@ -521,7 +521,7 @@ class ModelRunner:
                 self._shape_seen.clear()
             self._shape_seen[key] = seen
             if seen < 2:
-                return self.model.forward(self._context(self._to_device(packed.buf, packed.total), packed))
+                return self._forward(self._context(self._to_device(packed.buf, packed.total), packed))
             return self._capture_shape(key, packed)
         self._shape_graphs[key] = self._shape_graphs.pop(key)         # most recently used last
         self._stage(state, packed)
@@ -532,6 +532,14 @@ class ModelRunner:
         if state.logits is None:
             return None
         return state.logits.clone() if copy else state.logits
+
+    def _forward(self, ctx):
+        """The model's forward pass over one batch; the kernel set is told that a pass begins (what
+        it remembers from launch to launch, such as which matrix followed which, starts anew)."""
+        begin = getattr(self.ops, "begin_forward", None)
+        if begin is not None:
+            begin()
+        return self.model.forward(ctx)
 
     def _stage(self, state: _ShapeGraph, packed: _Packed) -> None:
         if self._copy_done is not None:
@@ -551,7 +559,7 @@ class ModelRunner:
                             torch.zeros(size, dtype=torch.int32, pin_memory=True), None, None, 0)
         self._stage(state, packed)
         ctx = self._context(state.meta, packed)
-        result = self.model.forward(ctx)
+        result = self._forward(ctx)
         if result is not None:
             result = result.clone()                        # the capture below reuses the memory
         torch.cuda.synchronize(self.device)
@@ -562,7 +570,7 @@ class ModelRunner:
             dependent(True)
         try:
             with torch.cuda.graph(graph, pool=self._graph_pool):
-                state.logits = self.model.forward(ctx)
+                state.logits = self._forward(ctx)
         finally:
             if dependent is not None:
                 dependent(False)

@@ -103,6 +103,11 @@ class CudaOps:
         self._tile_lists = {}      # (rows, contexts, slots) of a step -> the prompt attention's work list
         self._ring = None          # (tensor that holds the residual stream, zeroed buffer, spare buffer)
 
+    def begin_forward(self) -> None:
+        """A forward pass begins: the first projection of a pass follows no other (the hint for the
+        L2 prefetch never points from one pass, or one model, into another)."""
+        self._last_weight = None
+
     # ---- helpers --------------------------------------------------------------------------
     def _run(self, code: int, what: str) -> None:
         """Check a launch's return code and count it."""
