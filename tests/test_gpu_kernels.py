@@ -356,6 +356,59 @@ def test_large_matrix_kernel_takes_the_greedy_choice_on_its_way(ops, m, vocab, k
     ops.check_status()
 
 
+def test_large_matrix_kernel_at_random_shapes(ops):
+    """Shapes drawn at random (1 to 16 tokens, rows in multiples of 64 up to 4096, any number of
+    weight rows, each epilogue, with and without bias and LayerNorm prologue): the cuts of the
+    kernel of tiled copies (rows per box, slices of K, warps that own or share a box, bias kept in
+    shared memory or not) against a 64-bit product."""
+    import random
+
+    rng = random.Random(5)
+    flags = (ops.stream_min_bytes, ops.use_stream, ops.use_skinny, ops.use_cluster)
+    ops.stream_min_bytes, ops.use_stream, ops.use_skinny, ops.use_cluster = 0, False, False, False
+    taken = 0
+    try:
+        for case in range(40):
+            m = rng.choice([1, 2, 3, 5, 8, 9, 13, 16])
+            k = 64 * rng.choice([1, 2, 3, 5, 8, 12, 16, 17, 25, 32, 40, 64])
+            n = rng.choice([8, 17, 64, 100, 333, 1024, 1601, 4099, 20011, 70001])
+            epilogue = rng.choice(["none", "gelu_tanh", "residual"])
+            prologue = rng.random() < 0.5 and k <= 2048
+            with_bias = rng.random() < 0.7
+            x32 = randn(m, k, seed=200 + case, scale=1.5) + 0.25
+            gain, shift = randn(k, seed=300 + case) + 1.0, randn(k, seed=400 + case)
+            w = randn(n, k, dtype=torch.bfloat16, seed=500 + case, scale=1 / math.sqrt(k))
+            b = randn(n, seed=600 + case) if with_bias else None
+            if prologue:
+                xin = ops.defer_layernorm(x32, gain, shift, 1e-5, torch.bfloat16)
+                xr = torch.nn.functional.layer_norm(x32.double(), (k,), gain.double(), shift.double(), 1e-5)
+                xr = xr.to(torch.bfloat16).double()
+            else:
+                xin = x32.to(torch.bfloat16)
+                xr = xin.double()
+            want = xr @ w.double().T + (b.double() if with_bias else 0.0)
+            before = ops.launches
+            if epilogue == "residual":
+                res = randn(m, n, seed=700 + case)
+                keep = res.clone()
+                if prologue:
+                    xin = xin.materialize()
+                ops.linear_residual(xin, w, b, res)
+                got, want = res.double(), keep.double() + want
+                tol = 2e-2 if prologue else 2e-4
+            else:
+                got = ops.linear(xin, w, b, epilogue, torch.float32).double()
+                if epilogue == "gelu_tanh":
+                    want = plain_gpt.gelu_tanh(want)
+                tol = 2e-2 if prologue else 2e-4
+            taken += int(ops.launches == before + 1)
+            assert (got - want).abs().max() <= tol, (case, m, n, k, epilogue, prologue, with_bias)
+    finally:
+        ops.stream_min_bytes, ops.use_stream, ops.use_skinny, ops.use_cluster = flags
+    assert taken >= 25, "most of these shapes are the kernel's own (the others it refuses: other kernels run)"
+    ops.check_status()
+
+
 def test_large_matrix_kernel_asks_for_the_matrix_that_followed_it_last_time(ops):
     """The kernel for large matrices asks the weights of the projection that came next the last
     time into L2 (a hint learned from the order of the calls): results do not change with it, and
