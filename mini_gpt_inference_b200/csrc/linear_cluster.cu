@@ -37,40 +37,49 @@ struct ClusterArgs {
     int xstride;                     // bytes between staged activation rows
 };
 
-template <int MG>   // groups of 16 tokens held: 2, 4, 6 or 8
+// MG: groups of 16 tokens held: 2, 4, 6 or 8.  NTW: tiles of 8 weight rows per warp (2 for matrices of
+// so many rows that one tile per warp would need several rounds of CTAs: half the CTAs, and a
+// fragment of the activations feeds two tiles).
+template <int MG, int NTW>
 __global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const ClusterArgs a) {
     constexpr int MT = MG * 16;
+    constexpr int CTILES = WARPS * NTW;                                            // tiles per cluster
     // k blocks (of 32) whose weights a lane holds at once: fewer where the sums take more registers,
     // so that two CTAs still share an SM
-    constexpr int PRE = MG <= 4 ? 8 : 4;
+    constexpr int PRE = (MG <= 4 ? 8 : 4) / NTW;
     cg::cluster_group cluster = cg::this_cluster();
     const int rank = (int)cluster.block_rank();
     const int ranks = a.ranks;
     const int cluster_id = blockIdx.x / ranks;
     extern __shared__ __align__(16) uint8_t smem_raw[];
     uint8_t* xs = smem_raw;                                                        // [MT][xstride]
-    float* part = reinterpret_cast<float*>(smem_raw + (size_t)MT * a.xstride);     // [WARPS][MT][8]
+    float* part = reinterpret_cast<float*>(smem_raw + (size_t)MT * a.xstride);     // [CTILES][MT][8]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int K = a.K, N = a.ep.N, M = a.ep.M;
     const int kblocks = (K + 31) / 32;
     const int b_begin = min(kblocks, rank * a.per_rank), b_end = min(kblocks, b_begin + a.per_rank);
     const int total_tiles = (N + TILE_N - 1) / TILE_N;
-    const int tile = cluster_id * WARPS + warp;
-    const bool live = tile < total_tiles;
+    const int tile0 = cluster_id * CTILES + warp * NTW;                            // this warp's first tile
     const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
     // this warp's weights first: they travel while the kernel in front drains
-    const bf16* wrow = a.w + (size_t)min(tile * TILE_N + g, N - 1) * K;
-    uint4 first_w[PRE];
+    const bf16* wrow[NTW];
+    bool live[NTW];
+    uint4 first_w[NTW][PRE];
 #pragma unroll
-    for (int i = 0; i < PRE; ++i) {
-        const int k = (b_begin + i) * 32 + 8 * t;
-        first_w[i] = (live && b_begin + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow + k) : zero4;
+    for (int h = 0; h < NTW; ++h) {
+        live[h] = tile0 + h < total_tiles;
+        wrow[h] = a.w + (size_t)min((tile0 + h) * TILE_N + g, N - 1) * K;
+#pragma unroll
+        for (int i = 0; i < PRE; ++i) {
+            const int k = (b_begin + i) * 32 + 8 * t;
+            first_w[h][i] = (live[h] && b_begin + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow[h] + k) : zero4;
+        }
     }
     // the first result this thread will finish (tile `rank` of the cluster), and its bias
-    const int e_m = tid / TILE_N, e_n = (cluster_id * WARPS + rank) * TILE_N + tid % TILE_N;
-    const bool e_live = rank < WARPS && e_m < M && e_n < N;
+    const int e_m = tid / TILE_N, e_n = (cluster_id * CTILES + rank) * TILE_N + tid % TILE_N;
+    const bool e_live = rank < CTILES && e_m < M && e_n < N;
     float e_bias = (e_live && a.ep.bias) ? a.ep.bias[e_n] : 0.f;
     // for the QKV projection, the cache rows of the tokens this thread finishes (inputs of the step)
     int e_slot[MT * TILE_N / THREADS];
@@ -110,22 +119,27 @@ __global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const Cluste
     }
     __syncthreads();
 
-    float c[MG][4];
+    float c[NTW][MG][4];
 #pragma unroll
-    for (int mg = 0; mg < MG; ++mg)
+    for (int h = 0; h < NTW; ++h)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) c[mg][i] = 0.f;
-    if (live) {
+        for (int mg = 0; mg < MG; ++mg)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) c[h][mg][i] = 0.f;
+    if (live[0]) {                                                                 // (a warp's tiles are live from the first on)
         for (int b0 = b_begin; b0 < b_end; b0 += PRE) {
-            uint4 wv[PRE];
-            if (b0 == b_begin) {
+            uint4 wv[NTW][PRE];
 #pragma unroll
-                for (int i = 0; i < PRE; ++i) wv[i] = first_w[i];
-            } else {
+            for (int h = 0; h < NTW; ++h) {
+                if (b0 == b_begin) {
 #pragma unroll
-                for (int i = 0; i < PRE; ++i) {
-                    const int k = (b0 + i) * 32 + 8 * t;
-                    wv[i] = (b0 + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow + k) : zero4;
+                    for (int i = 0; i < PRE; ++i) wv[h][i] = first_w[h][i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < PRE; ++i) {
+                        const int k = (b0 + i) * 32 + 8 * t;
+                        wv[h][i] = (live[h] && b0 + i < b_end && k < K) ? *reinterpret_cast<const uint4*>(wrow[h] + k) : zero4;
+                    }
                 }
             }
 #pragma unroll
@@ -136,30 +150,34 @@ __global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const Cluste
                     for (int mg = 0; mg < MG; ++mg) {
                         const uint4 x0 = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 16 + g) * a.xstride + off);
                         const uint4 x1 = *reinterpret_cast<const uint4*>(xs + (size_t)(mg * 16 + g + 8) * a.xstride + off);
-                        mma_bf16(c[mg], x0.x, x1.x, x0.y, x1.y, wv[i].x, wv[i].y);
-                        mma_bf16(c[mg], x0.z, x1.z, x0.w, x1.w, wv[i].z, wv[i].w);
+#pragma unroll
+                        for (int h = 0; h < NTW; ++h) {
+                            mma_bf16(c[h][mg], x0.x, x1.x, x0.y, x1.y, wv[h][i].x, wv[h][i].y);
+                            mma_bf16(c[h][mg], x0.z, x1.z, x0.w, x1.w, wv[h][i].z, wv[h][i].w);
+                        }
                     }
                 }
             }
         }
     }
     // c0, c1: token 16 mg + g, rows 2t and 2t+1 of the tile; c2, c3: token 16 mg + g + 8.
-    // The partial sums of tile `warp` go straight into the shared memory of the CTA that finishes
-    // that tile (rank warp % ranks), into the row of this rank: [slot][source rank][MT][8].
-    {
-        float* theirs = cluster.map_shared_rank(part, warp % ranks) +
-                        ((size_t)(warp / ranks) * ranks + rank) * MT * TILE_N;
+    // The partial sums of a tile go straight into the shared memory of the CTA that finishes that
+    // tile (rank tile % ranks), into the row of this rank: [slot][source rank][MT][8].
+#pragma unroll
+    for (int h = 0; h < NTW; ++h) {
+        const int tl = warp * NTW + h;                                             // the tile's number in the cluster
+        float* theirs = cluster.map_shared_rank(part, tl % ranks) + ((size_t)(tl / ranks) * ranks + rank) * MT * TILE_N;
 #pragma unroll
         for (int mg = 0; mg < MG; ++mg) {
-            *reinterpret_cast<float2*>(theirs + (mg * 16 + g) * TILE_N + 2 * t) = make_float2(c[mg][0], c[mg][1]);
-            *reinterpret_cast<float2*>(theirs + (mg * 16 + g + 8) * TILE_N + 2 * t) = make_float2(c[mg][2], c[mg][3]);
+            *reinterpret_cast<float2*>(theirs + (mg * 16 + g) * TILE_N + 2 * t) = make_float2(c[h][mg][0], c[h][mg][1]);
+            *reinterpret_cast<float2*>(theirs + (mg * 16 + g + 8) * TILE_N + 2 * t) = make_float2(c[h][mg][2], c[h][mg][3]);
         }
     }
     cluster.sync();                                    // all partial sums have arrived; nothing remote is touched after this
     // ---- the CTA of rank r finishes tiles r, r + ranks, ...: slices added in rank order ----
-    for (int slot = 0; slot * ranks + rank < WARPS; ++slot) {
+    for (int slot = 0; slot * ranks + rank < CTILES; ++slot) {
         const int tl = slot * ranks + rank;
-        const int out_tile = cluster_id * WARPS + tl;
+        const int out_tile = cluster_id * CTILES + tl;
         if (out_tile >= total_tiles) break;
 #pragma unroll
         for (int j = 0; j < MT * TILE_N / THREADS; ++j) {
@@ -200,7 +218,11 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
     const int slice_bytes = per_rank * 64;
     const int xstride = slice_bytes + (slice_bytes % 128 == 0 ? 64 : 0);               // rows 64 bytes apart mod 128
     const int mg = M <= 32 ? 2 : M <= 64 ? 4 : M <= 96 ? 6 : 8;
-    const size_t smem = (size_t)mg * 16 * xstride + (size_t)WARPS * mg * 16 * TILE_N * sizeof(float);
+    const int tiles = (N + TILE_N - 1) / TILE_N;
+    // two tiles per warp where one would make more CTAs than two rounds of them hold (up to 64 tokens:
+    // beyond, the sums of two tiles do not fit the registers beside two CTAs per SM)
+    const int ntw = (mg <= 4 && (long long)((tiles + WARPS - 1) / WARPS) * ranks > 2 * 296) ? 2 : 1;
+    const size_t smem = (size_t)mg * 16 * xstride + (size_t)WARPS * ntw * mg * 16 * TILE_N * sizeof(float);
     if (M > MAX_M || K % 8 != 0 || smem > 200 * 1024 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15))
         return mg_set_error(MG_ERR_UNSUPPORTED, "linear (cluster): needs M <= 128, K %% 8 == 0, aligned operands");
     ClusterArgs a;
@@ -209,17 +231,16 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
     a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(linear_cluster_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(linear_cluster_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    void (*kernel)(const ClusterArgs) = nullptr;
+    if (ntw == 2) kernel = mg == 2 ? linear_cluster_kernel<2, 2> : linear_cluster_kernel<4, 2>;
+    else kernel = mg == 2 ? linear_cluster_kernel<2, 1> : mg == 4 ? linear_cluster_kernel<4, 1>
+                  : mg == 6 ? linear_cluster_kernel<6, 1> : linear_cluster_kernel<8, 1>;
+    {
+        // (once per variant: the attribute is cheap to set again)
+        const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         if (e != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear (cluster): cannot raise shared memory: %s", cudaGetErrorString(e));
-        configured = true;
     }
-    const int tiles = (N + TILE_N - 1) / TILE_N;
-    const int clusters = (tiles + WARPS - 1) / WARPS;
+    const int clusters = (tiles + WARPS * ntw - 1) / (WARPS * ntw);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)clusters * ranks);
     cfg.blockDim = dim3(THREADS);
@@ -237,10 +258,7 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
         cfg.numAttrs = 2;
     }
     cfg.attrs = attr;
-    const cudaError_t le = mg == 2   ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<2>, a)
-                           : mg == 4 ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<4>, a)
-                           : mg == 6 ? cudaLaunchKernelEx(&cfg, linear_cluster_kernel<6>, a)
-                                     : cudaLaunchKernelEx(&cfg, linear_cluster_kernel<8>, a);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kernel, a);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "linear_cluster: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("linear_cluster");
     return MG_OK;
