@@ -261,15 +261,18 @@ class LLMEngine:
 
     @staticmethod
     def _check_finish(seq: SequenceState, token: int, text: str = "") -> str | None:
-        params = seq.request.sampling_params
-        if seq.request.eot_token_id is not None and token == seq.request.eot_token_id:
+        request = seq.request
+        params = request.sampling_params
+        if request.eot_token_id is not None and token == request.eot_token_id:
             return "eot"
         if len(seq.output_token_ids) >= params.max_tokens:
             return "length"
-        if token in params.stop_token_ids:
+        if params.stop_token_ids and token in params.stop_token_ids:
             return "stop"
-        if any(stop and stop in text for stop in params.stop):
-            return "stop"
+        if params.stop and text:
+            for stop in params.stop:
+                if stop and stop in text:
+                    return "stop"
         return None
 
     # ---- convenience ------------------------------------------------------------------------

@@ -164,11 +164,19 @@ class ModelRunner:
         a portion of a prompt (None for the few tokens of a decoding request)."""
         seen = set()
         arrays = []
+        vocab, max_context, length_of = self.vocab_size, self.max_context, self.length_of
         for e in entries:
             if e.request_id in seen:
                 raise StepError(f"request {e.request_id!r} appears twice in one step")
             seen.add(e.request_id)
             n = len(e.tokens)
+            if n == 1:                                   # a decoding request: the common case, kept short
+                t = e.tokens[0]
+                want = e.want
+                if (0 <= t < vocab and (not want or (len(want) == 1 and want[0] == 0))
+                        and length_of(e.request_id) + 1 <= max_context):
+                    arrays.append(None)
+                    continue                             # (anything else falls through to the messages below)
             if n == 0:
                 raise StepError(f"request {e.request_id!r} brings no tokens")
             if n > 16:                                   # a prompt portion: one pass in numpy
