@@ -20,6 +20,10 @@ bfloat16, a batch of 8 and contexts that end at 2048 tokens.  One JSON line is p
 ``--only serve`` prints a line of its own: 64 requests (prompts of 16 to 512 tokens, 256 greedy
 tokens each) through ``LLMEngine.generate``, wall clock: the scheduler's mixed batches.
 
+``--only kernels`` prints the device time of each function of the kernel library in one decode step
+and one 2,048-token prompt (an event pair around every launch; the reference sums its kernels' time
+from a profiler's trace, bench/bench_kernels.py:71-116).
+
 ``--sizes`` runs the same measurement at the layer sizes of GPT-2 small or GPT-2 XL (position
 table of 1,024: the prefill step is then two whole prompts of 1,024 tokens).
 
@@ -78,7 +82,7 @@ def parse_args():
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 / 64 and prefill")
-    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve"], default="all",
+    ap.add_argument("--only", choices=["all", "decode", "prefill", "serve", "kernels"], default="all",
                     help="a small case for profilers: only the device-timed decode steps, or only "
                          "the 2,048-token prefill (the printed line is then partial); serve: 64 "
                          "requests with prompts of 16 to 512 tokens and 256 generated tokens each "
@@ -389,6 +393,44 @@ def serve_mixed(args, requests: int = 64, new_tokens: int = 256) -> dict:
             "finish_reasons": sorted({o["finish_reason"] for o in outs})}
 
 
+def kernel_times(args) -> dict:
+    """Device time of each exported function of the kernel library in one decode step at the
+    headline batch and in one 2,048-token prompt, launches issued one by one with an event before
+    and after each (no CUDA graph, nothing overlaps: shares, not the step's time)."""
+    import torch
+
+    from mini_gpt_inference_b200.engine.runner import StepEntry
+    from mini_gpt_inference_b200.kernels.timing import LaunchTimer
+
+    batch = args.batch
+    cfg, engine = build_engine(args, batch + 1, args.context)
+    runner = engine.runner
+    runner.use_cuda_graphs = False
+    gen = torch.Generator().manual_seed(1)
+    rids = [f"k{i}" for i in range(batch)]
+    for rid in rids:
+        runner.step([StepEntry(rid, torch.randint(0, cfg.vocab_size, (args.context - 4,), generator=gen).tolist(), [])])
+    out = {"impl": "ours", "partial": "device time of each launch, issued one by one", "batch": batch,
+           "context": args.context}
+    for name, entries in (
+            ("decode", lambda: [StepEntry(rid, [7], [0]) for rid in rids]),
+            ("prefill", lambda: [StepEntry("kp", torch.randint(0, cfg.vocab_size, (min(PREFILL_TOKENS, args.context),),
+                                                               generator=gen).tolist(), [min(PREFILL_TOKENS, args.context) - 1])])):
+        for rep in range(3):                               # the third pass is the one reported
+            with LaunchTimer(runner.ops) as timer:
+                runner.step(entries())
+            rows = timer.summary()
+            if name == "prefill":
+                runner.finish("kp")
+        out[name] = [{"function": r.name, "calls": r.calls, "total_us": round(r.total_us, 1),
+                      "mean_us": round(r.mean_us, 2), "share": round(r.share, 3)} for r in rows]
+        out[name + "_total_us"] = round(sum(r.total_us for r in rows), 1)
+    for rid in rids:
+        runner.finish(rid)
+    runner.ops.check_status()
+    return out
+
+
 def check_decode_logits(args) -> dict:
     """Outside every timed region: the decode step that the benchmark times (batch 8, contexts of
     2,048, the replayed graph) is run once on fixed tokens and its logits are compared with rows
@@ -446,6 +488,8 @@ def run_ours(args) -> dict:
             "value": round(PREFILL_TOKENS / (pre_ms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pre_ms, 4)}}
     if args.only == "serve":
         return serve_mixed(args)
+    if args.only == "kernels":
+        return kernel_times(args)
     if args.only == "decode":
         cfg, windows, launches, mean_ctx, clocks = device_decode(args, args.batch, args.steps, args.warmup,
                                                                  min_seconds=0.0)
