@@ -646,12 +646,21 @@ def run_reference(args) -> dict:
         clocks = sampler.stop()
         assert host_ids.shape == (batch, 1)
         # How much of a step the device is busy: the sum of the kernels' own durations over a few
-        # further steps (the events above bracket the host's work between launches as well).
+        # further steps (the events above bracket the host's work between launches as well).  The
+        # timed steps have filled the cache to its end, so these run on a second cache, right after
+        # the same prompt.
         busy_ms = None
         try:
             from torch.profiler import ProfilerActivity, profile
 
             probe_steps = 3
+            del cache
+            cache = StaticKVCache(n_layer=cfg.n_layer, n_head=cfg.n_head, head_dim=model.head_dim,
+                                  max_batch_size=batch, max_seq_len=cfg.block_size, device="cuda", dtype=dtype)
+            logits = model(ForwardBatch(input_ids=prompt, position_ids=pos, is_prefill=True, cache=cache))
+            cache.advance(prompt_len, batch)
+            torch.cuda.synchronize()
+            ran = 0
             with profile(activities=[ProfilerActivity.CUDA]) as prof:
                 for _ in range(probe_steps):
                     next_id = torch.argmax(logits, dim=-1, keepdim=True)
@@ -661,9 +670,10 @@ def run_reference(args) -> dict:
                     p = torch.full((batch, 1), cur_len, device="cuda", dtype=torch.long)
                     logits = model(ForwardBatch(input_ids=next_id, position_ids=p, is_prefill=False, cache=cache))
                     cache.advance(1, batch)
+                    ran += 1
                 torch.cuda.synchronize()
             total_us = sum(getattr(e, "self_device_time_total", 0.0) for e in prof.key_averages())
-            busy_ms = round(total_us / 1e3 / probe_steps, 4) if total_us else None
+            busy_ms = round(total_us / 1e3 / ran, 4) if total_us and ran else None
         except Exception:  # noqa: BLE001 - no profiler on this machine: the figure is left out
             busy_ms = None
     ms = statistics.fmean(times)
