@@ -36,6 +36,7 @@
 #include "common.cuh"
 
 MG_STAMP_DECLARE(attn)
+MG_GUARD_DECLARE(attention_split)
 #ifdef MG_STAMPS
 // (the grid is three-dimensional here: stamps go by the CTA's linear index, thread 0 of each CTA)
 #define MG_STAMP_ATTN(slot)                                                                                  \
@@ -212,6 +213,7 @@ attention_merge_kernel(const int* __restrict__ positions, const float* __restric
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int splits = (p - lo) / SPLIT + 1;
     if (splits == 1) return;                                            // the attention kernel wrote the row itself
+    if (!MG_GUARDED(attention_split, MG_GUARD_POSITION, splits - 1, max_splits)) return;   // (more blocks than the scratch holds)
     const size_t pair = (size_t)token * n_head + head;
     merge_row<D>(part_out, part_ml, pair * max_splits, splits, scratch, out + pair * D, warp, lane);
 }
@@ -229,7 +231,8 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
                        const int* __restrict__ token_request, const int* __restrict__ positions,
                        bf16* __restrict__ out, float* __restrict__ part_out, float* __restrict__ part_ml,
                        int* __restrict__ counters, int n_head, int n_kv_head, int page_tokens, int max_pages,
-                       int window, int max_splits, float scale_log2e, int head_tiles, int merge_inside) {
+                       int window, int max_splits, float scale_log2e, int head_tiles, int merge_inside,
+                       int num_pages, int n_requests) {
     constexpr int SPLIT = split_keys(D);
     constexpr int KW = SPLIT / WARPS;          // keys per warp
     constexpr int CPR = D / 8;                 // 16-byte pieces per row
@@ -257,8 +260,12 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     const int g = lane >> 2, t = lane & 3;
     MG_STAMP_ATTN(0);
     pdl_trigger();
-    const int request = token_request[token];                          // asked for together with the position:
-    const int p = positions[token];                                    // one trip to memory, not two
+    int request = token_request[token];                                // asked for together with the position:
+    int p = positions[token];                                          // one trip to memory, not two
+    // (guarded builds: a request beyond the block tables' rows, a position beyond their width or a page
+    // beyond the pool is recorded, and request 0, position 0 or page 0 is read in its place)
+    if (!MG_GUARDED(attention_split, MG_GUARD_REQUEST, request, n_requests)) request = 0;
+    if (p >= 0 && !MG_GUARDED(attention_split, MG_GUARD_POSITION, p, (long long)max_pages * page_tokens)) p = 0;
     if (p < 0) {                                                        // padding row of a fixed-size batch
         pdl_wait();                                                     // `out` may still be in use before
         if (split == 0)
@@ -271,6 +278,7 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
     if (start > p) return;                                              // this block holds no key of the token
     const int count = min(SPLIT, p + 1 - start);
     const int splits = (p - lo) / SPLIT + 1;
+    if (!MG_GUARDED(attention_split, MG_GUARD_POSITION, splits - 1, max_splits)) return;   // (more blocks than the scratch holds)
     const int* table = block_table + (size_t)request * max_pages;
     const bool holds_newest = start + count - 1 == p;
     const int old_count = holds_newest ? count - 1 : count;            // rows [0, old_count) are old
@@ -280,7 +288,9 @@ attention_split_kernel(const bf16* __restrict__ qkv, const bf16* __restrict__ k_
         const int r = warp * KW + i;
         if (r < count) {
             const int pos = start + r, pi = pos / page_tokens;
-            grow[r] = (table[pi] * n_kv_head + kv_head) * page_tokens + (pos - pi * page_tokens);
+            int page = table[pi];
+            if (!MG_GUARDED(attention_split, MG_GUARD_PAGE, page, num_pages)) page = 0;
+            grow[r] = (page * n_kv_head + kv_head) * page_tokens + (pos - pi * page_tokens);
         }
     }
     __syncwarp();
@@ -530,7 +540,7 @@ template <int D>
 int launch(const void* qkv, const void* k_pages, const void* v_pages, const int* block_table,
            const int* token_request, const int* positions, void* out, float* part_out, float* part_ml,
            int* counters, int n_tokens, int n_head, int n_kv_head, int page_tokens, int max_pages, int window,
-           int max_splits, float scale, cudaStream_t s) {
+           int max_splits, float scale, int num_pages, int n_requests, cudaStream_t s) {
     const int group = n_head / n_kv_head;
     const int head_tiles = (group + HEAD_ROWS - 1) / HEAD_ROWS;
     const int nh_max = group < HEAD_ROWS ? group : HEAD_ROWS;
@@ -573,7 +583,7 @@ int launch(const void* qkv, const void* k_pages, const void* v_pages, const int*
     cudaError_t le = mg_launch(kernel, grid, dim3(THREADS), smem, s, true, (const bf16*)qkv, (const bf16*)k_pages,
                                (const bf16*)v_pages, block_table, token_request, positions, (bf16*)out, part_out, part_ml,
                                counters, n_head, n_kv_head, page_tokens, max_pages, window, max_splits,
-                               scale * 1.4426950408889634f, head_tiles, merge_inside);
+                               scale * 1.4426950408889634f, head_tiles, merge_inside, num_pages, n_requests);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_split: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_split");
     if (!merge_inside) {
@@ -617,13 +627,15 @@ MG_API long long mg_attention_split_scratch_floats(int n_tokens, int n_head, int
 // qkv / pages / out as mg_paged_attention_generic, bfloat16 only.  `scratch` holds
 // mg_attention_split_scratch_floats() floats and need not be initialised; `counters` holds
 // n_tokens * n_head ints that are ZERO before the first launch (the kernel leaves them zero);
-// `max_splits` = mg_attention_split_count() of the longest context; `status` is not written
+// `max_splits` = mg_attention_split_count() of the longest context; `num_pages` and `n_requests`: pages
+// of the pool and rows of the block table (what guarded builds hold the indices against); `status` is not written
 // (the kernel has no bounded wait).  Launches that share scratch or counters must not overlap.
 MG_API int mg_paged_attention_split(const void* qkv, const void* k_pages, const void* v_pages,
                                     const int* block_table, const int* token_request, const int* positions,
                                     void* out, float* scratch, int* counters, int n_tokens, int n_head,
                                     int n_kv_head, int head_dim, int page_tokens, int max_pages, int window,
-                                    int max_splits, float scale, int* status, void* stream) {
+                                    int max_splits, float scale, int num_pages, int n_requests, int* status,
+                                    void* stream) {
     (void)status;
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && max_splits > 0,
@@ -638,7 +650,7 @@ MG_API int mg_paged_attention_split(const void* qkv, const void* k_pages, const 
     case DIM:                                                                                                     \
         return launch<DIM>(qkv, k_pages, v_pages, block_table, token_request, positions, out, part_out, part_ml, \
                            counters, n_tokens, n_head, n_kv_head, page_tokens, max_pages, window, max_splits,    \
-                           scale, s)
+                           scale, num_pages, n_requests, s)
     switch (head_dim) {
         MG_SPLIT_CASE(16);
         MG_SPLIT_CASE(32);

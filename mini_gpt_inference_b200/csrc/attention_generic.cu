@@ -14,6 +14,8 @@
 
 #include "common.cuh"
 
+MG_GUARD_DECLARE(attention_generic)
+
 namespace {
 
 constexpr int WARPS = 4;
@@ -25,7 +27,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
                                const T* __restrict__ v_pages, const int* __restrict__ block_table,
                                const int* __restrict__ token_request, const int* __restrict__ positions,
                                T* __restrict__ out, int n_tokens, int n_head, int n_kv_head, int head_dim,
-                               int page_tokens, int max_pages, int window, float scale) {
+                               int page_tokens, int max_pages, int window, float scale, int num_pages,
+                               int n_requests) {
     extern __shared__ float q_smem[];                     // [WARPS][head_dim]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int token = blockIdx.x;
@@ -33,14 +36,19 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
     if (head >= n_head) return;                            // whole warp leaves together
     const int kv_head = head / (n_head / n_kv_head);
     const int qkv_width = (n_head + 2 * n_kv_head) * head_dim;
-    const int p = positions[token];
+    int p = positions[token];
     if (p < 0) {                                           // padding row of a fixed-size batch
         T* pad = out + (size_t)token * n_head * head_dim + (size_t)head * head_dim;
         for (int d = lane; d < head_dim; d += 32) pad[d] = from_float<T>(0.f);
         return;
     }
+    // (guarded builds: a position beyond the block table, a request beyond its rows or a page beyond
+    // the pool is recorded, and position 0, request 0 or page 0 is read in its place)
+    if (!MG_GUARDED(attention_generic, MG_GUARD_POSITION, p, (long long)max_pages * page_tokens)) p = 0;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-    const int* table = block_table + (size_t)token_request[token] * max_pages;
+    int request = token_request[token];
+    if (!MG_GUARDED(attention_generic, MG_GUARD_REQUEST, request, n_requests)) request = 0;
+    const int* table = block_table + (size_t)request * max_pages;
 
     float* q = q_smem + warp * head_dim;
     const T* qrow = qkv + (size_t)token * qkv_width + (size_t)head * head_dim;
@@ -58,7 +66,8 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
         int row = 0;                                       // row of key j in the page storage
         float s = -INFINITY;
         if (valid) {
-            const int page = table[j / page_tokens];
+            int page = table[j / page_tokens];
+            if (!MG_GUARDED(attention_generic, MG_GUARD_PAGE, page, num_pages)) page = 0;
             row = (page * n_kv_head + kv_head) * page_tokens + (j % page_tokens);
             const T* kr = k_pages + (size_t)row * head_dim;
             float dot = 0.f;
@@ -96,12 +105,14 @@ paged_attention_generic_kernel(const T* __restrict__ qkv, const T* __restrict__ 
 }  // namespace
 
 // qkv: [n_tokens, (n_head + 2 n_kv_head) * head_dim]; pages: [page, kv head, page_tokens, head_dim];
-// block_table: [requests, max_pages]; out: [n_tokens, n_head * head_dim].  window <= 0: none.
+// block_table: [n_requests, max_pages]; out: [n_tokens, n_head * head_dim].  window <= 0: none.
+// num_pages: pages of the pool (with n_requests, what guarded builds hold the indices against).
 MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, const void* v_pages,
                                       const int* block_table, const int* token_request,
                                       const int* positions, void* out, int n_tokens, int n_head,
                                       int n_kv_head, int head_dim, int page_tokens, int max_pages,
-                                      int window, float scale, int is_bf16, void* stream) {
+                                      int window, float scale, int num_pages, int n_requests, int is_bf16,
+                                      void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0,
                "attention: bad sizes");
@@ -114,11 +125,11 @@ MG_API int mg_paged_attention_generic(const void* qkv, const void* k_pages, cons
     if (is_bf16)
         paged_attention_generic_kernel<bf16><<<grid, block, smem, s>>>(
             (const bf16*)qkv, (const bf16*)k_pages, (const bf16*)v_pages, block_table, token_request, positions,
-            (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale);
+            (bf16*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale, num_pages, n_requests);
     else
         paged_attention_generic_kernel<float><<<grid, block, smem, s>>>(
             (const float*)qkv, (const float*)k_pages, (const float*)v_pages, block_table, token_request, positions,
-            (float*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale);
+            (float*)out, n_tokens, n_head, n_kv_head, head_dim, page_tokens, max_pages, window, scale, num_pages, n_requests);
     MG_CHECK_LAUNCH("paged_attention_generic");
     return MG_OK;
 }

@@ -41,6 +41,8 @@
 
 #include "blackwell.cuh"
 
+MG_GUARD_DECLARE(attention_prefill)
+
 namespace {
 
 constexpr int D = 64;                 // head_dim of this kernel
@@ -72,7 +74,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ block_table, const int* __restrict__ positions,
                             bf16* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
                             int n_head, int n_kv_head, int page_tokens, int box_rows, int max_pages, int window,
-                            float scale_log2e, int* __restrict__ status) {
+                            float scale_log2e, int* __restrict__ status, int n_tokens, int num_pages, int n_requests) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t pad = (1024u - (smem_u32(smem_raw) & 1023u)) & 1023u;
     if (pad > ALIGN_SLACK) {                           // uniform over the CTA; nothing is held yet
@@ -88,9 +90,18 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item = blockIdx.x, head = blockIdx.y;
-    const int req = work[5 * item], row0 = work[5 * item + 1], n_rows = work[5 * item + 2];
+    int req = work[5 * item], row0 = work[5 * item + 1], n_rows = work[5 * item + 2];
     const int chunk = work[5 * item + 3], n_chunks = work[5 * item + 4];
     const int kv_head = head / (n_head / n_kv_head);
+    // (guarded builds: a request beyond the block tables' rows, a first row beyond the batch or a page
+    // beyond the pool is recorded; request 0 and row 0 are read in their place, and such a page counts
+    // as missing: its keys are zeros)
+    if (!MG_GUARDED(attention_prefill, MG_GUARD_REQUEST, req, n_requests)) req = 0;
+    if (!MG_GUARDED(attention_prefill, MG_GUARD_ROW, n_rows - 1, BQ) || !MG_GUARDED(attention_prefill, MG_GUARD_ROW, row0, n_tokens) ||
+        !MG_GUARDED(attention_prefill, MG_GUARD_ROW, row0 + n_rows - 1, n_tokens)) {
+        row0 = 0;
+        n_rows = 1;
+    }
     const int pos0 = positions[row0];
     const int last_key = pos0 + n_rows - 1;
     const int lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
@@ -124,7 +135,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     auto box_row = [&](int it) {
         const int pos = (first_blk + it) * BK + lane * box_rows;
         const int pi = pos / page_tokens;
-        const int page = (lane * box_rows < BK && pi < max_pages) ? table[pi] : -1;
+        int page = (lane * box_rows < BK && pi < max_pages) ? table[pi] : -1;
+        if (page >= 0 && !MG_GUARDED(attention_prefill, MG_GUARD_PAGE, page, num_pages)) page = -1;
         return (page * n_kv_head + kv_head) * page_tokens + (pos % page_tokens);
     };
     // The work list, positions and block tables are inputs of the step: the loading warp looks up
@@ -485,14 +497,15 @@ MG_API long long mg_attention_prefill_scratch_floats(int n_items, int n_head) {
 // (merge != 0), `partial` holds mg_attention_prefill_scratch_floats() floats and `counters`
 // n_items * n_head ints that are zero before the call and zero again after it.
 // qkv: [n_tokens, (n_head + 2 n_kv_head) * 64] bf16; pages: [num_pages, n_kv_head, page_tokens, 64];
-// out: [n_tokens, n_head * 64].  Returns MG_ERR_UNSUPPORTED unless head_dim is 64 and page_tokens
+// out: [n_tokens, n_head * 64]; n_requests: rows of the block table (guarded builds hold the work
+// items' request numbers against it).  Returns MG_ERR_UNSUPPORTED unless head_dim is 64 and page_tokens
 // is 8, 16, 32, 64, 128 or a multiple of 128.
 MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const void* v_pages, const int* work,
                                    const int* block_table, const int* positions, void* out, float* partial,
                                    int* counters, int merge, int n_items,
                                    int n_tokens, int n_head, int n_kv_head, int head_dim, int page_tokens,
-                                   long long num_pages, int max_pages, int window, float scale, int* status,
-                                   void* stream) {
+                                   long long num_pages, int max_pages, int window, float scale, int n_requests,
+                                   int* status, void* stream) {
     if (n_items == 0) return MG_OK;
     MG_REQUIRE(n_items > 0 && n_tokens > 0 && n_head > 0 && n_kv_head > 0 && page_tokens > 0 && max_pages > 0 && status,
                "attention (prefill): bad arguments");
@@ -522,7 +535,8 @@ MG_API int mg_attention_prefill_tc(const void* qkv, const void* k_pages, const v
     dim3 grid(n_items, n_head);
     cudaError_t le = mg_launch(attention_prefill_tc_kernel, grid, dim3(THREADS), smem, (cudaStream_t)stream, true, map_q,
                                map_k, map_v, work, block_table, positions, (bf16*)out, partial, counters, n_head, n_kv_head,
-                               page_tokens, box_rows, max_pages, window, scale * 1.4426950408889634f, status);
+                               page_tokens, box_rows, max_pages, window, scale * 1.4426950408889634f, status, n_tokens,
+                               (int)num_pages, n_requests);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "attention_prefill_tc: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("attention_prefill_tc");
     return MG_OK;

@@ -199,6 +199,62 @@ static inline cudaError_t mg_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
+// ---- index guards (guarded builds only) ------------------------------------------------------------
+// Token ids, positions, cache rows, page numbers and request numbers reach the kernels through device
+// memory; the host checks them before every launch, and ordinary builds trust it.  With -DMG_GUARDS
+// the kernels check them again where they use them: MG_GUARDED(name, code, value, limit) is true if
+// 0 <= value < limit; else it records the first such fault of the kernel file (code, value, limit,
+// block) and is false, and the caller skips the access or takes index 0 instead, so that a guarded
+// build never reads or writes outside a table.  mg_<name>_index_fault() hands the record to the host
+// and clears it.  In ordinary builds the macro is the constant true, the limits are unused
+// parameters, and the exported reader reports nothing.
+#define MG_GUARD_TOKEN 1        // token id >= vocabulary
+#define MG_GUARD_POSITION 2     // position beyond the position table or the block table
+#define MG_GUARD_CACHE_ROW 3    // cache row (page * page size + offset) beyond the pool
+#define MG_GUARD_PAGE 4         // page number beyond the pool
+#define MG_GUARD_REQUEST 5      // request number beyond the block tables' rows
+#define MG_GUARD_ROW 6          // row index beyond the tensor gathered from
+#define MG_GUARD_SOURCE 7       // index into the ids of the step before
+#ifdef MG_GUARDS
+struct MgIndexFault {
+    int code;
+    int block;
+    long long value;
+    long long limit;
+};
+__device__ __forceinline__ bool mg_guarded(MgIndexFault* fault, int code, long long value, long long limit) {
+    if (value >= 0 && value < limit) return true;
+    if (atomicCAS(&fault->code, 0, code) == 0) {
+        fault->block = (int)blockIdx.x;
+        fault->value = value;
+        fault->limit = limit;
+    }
+    return false;
+}
+#define MG_GUARD_RECORD(var) static __device__ MgIndexFault var;
+#define MG_GUARD_EXPORT(name, var)                                                                  \
+    MG_API int mg_##name##_index_fault(long long* host) {                                           \
+        MgIndexFault f, none = {0, 0, 0, 0};                                                        \
+        if (cudaMemcpyFromSymbol(&f, var, sizeof(f)) != cudaSuccess ||                              \
+            cudaMemcpyToSymbol(var, &none, sizeof(none)) != cudaSuccess)                            \
+            return mg_set_error(MG_ERR_CUDA, "cannot read the index guard of " #name);              \
+        host[0] = f.code; host[1] = f.block; host[2] = f.value; host[3] = f.limit;                  \
+        return MG_OK;                                                                               \
+    }
+#define MG_GUARDED_IN(var, code, value, limit) mg_guarded(&var, (code), (long long)(value), (long long)(limit))
+#else
+#define MG_GUARD_RECORD(var)
+#define MG_GUARD_EXPORT(name, var)                                                                  \
+    MG_API int mg_##name##_index_fault(long long* host) {                                           \
+        host[0] = host[1] = host[2] = host[3] = 0;                                                  \
+        return MG_OK;                                                                               \
+    }
+#define MG_GUARDED_IN(var, code, value, limit) (true)
+#endif
+// a kernel file's own record and its reader, and the check against it
+#define MG_GUARD_DECLARE(name) MG_GUARD_RECORD(name##_index_fault) MG_GUARD_EXPORT(name, name##_index_fault)
+#define MG_GUARDED(name, code, value, limit) MG_GUARDED_IN(name##_index_fault, code, value, limit)
+
 // ---- phase stamps (tracing builds only) ----------------------------------------------------------
 // With -DMG_STAMPS a kernel file keeps a small device array of clock readings: thread 0 of each CTA
 // records, at MG_STAMP(name, 0), the global nanosecond timer (one clock for all SMs and kernels) in

@@ -1,6 +1,8 @@
 // Row-wise kernels: embedding with position add, LayerNorm, row gather, KV page write.
 #include "common.cuh"
 
+MG_GUARD_DECLARE(elementwise)
+
 // ---- embedding + learned position add ---------------------------------------------------
 // x[n, :] = tok_emb[id[n], :] + pos_emb[pos[n], :]   (32-bit out; pos_emb may be null)
 // A row with a negative position is padding of a fixed-size batch: it becomes zeros.
@@ -10,20 +12,24 @@ template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict__ pos,
                              const TW* __restrict__ tok, const TW* __restrict__ ptab,
                              float* __restrict__ out, int width, const int* __restrict__ source,
-                             const int* __restrict__ previous) {
+                             const int* __restrict__ previous, int vocab, int n_positions, int n_previous) {
     const int n = blockIdx.x;
     float* orow = out + (size_t)n * width;
-    if (pos[n] < 0) {
+    int p = pos[n];
+    if (p < 0) {
         for (int c = threadIdx.x; c < width; c += blockDim.x) orow[c] = 0.f;
         return;
     }
     int id = ids[n];
     if (source != nullptr) {
         const int src = source[n];
-        if (src >= 0) id = previous[src];
+        if (src >= 0 && MG_GUARDED(elementwise, MG_GUARD_SOURCE, src, n_previous)) id = previous[src];
     }
+    // (guarded builds: an index out of range is recorded and row 0 is read in its place)
+    if (!MG_GUARDED(elementwise, MG_GUARD_TOKEN, id, vocab)) id = 0;
+    if (ptab != nullptr && !MG_GUARDED(elementwise, MG_GUARD_POSITION, p, n_positions)) p = 0;
     const TW* trow = tok + (size_t)id * width;
-    const TW* prow = ptab ? ptab + (size_t)pos[n] * width : nullptr;
+    const TW* prow = ptab ? ptab + (size_t)p * width : nullptr;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float v = to_float(trow[c]);
         if (prow) v += to_float(prow[c]);
@@ -31,19 +37,22 @@ __global__ void embed_kernel(const int* __restrict__ ids, const int* __restrict_
     }
 }
 
+// vocab, n_positions: rows of tok and ptab; n_previous: ids that `previous` holds (what the indices
+// are held against in guarded builds).
 MG_API int mg_embed(const int* ids, const int* pos, const void* tok, const void* ptab, float* out,
-                    int n_tokens, int width, int weights_bf16, const int* source, const int* previous, void* stream) {
+                    int n_tokens, int width, int weights_bf16, const int* source, const int* previous,
+                    int vocab, int n_positions, int n_previous, void* stream) {
     if (n_tokens == 0) return MG_OK;
-    MG_REQUIRE(n_tokens > 0 && width > 0, "embed: bad sizes");
+    MG_REQUIRE(n_tokens > 0 && width > 0 && vocab > 0, "embed: bad sizes");
     MG_REQUIRE(source == nullptr || previous != nullptr, "embed: token sources without the ids they point to");
     cudaStream_t s = (cudaStream_t)stream;
     int threads = width >= 256 ? 256 : 128;
     if (weights_bf16)
         embed_kernel<bf16><<<n_tokens, threads, 0, s>>>(ids, pos, (const bf16*)tok, (const bf16*)ptab, out, width, source,
-                                                       previous);
+                                                       previous, vocab, n_positions, n_previous);
     else
         embed_kernel<float><<<n_tokens, threads, 0, s>>>(ids, pos, (const float*)tok, (const float*)ptab, out, width,
-                                                        source, previous);
+                                                        source, previous, vocab, n_positions, n_previous);
     MG_CHECK_LAUNCH("embed");
     return MG_OK;
 }
@@ -138,17 +147,19 @@ MG_API int mg_layernorm(const float* x, const float* gain, const float* shift, v
 
 // ---- row gather (32-bit) ----------------------------------------------------------------------
 __global__ void gather_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
-                                   float* __restrict__ out, int width) {
-    const float* src = x + (size_t)rows[blockIdx.x] * width;
+                                   float* __restrict__ out, int width, int x_rows) {
+    int row = rows[blockIdx.x];
+    if (!MG_GUARDED(elementwise, MG_GUARD_ROW, row, x_rows)) row = 0;
+    const float* src = x + (size_t)row * width;
     float* dst = out + (size_t)blockIdx.x * width;
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
 }
 
-MG_API int mg_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width,
+MG_API int mg_gather_rows(const float* x, const int* rows, float* out, int n_rows, int width, int x_rows,
                           void* stream) {
     if (n_rows == 0) return MG_OK;
-    MG_REQUIRE(n_rows > 0 && width > 0, "gather_rows: bad sizes");
-    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>(x, rows, out, width);
+    MG_REQUIRE(n_rows > 0 && width > 0 && x_rows > 0, "gather_rows: bad sizes");
+    gather_rows_kernel<<<n_rows, 128, 0, (cudaStream_t)stream>>>(x, rows, out, width, x_rows);
     MG_CHECK_LAUNCH("gather_rows");
     return MG_OK;
 }
@@ -159,12 +170,13 @@ MG_API int mg_gather_rows(const float* x, const int* rows, float* out, int n_row
 template <typename T>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, const int* __restrict__ slots,
                                 T* __restrict__ k_pages, T* __restrict__ v_pages, int qkv_width,
-                                int q_width, int n_kv_head, int head_dim, int page_tokens) {
+                                int q_width, int n_kv_head, int head_dim, int page_tokens, int num_pages) {
     const int n = blockIdx.x;
     const int slot = slots[n];
     pdl_trigger();
     pdl_wait();                                        // qkv comes from the kernel in front
     if (slot < 0) return;
+    if (!MG_GUARDED(elementwise, MG_GUARD_CACHE_ROW, slot, (long long)num_pages * page_tokens)) return;
     const int page = slot / page_tokens, off = slot - page * page_tokens;
     const int kv_width = n_kv_head * head_dim;
     const T* krow = qkv + (size_t)n * qkv_width + q_width;
@@ -178,7 +190,7 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, const int* __restrict
 }
 
 MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v_pages, int n_tokens,
-                       int n_head, int n_kv_head, int head_dim, int page_tokens, int is_bf16,
+                       int n_head, int n_kv_head, int head_dim, int page_tokens, int num_pages, int is_bf16,
                        void* stream) {
     if (n_tokens == 0) return MG_OK;
     MG_REQUIRE(n_tokens > 0 && n_head > 0 && n_kv_head > 0 && head_dim > 0 && page_tokens > 0,
@@ -187,9 +199,9 @@ MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v
     const int q_width = n_head * head_dim, qkv_width = (n_head + 2 * n_kv_head) * head_dim;
     const cudaError_t le =
         is_bf16 ? mg_launch(kv_store_kernel<bf16>, dim3(n_tokens), dim3(128), 0, s, true, (const bf16*)qkv, slots, (bf16*)k_pages,
-                            (bf16*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens)
+                            (bf16*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens, num_pages)
                 : mg_launch(kv_store_kernel<float>, dim3(n_tokens), dim3(128), 0, s, true, (const float*)qkv, slots,
-                            (float*)k_pages, (float*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens);
+                            (float*)k_pages, (float*)v_pages, qkv_width, q_width, n_kv_head, head_dim, page_tokens, num_pages);
     if (le != cudaSuccess) return mg_set_error(MG_ERR_CUDA, "kv_store: %s", cudaGetErrorString(le));
     MG_CHECK_LAUNCH("kv_store");
     return MG_OK;
@@ -198,15 +210,17 @@ MG_API int mg_kv_store(const void* qkv, const int* slots, void* k_pages, void* v
 // ---- feed sampled tokens back without a trip to the host -------------------------------------------
 // token_ids[i] = previous[source[i]] where source[i] >= 0; other rows keep what the host wrote.
 __global__ void gather_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ source,
-                                     const int* __restrict__ previous, int n) {
+                                     const int* __restrict__ previous, int n, int n_previous) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n && source[i] >= 0) token_ids[i] = previous[source[i]];
+    if (i < n && source[i] >= 0 && MG_GUARDED(elementwise, MG_GUARD_SOURCE, source[i], n_previous))
+        token_ids[i] = previous[source[i]];
 }
 
-MG_API int mg_gather_tokens(int* token_ids, const int* source, const int* previous, int n, void* stream) {
+MG_API int mg_gather_tokens(int* token_ids, const int* source, const int* previous, int n, int n_previous,
+                            void* stream) {
     if (n == 0) return MG_OK;
     MG_REQUIRE(n > 0 && token_ids && source && previous, "gather_tokens: bad arguments");
-    gather_tokens_kernel<<<ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(token_ids, source, previous, n);
+    gather_tokens_kernel<<<ceil_div(n, 128), 128, 0, (cudaStream_t)stream>>>(token_ids, source, previous, n, n_previous);
     MG_CHECK_LAUNCH("gather_tokens");
     return MG_OK;
 }

@@ -33,6 +33,7 @@
 #include "tensor_map.cuh"
 
 MG_STAMP_DECLARE(gemm)
+MG_GUARD_DECLARE(linear_tc)
 
 #define EPI_STORE 0
 #define EPI_GELU 1
@@ -61,6 +62,7 @@ struct KvSink {
     bf16* v_pages;
     const int* slots;                // [tokens] flat cache row, < 0: skip
     int q_width, n_kv_head, head_dim, page_tokens;
+    int num_pages;                   // pages of the pool (what a cache row is held against in guarded builds)
 };
 
 // First element of feature n (>= q_width) of the token in cache row `slot`; *is_value says which array.
@@ -97,6 +99,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     int cache_row = -1;                                   // of this thread's token (not SWAP)
     if (!SWAP) {
         if (sink.k_pages != nullptr && p0 + tid < rows_p) cache_row = sink.slots[p0 + tid];
+        // (guarded builds: a row beyond the pool is recorded and its keys and values are not copied)
+        if (cache_row >= 0 && !MG_GUARDED(linear_tc, MG_GUARD_CACHE_ROW, cache_row, (long long)sink.num_pages * sink.page_tokens))
+            cache_row = -1;
         for (int j = tid; j < BN; j += 128) bias_tile[j] = (bias && q0 + j < rows_q) ? bias[q0 + j] : 0.f;
         if (epilogue == EPI_RESIDUAL && p0 + tid < rows_p) {
             const float* rrow = residual + (size_t)(p0 + tid) * ld_out + q0;
@@ -406,7 +411,8 @@ int launch(const void* p, const void* q, int rows_p, int rows_q, int K, const fl
 // K not a multiple of 8, pointers not 16-byte aligned.
 MG_API int mg_linear_tc(const void* x, const void* w, const float* bias, void* out, float* residual, int M,
                         int N, int K, int epilogue, int out_bf16, void* k_pages, void* v_pages, const int* slots,
-                        int q_width, int n_kv_head, int head_dim, int page_tokens, int* status, void* stream) {
+                        int q_width, int n_kv_head, int head_dim, int page_tokens, int num_pages, int* status,
+                        void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
@@ -420,7 +426,7 @@ MG_API int mg_linear_tc(const void* x, const void* w, const float* bias, void* o
         MG_REQUIRE(head_dim > 0 && head_dim % 8 == 0 && q_width % 8 == 0 && n_kv_head > 0 && page_tokens > 0 &&
                        q_width + 2 * n_kv_head * head_dim == N,
                    "linear: key/value copy with q_width=%d n_kv_head=%d head_dim=%d N=%d", q_width, n_kv_head, head_dim, N);
-        sink = KvSink{(bf16*)k_pages, (bf16*)v_pages, slots, q_width, n_kv_head, head_dim, page_tokens};
+        sink = KvSink{(bf16*)k_pages, (bf16*)v_pages, slots, q_width, n_kv_head, head_dim, page_tokens, num_pages};
     }
     if (M <= 64 && k_pages == nullptr) {
         // few tokens: weight rows fill the 128-row side of the tile, the batch sits on the narrow side

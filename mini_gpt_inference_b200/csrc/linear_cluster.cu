@@ -199,12 +199,14 @@ __global__ void __launch_bounds__(THREADS, 2) linear_cluster_kernel(const Cluste
 // Largest M this kernel takes.
 MG_API int mg_linear_cluster_max_rows() { return MAX_M; }
 
+MG_GUARD_EXPORT(linear_cluster, linear_index_fault)
+
 // x: [M, K] bf16; w: [N, K] bf16; epilogues and the key/value sink as mg_linear_skinny.
 // Returns MG_ERR_UNSUPPORTED (nothing launched) for M > 128, K % 8 != 0, operands that are not
 // 16-byte aligned or a slice of activations beyond the shared memory.
 MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, void* out, float* residual, int M, int N,
                              int K, int epilogue, int out_bf16, void* k_pages, void* v_pages, const int* slots,
-                             int q_width, int n_kv_head, int head_dim, int page_tokens, void* stream) {
+                             int q_width, int n_kv_head, int head_dim, int page_tokens, int num_pages, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0 && x != nullptr && w != nullptr, "linear: bad arguments M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(epilogue == EPI_RESIDUAL ? residual != nullptr : out != nullptr, "linear: missing output");
@@ -230,7 +232,7 @@ MG_API int mg_linear_cluster(const void* x, const void* w, const float* bias, vo
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
-    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens; a.ep.num_pages = num_pages;
     void (*kernel)(const ClusterArgs) = nullptr;
     if (ntw == 2) kernel = mg == 2 ? linear_cluster_kernel<2, 2> : linear_cluster_kernel<4, 2>;
     else kernel = mg == 2 ? linear_cluster_kernel<2, 1> : mg == 4 ? linear_cluster_kernel<4, 1>

@@ -19,7 +19,11 @@ struct LinearEpilogue {
     bf16* v_pages;
     const int* slots;                // [M] flat cache row of each token, < 0: skip
     int q_width, n_kv_head, head_dim, page_tokens;
+    int num_pages;                   // pages of the pool (what a cache row is held against in guarded builds)
 };
+
+// the fault record of the file that includes this (each exports its own reader)
+MG_GUARD_RECORD(linear_index_fault)
 
 // v: the sum with its bias.  `res` is the residual value if the caller fetched it already, `slot`
 // the token's cache row if it did (pass have_slot = false to have it read here).
@@ -34,7 +38,7 @@ __device__ __forceinline__ void linear_finish(const LinearEpilogue& e, int m, in
         reinterpret_cast<bf16*>(e.out)[idx] = hv;
         if (e.k_pages != nullptr && n >= e.q_width) {
             const int slot = have_slot ? slot_in : e.slots[m];
-            if (slot >= 0) {
+            if (slot >= 0 && MG_GUARDED_IN(linear_index_fault, MG_GUARD_CACHE_ROW, slot, (long long)e.num_pages * e.page_tokens)) {
                 const int kv_width = e.n_kv_head * e.head_dim;
                 const int f = n - e.q_width;
                 const int which = f / kv_width, fi = f - which * kv_width;

@@ -336,6 +336,8 @@ static size_t skinny_smem(int mt, int K) {
            (size_t)2 * WARPS * mt * sizeof(float);
 }
 
+MG_GUARD_EXPORT(linear_skinny, linear_index_fault)
+
 // x: [M, K] bf16 (or null when x32 is given: then rows row_index[m] (or m) of x32 [*, K] are
 // LayerNorm-ed with gain/shift/eps first).  w: [N, K] bf16.  Epilogues as mg_linear_simt.
 // With k_pages given (QKV projection, bf16 out), features >= q_width also go to the cache rows
@@ -344,7 +346,7 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
                             const float* shift, float eps, const void* w, const float* bias, void* out,
                             float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
                             void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
-                            int page_tokens, float* amax_v, int* amax_i, int amax_limit, void* stream) {
+                            int page_tokens, int num_pages, float* amax_v, int* amax_i, int amax_limit, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
     MG_REQUIRE(x != nullptr || (x32 != nullptr && gain != nullptr), "linear: missing input");
@@ -363,7 +365,7 @@ MG_API int mg_linear_skinny(const void* x, const float* x32, const int* row_inde
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
-    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens; a.ep.num_pages = num_pages;
     MG_REQUIRE(amax_v == nullptr || (amax_i != nullptr && epilogue == EPI_STORE && !out_bf16),
                "linear: the greedy choice goes with 32-bit stored outputs");
     a.amax_v = amax_v; a.amax_i = amax_i; a.amax_limit = (amax_limit <= 0 || amax_limit > N) ? N : amax_limit;

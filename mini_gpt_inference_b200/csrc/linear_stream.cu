@@ -322,6 +322,8 @@ MG_API int mg_linear_stream_parts(int N) {
     return stream_split(N, sms, &per) * WARPS;
 }
 
+MG_GUARD_EXPORT(linear_stream, linear_index_fault)
+
 // As mg_linear_skinny (same operands, prologue, epilogues and greedy choice), for wide matrices.
 // A stage holds a tile's rows whole where two such stages per warp fit beside the activations;
 // longer rows are cut into K chunks (four stages per warp), a tile's sums staying in registers from
@@ -333,7 +335,7 @@ MG_API int mg_linear_stream(const void* x, const float* x32, const int* row_inde
                             const float* shift, float eps, const void* w, const float* bias, void* out,
                             float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
                             void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
-                            int page_tokens, float* amax_v, int* amax_i, int amax_limit, int max_chunks,
+                            int page_tokens, int num_pages, float* amax_v, int* amax_i, int amax_limit, int max_chunks,
                             int* status, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0 && status != nullptr, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -368,7 +370,7 @@ MG_API int mg_linear_stream(const void* x, const float* x32, const int* row_inde
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
-    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens; a.ep.num_pages = num_pages;
     a.amax_v = amax_v; a.amax_i = amax_i; a.amax_limit = (amax_limit <= 0 || amax_limit > N) ? N : amax_limit;
     a.status = status;
     a.stages = stages;

@@ -716,6 +716,8 @@ MG_API int mg_linear_wide_parts(int M, int N, int K, int prologue) {
     return p.ok ? p.groups * p.k_slices * (p.solo ? CONSUMERS : FINISHERS) : 0;
 }
 
+MG_GUARD_EXPORT(linear_wide, linear_index_fault)
+
 // As mg_linear_skinny (same operands, prologue, epilogues and greedy choice), for matrices of many
 // megabytes and up to 16 tokens.  next_w / next_lines: optionally the start and the size (in 128-byte
 // lines) of memory that the caller expects to be read next (the weights of the projection behind this
@@ -728,7 +730,7 @@ MG_API int mg_linear_wide(const void* x, const float* x32, const int* row_index,
                           const float* shift, float eps, const void* w, const float* bias, void* out,
                           float* residual, int M, int N, int K, int epilogue, int out_bf16, void* k_pages,
                           void* v_pages, const int* slots, int q_width, int n_kv_head, int head_dim,
-                          int page_tokens, float* amax_v, int* amax_i, int amax_limit, const void* next_w,
+                          int page_tokens, int num_pages, float* amax_v, int* amax_i, int amax_limit, const void* next_w,
                           int next_lines, int* status, void* stream) {
     if (M == 0) return MG_OK;
     MG_REQUIRE(M > 0 && N > 0 && K > 0 && status != nullptr, "linear: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -754,7 +756,7 @@ MG_API int mg_linear_wide(const void* x, const float* x32, const int* row_index,
     a.ep.bias = bias; a.ep.out = out; a.ep.residual = residual; a.ep.M = M; a.ep.N = N;
     a.ep.epilogue = epilogue; a.ep.out_bf16 = out_bf16;
     a.ep.k_pages = (bf16*)k_pages; a.ep.v_pages = (bf16*)v_pages; a.ep.slots = slots;
-    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens;
+    a.ep.q_width = q_width; a.ep.n_kv_head = n_kv_head; a.ep.head_dim = head_dim; a.ep.page_tokens = page_tokens; a.ep.num_pages = num_pages;
     a.k_slices = p.k_slices; a.slice_k = p.slice_k; a.groups = p.groups; a.row_boxes = p.row_boxes;
     a.box_blocks = p.box_blocks; a.stages = p.stages; a.warps = p.warps;
     a.early = (int)(EARLY_BYTES / ((size_t)p.box_rows * p.box_blocks * 128));

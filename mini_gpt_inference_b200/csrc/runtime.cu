@@ -40,3 +40,12 @@ MG_API int mg_set_dependent_launch(int on) {
     g_dependent_launch = on ? 1 : 0;
     return MG_OK;
 }
+
+// Whether the kernels of this build check the indices they read from device memory (-DMG_GUARDS).
+MG_API int mg_guards_enabled() {
+#ifdef MG_GUARDS
+    return 1;
+#else
+    return 0;
+#endif
+}

@@ -29,6 +29,11 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]
 STAMPS = os.environ.get("MINIGPT_B200_STAMPS", "") not in ("", "0")
 if STAMPS:
     NVCC_FLAGS = NVCC_FLAGS + ["-DMG_STAMPS"] + os.environ.get("MINIGPT_B200_STAMPS_FLAGS", "").split()
+# MINIGPT_B200_GUARDS=1 builds a guarded variant (in a folder of its own) whose kernels check every
+# index they read from device memory before they use it (MG_GUARDED in common.cuh).
+GUARDS = os.environ.get("MINIGPT_B200_GUARDS", "") not in ("", "0")
+if GUARDS:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DMG_GUARDS"]
 
 
 class BuildError(RuntimeError):
@@ -57,7 +62,7 @@ def _stamp() -> str:
 
 
 def _build_dir() -> Path:
-    d = CSRC / ("_build_stamps" if STAMPS else "_build")
+    d = CSRC / ("_build" + ("_stamps" if STAMPS else "") + ("_guards" if GUARDS else ""))
     try:
         d.mkdir(parents=True, exist_ok=True)
         probe = d / f".write_probe_{os.getpid()}"

@@ -20,29 +20,30 @@ _SIGNATURES = {
     "mg_device_arch": [_I],
     "mg_set_device": [_I],
     "mg_set_dependent_launch": [_I],
-    "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _P],
+    "mg_guards_enabled": [],
+    "mg_embed": [_P, _P, _P, _P, _P, _I, _I, _I, _P, _P, _I, _I, _I, _P],
     "mg_layernorm": [_P, _P, _P, _P, _I, _I, _F, _I, _P],
-    "mg_gather_rows": [_P, _P, _P, _I, _I, _P],
-    "mg_gather_tokens": [_P, _P, _P, _I, _P],
-    "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "mg_gather_rows": [_P, _P, _P, _I, _I, _I, _P],
+    "mg_gather_tokens": [_P, _P, _P, _I, _I, _P],
+    "mg_kv_store": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_simt": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     "mg_linear_skinny": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
-                         _I, _I, _I, _I, _P, _P, _I, _P],
+                         _I, _I, _I, _I, _I, _P, _P, _I, _P],
     "mg_linear_skinny_ctas": [_I, _I],
     "mg_linear_stream": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
-                         _I, _I, _I, _I, _P, _P, _I, _I, _P, _P],
+                         _I, _I, _I, _I, _I, _P, _P, _I, _I, _P, _P],
     "mg_linear_stream_parts": [_I],
     "mg_linear_wide": [_P, _P, _P, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P,
-                       _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P],
+                       _I, _I, _I, _I, _I, _P, _P, _I, _P, _I, _P, _P],
     "mg_linear_wide_parts": [_I, _I, _I, _I],
     "mg_argmax_merge": [_P, _P, _P, _I, _I, _P],
-    "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
-    "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P, _P],
-    "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _P],
+    "mg_linear_cluster": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "mg_linear_tc": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    "mg_paged_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _I, _P],
     "mg_paged_attention_split": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I,
-                                 _F, _P, _P],
+                                 _F, _I, _I, _P, _P],
     "mg_attention_prefill_tc": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I,
-                                ctypes.c_longlong, _I, _I, _F, _P, _P],
+                                ctypes.c_longlong, _I, _I, _F, _I, _P, _P],
     "mg_copy_ints": [_P, _P, _I, _P],
     "mg_argmax": [_P, _P, _I, _I, _I, _P],
     "mg_argmax_wide": [_P, _P, _P, _P, _I, _I, _I, _P],
@@ -53,6 +54,13 @@ _SIGNATURES = {
     "mg_sample": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
 }
 
+
+# exported readers of the kernel files' index guards: mg_<name>_index_fault(long long[4])
+GUARDED_FILES = ("elementwise", "linear_skinny", "linear_stream", "linear_wide", "linear_cluster", "linear_tc",
+                 "attention_generic", "attention_split", "attention_prefill")
+for _name in GUARDED_FILES:
+    _SIGNATURES[f"mg_{_name}_index_fault"] = [_P]
+GUARD_CODES = {1: "token id", 2: "position", 3: "cache row", 4: "page", 5: "request", 6: "row", 7: "token source"}
 
 UNSUPPORTED = -3     # a kernel refused the sizes; the caller may take another path
 

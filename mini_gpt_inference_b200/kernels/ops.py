@@ -8,6 +8,7 @@ computes anything on this path.
 
 from __future__ import annotations
 
+import ctypes
 import weakref
 
 import torch
@@ -70,6 +71,8 @@ class CudaOps:
                 "are built for sm_100a (NVIDIA B200) only")
         check(self.lib.mg_set_device(self.index), "set device")
         self.launches = 0          # kernels launched through this object
+        # a guarded build (MINIGPT_B200_GUARDS=1): the kernels check the indices they read from device memory
+        self.guards = bool(self.lib.mg_guards_enabled())
         # Kernels with bounded waits record a non-zero code here if a wait ran out.
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.use_tensor_cores = True
@@ -160,8 +163,28 @@ class CudaOps:
         check(self.lib.mg_set_dependent_launch(1 if (on and self.use_dependent_launch) else 0),
               "set_dependent_launch")
 
+    def check_indices(self) -> None:
+        """Guarded builds: raise if a kernel met a token id, position, cache row, page, request or row
+        number outside its table since the last call (synchronises; the kernel skipped the access
+        or read index 0 in its place, so the results of that step are invalid but no memory
+        outside a table was touched).  Ordinary builds: nothing to ask."""
+        if not self.guards:
+            return
+        torch.cuda.synchronize(self.device)
+        record = (ctypes.c_longlong * 4)()
+        faults = []
+        for name in library.GUARDED_FILES:
+            check(getattr(self.lib, f"mg_{name}_index_fault")(record), "index guard")
+            if record[0]:
+                what = library.GUARD_CODES.get(int(record[0]), f"index (code {record[0]})")
+                faults.append(f"{name}: {what} {record[2]} is outside 0..{record[3] - 1} (block {record[1]})")
+        if faults:
+            raise KernelLibraryError("a kernel met an index outside its table: " + "; ".join(faults))
+
     def check_status(self) -> None:
-        """Raise if a kernel reported that one of its bounded waits ran out (synchronises)."""
+        """Raise if a kernel reported that one of its bounded waits ran out (synchronises); in a
+        guarded build also if one met an index outside its table."""
+        self.check_indices()
         code = int(self.status.item())
         if code != 0:
             self.status.zero_()
@@ -183,6 +206,7 @@ class CudaOps:
         return pinned
 
     def raise_on_status(self, pinned) -> None:
+        self.check_indices()
         code = int(pinned[0])
         if code != 0:
             self.status.zero_()
@@ -208,7 +232,8 @@ class CudaOps:
         out = torch.empty((n, width), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_embed(_ptr(token_ids), _ptr(positions), _ptr(tok_emb), _ptr(pos_table),
                                 _ptr(out), n, width, self._is_bf16(tok_emb), _ptr(source), _ptr(previous),
-                                self._stream()),
+                                tok_emb.shape[0], pos_table.shape[0] if pos_table is not None else 0,
+                                previous.numel() if previous is not None else 0, self._stream()),
               "embed")
         return out
 
@@ -230,7 +255,7 @@ class CudaOps:
         self._want(rows, torch.int32, "rows", 1)
         out = torch.empty((rows.numel(), x32.shape[1]), dtype=torch.float32, device=self.device)
         self._run(self.lib.mg_gather_rows(_ptr(x32), _ptr(rows), _ptr(out), rows.numel(), x32.shape[1],
-                                      self._stream()), "gather_rows")
+                                      x32.shape[0], self._stream()), "gather_rows")
         return out
 
     def gather_tokens(self, token_ids, source, previous):
@@ -239,7 +264,7 @@ class CudaOps:
         for name, t in (("token_ids", token_ids), ("source", source), ("previous", previous)):
             self._want(t, torch.int32, name, 1)
         self._run(self.lib.mg_gather_tokens(_ptr(token_ids), _ptr(source), _ptr(previous),
-                                            token_ids.numel(), self._stream()), "gather_tokens")
+                                            token_ids.numel(), previous.numel(), self._stream()), "gather_tokens")
 
     def upload_ints(self, dst, pinned) -> None:
         """dst[:] = pinned[:] where ``pinned`` is page-locked host memory: the device reads it
@@ -264,10 +289,10 @@ class CudaOps:
     def _sink_args(kv_sink):
         """The key/value sink of a QKV projection as the C functions take it."""
         if kv_sink is None:
-            return [None, None, None, 0, 0, 0, 0]
+            return [None, None, None, 0, 0, 0, 0, 0]
         cache, slots, n_head, n_kv_head, head_dim = kv_sink
         return [_ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(slots), n_head * head_dim, n_kv_head,
-                head_dim, cache.page_tokens]
+                head_dim, cache.page_tokens, cache.k_pages.shape[0]]
 
     def _linear(self, x, weight, bias, epilogue, out, residual, kv_sink=None, greedy=None):
         """x: a tensor [M, K] or a DeferredNorm.  kv_sink: (cache view, slots, n_head, n_kv_head,
@@ -526,7 +551,8 @@ class CudaOps:
             raise KernelLibraryError("kv_store: page storage does not match the head sizes")
         self._run(self.lib.mg_kv_store(_ptr(qkv), _ptr(slot_mapping), _ptr(cache.k_pages),
                                    _ptr(cache.v_pages), qkv.shape[0], n_head, n_kv_head, head_dim,
-                                   cache.page_tokens, self._is_bf16(qkv), self._stream()), "kv_store")
+                                   cache.page_tokens, cache.k_pages.shape[0], self._is_bf16(qkv),
+                                   self._stream()), "kv_store")
 
     SPLIT_HEAD_DIMS = (16, 32, 64, 128, 256)
 
@@ -577,7 +603,8 @@ class CudaOps:
                 _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
                 _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), _ptr(scratch),
                 _ptr(self._counters(n * n_head)), n, n_head, n_kv_head, head_dim, cache.page_tokens,
-                table.shape[1], window, splits, float(scale), _ptr(self.status), self._stream()),
+                table.shape[1], window, splits, float(scale), cache.k_pages.shape[0], table.shape[0],
+                _ptr(self.status), self._stream()),
                 "paged_attention (split)")
             # a grid of several waves merges in a kernel of its own
             self.launches += self.lib.mg_attention_split_launches(n, n_head, n_kv_head, splits) - 1
@@ -600,14 +627,14 @@ class CudaOps:
                 _ptr(ctx.positions), _ptr(out), _ptr(partial), _ptr(counters), merge, work.shape[0], n, n_head,
                 n_kv_head, head_dim,
                 cache.page_tokens, cache.k_pages.shape[0], table.shape[1], window, float(scale),
-                _ptr(self.status), self._stream())
+                table.shape[0], _ptr(self.status), self._stream())
             if code != library.UNSUPPORTED:
                 self._run(code, "paged_attention (prefill, tensor cores)")
                 return out
         self._run(self.lib.mg_paged_attention_generic(
             _ptr(qkv), _ptr(cache.k_pages), _ptr(cache.v_pages), _ptr(table),
             _ptr(ctx.token_request), _ptr(ctx.positions), _ptr(out), n, n_head, n_kv_head, head_dim,
-            cache.page_tokens, table.shape[1], window, float(scale),
+            cache.page_tokens, table.shape[1], window, float(scale), cache.k_pages.shape[0], table.shape[0],
             self._is_bf16(qkv), self._stream()), "paged_attention")
         return out
 
