@@ -21,6 +21,7 @@ sys.path.insert(0, str(ROOT / "tests"))
 import torch  # noqa: E402
 
 from harness import PAGE_TOKENS, TOLERANCE, gpu_runner, make_tensors, plain_logits, tiny_config, tokens_for  # noqa: E402
+from mini_gpt_inference_b200.config import GPTConfig  # noqa: E402
 from mini_gpt_inference_b200.engine.runner import StepEntry  # noqa: E402
 from mini_gpt_inference_b200.kernels.library import KernelLibraryError  # noqa: E402
 from mini_gpt_inference_b200.kernels.ops import default_ops  # noqa: E402
@@ -39,17 +40,23 @@ def fault_of(run) -> str:
     return ""
 
 
+# head size 64: the bfloat16 step runs the tensor-core projections and the prompt attention on them
+HEAD64 = dict(vocab_size=1003, n_positions=700, n_layer=2, n_head=3, n_embd=192, n_inner=520, bias=True,
+              layer_norm_epsilon=1e-5)
+
+
 def engine_steps(tag: str) -> None:
     """A prompt in portions and some single tokens through the runner: right logits, quiet guards."""
-    for which, dtype in (("A", "bfloat16"), ("B", "float32")):
-        cfg = tiny_config(which)
+    for which, dtype in (("A", "bfloat16"), ("B", "float32"), ("H", "bfloat16")):
+        cfg = GPTConfig.from_dict(HEAD64) if which == "H" else tiny_config(which)
         tensors = make_tensors(cfg, 3, dtype, False)
-        runner = gpu_runner(cfg, tensors, dtype, PAGE_TOKENS[which], 64)
-        tokens = tokens_for(cfg, 45, 1)
+        runner = gpu_runner(cfg, tensors, dtype, 16 if which == "H" else PAGE_TOKENS[which], 64)
+        tokens = tokens_for(cfg, 300 if which == "H" else 45, 1)
         want = plain_logits(cfg, tensors, tokens)
-        got = [runner.step([StepEntry("r", tokens[:20], list(range(20)))]),
-               runner.step([StepEntry("r", tokens[20:33], list(range(13)))])]
-        for t in range(33, 45):
+        n, first = len(tokens), len(tokens) - 25
+        got = [runner.step([StepEntry("r", tokens[:first], list(range(first)))]),
+               runner.step([StepEntry("r", tokens[first: first + 13], list(range(13)))])]
+        for t in range(first + 13, n):
             got.append(runner.step([StepEntry("r", tokens[t: t + 1], [0])]))
         diff = float((torch.cat(got).double().cpu() - want.double()).abs().max())
         runner.finish("r")

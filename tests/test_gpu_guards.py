@@ -34,7 +34,7 @@ def test_guarded_build_catches_indices_outside_their_tables():
     assert seen["guards"] is True
     # the engine's own steps: right logits, quiet guards, before and after the faults below
     for tag in ("before", "after"):
-        for key in (f"{tag}_A_bfloat16", f"{tag}_B_float32"):
+        for key in (f"{tag}_A_bfloat16", f"{tag}_B_float32", f"{tag}_H_bfloat16"):
             assert seen[key]["diff"] <= seen[key]["tolerance"], (key, seen[key])
     # each bad index is named with its value and its limit; the access was skipped or replaced
     assert "token id 77 is outside 0..49" in seen["token"] and seen["token_row_replaced"]
