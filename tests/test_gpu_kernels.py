@@ -672,6 +672,29 @@ def test_split_attention_of_many_rows_merges_in_a_second_kernel(ops, n_head, n_k
     assert int(ops._counters(1).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_tokens,lengths,launches", [
+    (2, 2, 64, 64, [2049, 2200, 4097, 6000, 8191, 2176], 1),     # 17 to 64 blocks of 128 keys, merged by the last CTA
+    (4, 1, 64, 16, [9000, 3333], 1),                             # grouped heads, 71 and 27 blocks
+    (2, 2, 32, 64, [4400, 5000, 7000], 1),                       # blocks of 256 keys: 18 to 28
+    (2, 2, 128, 32, [1100, 1500, 2300], 1),                      # blocks of 64 keys: 18 to 36
+    (8, 8, 64, 64, [2100 + 37 * i for i in range(12)], 2)])      # 12 x 8 x 20 blocks: the second kernel merges
+def test_split_attention_with_many_key_blocks(ops, n_head, n_kv_head, head_dim, page_tokens, lengths, launches):
+    """Contexts of more than sixteen key blocks: the merge then shares a row's blocks among the four
+    warps of a CTA (quarters, added in warp order), inside the attention kernel or in the second one.
+    A spike far back in the longest request must still decide its row."""
+    block = ops.lib.mg_attention_split_keys(head_dim)
+    assert min(lengths) > 16 * block
+    longest = max(range(len(lengths)), key=lambda i: lengths[i])
+    for spike in (None, (longest, 5, 3.0)):
+        got, want = _attention_case(ops, torch.bfloat16, n_head, n_kv_head, head_dim, page_tokens, 0,
+                                    lengths, [1] * len(lengths), seed=21, spike=spike)
+        assert _attention_case.kernels == launches
+        ops.check_status()
+        assert not torch.isnan(got).any()
+        assert (got - want).abs().max() <= _tol(torch.bfloat16, 1.0)
+    assert int(ops._counters(1).abs().sum()) == 0
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_far_key_among_hundreds_decides(ops, dtype):
     """One key far back gets a score that dominates: the output must be that key's value."""
