@@ -193,11 +193,15 @@ def test_whole_feed_forward_in_one_kernel(ops, m, c, f, bias):
     ops.check_status()
 
 
-@pytest.mark.parametrize("m", [17, 24, 32, 33, 50, 64])
-@pytest.mark.parametrize("n,k", [(1536, 512), (512, 2048), (509, 96), (200, 200), (77, 40), (2048, 4096)])
+@pytest.mark.parametrize("m", [17, 24, 32, 33, 50, 64, 65, 96, 100, 128])
+@pytest.mark.parametrize("n,k", [(1536, 512), (512, 2048), (509, 96), (200, 200), (77, 40), (2048, 4096),
+                                 (6400, 1600), (4800, 1600), (5003, 520)])
 def test_mid_batch_projection_over_a_cluster(ops, m, n, k):
-    """17 to 64 tokens: K cut over the CTAs of a cluster, partial sums met through distributed
-    shared memory; every epilogue, against the formula and against the tensor-core kernel."""
+    """17 to 128 tokens: K cut over the CTAs of a cluster, partial sums met through distributed
+    shared memory; every epilogue, against the formula and against the tensor-core kernel.  The
+    matrices of 4800 rows and more make a warp take two tiles (up to 64 tokens); beyond 64 tokens
+    the kernel holds six or eight groups of 16 tokens and serves matrices of up to 3 MB (the larger
+    ones here then go to the tensor-core kernel, and the comparison holds all the same)."""
     x = randn(m, k, dtype=torch.bfloat16, seed=31)
     w = randn(n, k, dtype=torch.bfloat16, seed=32, scale=1 / math.sqrt(k))
     b = randn(n, seed=33)
