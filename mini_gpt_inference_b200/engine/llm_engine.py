@@ -90,6 +90,13 @@ class LLMEngine:
         return cls(loaded, engine_cfg, **kwargs)
 
     # ---- requests ---------------------------------------------------------------------------
+    def warm_up(self) -> dict:
+        """Optional, before the first request: capture the CUDA graphs of decode batches of every
+        size up to ``max_batch_size`` now instead of when such a batch first forms.  Nothing else
+        changes; an engine that is never warmed up captures each graph at its first use."""
+        made = self.runner.capture_decode_graphs(self.engine_cfg.max_batch_size)
+        return {"decode_graphs_captured": made}
+
     def add_request(self, request: Request) -> None:
         prompt_len = len(request.prompt_token_ids)
         if prompt_len == 0:

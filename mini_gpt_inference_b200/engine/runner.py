@@ -422,6 +422,22 @@ class ModelRunner:
         state.graph = graph
         return state
 
+    def capture_decode_graphs(self, max_rows: int) -> int:
+        """Capture now, rather than at their first use, the decode graphs of every row bucket that
+        batches of up to ``max_rows`` single tokens can meet (a capture runs the model twice on
+        padding rows and takes some ten milliseconds: with this the first requests do not pay for
+        it).  Returns the number of graphs captured; 0 where decode steps are not replayed."""
+        if not self.use_cuda_graphs or max_rows < 1:
+            return 0
+        made = 0
+        for rows in self.GRAPH_ROWS:
+            if rows not in self._graphs:
+                self._graphs[rows] = self._capture(rows)
+                made += 1
+            if rows >= max_rows:
+                break
+        return made
+
     def _fill_graph_inputs(self, state: _DecodeGraph, entries: Sequence[StepEntry],
                            token_sources=None) -> None:
         """The step's integers into the pinned staging buffer.  The block tables of a row are

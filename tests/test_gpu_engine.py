@@ -196,3 +196,27 @@ def test_batch_of_seven_with_portions_of_13_and_forced_preemption(dtype):
         assert_greedy(cfg, tensors, prompt, out["token_ids"], TOLERANCE[dtype])
     assert engine.stats()["allocated_blocks"] == 0
     engine.runner.manager.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_warm_up_captures_the_decode_graphs_ahead_and_changes_no_token(dtype):
+    """warm_up() captures the graphs of all decode batch sizes up to max_batch_size before the first
+    request; generation afterwards captures nothing more and gives the tokens of a cold engine."""
+    kw = dict(block_size=8, num_blocks=64, max_batch_size=6, max_num_batched_tokens=32)
+    cfg, tensors, cold = engine_for("A", dtype, **kw)
+    prompts = [tokens_for(cfg, n, 70 + i) for i, n in enumerate([9, 3, 14, 6, 11])]
+    params = SamplingParams(max_tokens=9, temperature=0.0)
+    want = [o["token_ids"] for o in cold.generate(prompts, params)]
+    _, _, warm = engine_for("A", dtype, **kw)
+    assert warm.warm_up() == {"decode_graphs_captured": 4}            # rows 1, 2, 4, 8
+    assert sorted(warm.runner._graphs) == [1, 2, 4, 8]
+    assert warm.warm_up() == {"decode_graphs_captured": 0}            # nothing left to do
+    assert warm.stats()["allocated_blocks"] == 0                      # padding rows hold no page
+    got = [o["token_ids"] for o in warm.generate(prompts, params)]
+    assert sorted(warm.runner._graphs) == [1, 2, 4, 8] and warm.runner.graph_replays > 0
+    if dtype == "float32":
+        assert got == want
+    for prompt, tokens in zip(prompts, got):
+        assert_greedy(cfg, tensors, prompt, tokens, TOLERANCE[dtype])
+    _, _, eager = engine_for("A", dtype, use_cuda_graphs=False, **kw)
+    assert eager.warm_up() == {"decode_graphs_captured": 0}
