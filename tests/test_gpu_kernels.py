@@ -86,7 +86,8 @@ def test_linear_and_epilogues(ops, dtype, m, n, k):
 def test_tensor_core_and_cuda_core_products_agree(ops):
     """The tcgen05 path and the plain FMA path compute the same sums from the same bfloat16
     inputs; with 32-bit output they differ only by the order of the additions."""
-    for m, n, k in [(5, 300, 512), (200, 136, 200), (64, 50304, 512), (1000, 1536, 512)]:
+    # (the last shape has enough tiles for the 128 x 256 variant of the tensor-core kernel)
+    for m, n, k in [(5, 300, 512), (200, 136, 200), (64, 50304, 512), (1000, 1536, 512), (4200, 4800, 328)]:
         x = randn(m, k, dtype=torch.bfloat16, seed=11)
         w = randn(n, k, dtype=torch.bfloat16, seed=12, scale=1 / math.sqrt(k))
         ops.use_tensor_cores = True
@@ -97,6 +98,57 @@ def test_tensor_core_and_cuda_core_products_agree(ops):
         ops.use_tensor_cores = True
         assert ops.launches == before + 2
         assert (fast - slow).abs().max() <= 1e-5, (m, n, k)
+    ops.check_status()
+
+
+def test_tensor_core_tiles_of_256_columns_with_every_epilogue(ops):
+    """Steps of thousands of tokens on a large matrix take tiles of 128 x 256: bias, GELU with a
+    bfloat16 store, the residual add and the QKV projection's page write must come out as from the
+    plain FMA kernel (the same bfloat16 inputs, sums in another order)."""
+    m, k = 4300, 200
+    n_head, n_kv, d, pt = 40, 20, 64, 16                    # 5120 columns: 34 x 20 tiles of 256
+    n = (n_head + 2 * n_kv) * d
+    x = randn(m, k, dtype=torch.bfloat16, seed=41)
+    w = randn(n, k, dtype=torch.bfloat16, seed=42, scale=1 / math.sqrt(k))
+    b = randn(n, seed=43)
+    res = randn(m, n, seed=44)
+    pages = -(-m // pt) + 2
+    slots = torch.randperm(pages * pt)[:m].to(torch.int32)
+    slots[7] = -1
+    slots = slots.cuda()
+
+    def run():
+        cache = SimpleNamespace(k_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                                v_pages=torch.zeros(pages, n_kv, pt, d, dtype=torch.bfloat16).cuda(),
+                                page_tokens=pt, writes=True)
+        r = res.clone()
+        ops.linear_residual(x, w, b, r)
+        return (ops.linear(x, w, b, "gelu_tanh", torch.bfloat16).float(), r,
+                ops.linear_qkv(x, w, b, n_head, n_kv, d, cache, slots, torch.bfloat16).float(), cache)
+
+    before = ops.launches
+    fast = run()
+    assert ops.launches == before + 3, "each call was expected to be one tensor-core launch"
+    ops.use_tensor_cores = False
+    try:
+        slow = run()
+    finally:
+        ops.use_tensor_cores = True
+    def one_bf16_step(a, c):
+        # results rounded to bfloat16 may land on neighbouring values where a sum lies at a rounding
+        # edge (a step is 2^-7 of the value's power of two), never further apart
+        return bool(((a - c).abs() <= 2.0 ** -7 * c.abs().clamp(min=2.0 ** -6)).all())
+
+    assert one_bf16_step(fast[0], slow[0])
+    assert (fast[1] - slow[1]).abs().max() <= 1e-5          # 32-bit sums in another order
+    assert one_bf16_step(fast[2], slow[2])
+    for a, c in ((fast[3].k_pages, slow[3].k_pages), (fast[3].v_pages, slow[3].v_pages)):
+        assert one_bf16_step(a.float(), c.float())
+    # keys of token i lie where its slot says, bit for bit what the projection returned
+    qkv = ops.linear_qkv(x, w, b, n_head, n_kv, d, fast[3], slots, torch.bfloat16)
+    tok = 100
+    s_ = int(slots[tok])
+    assert torch.equal(fast[3].k_pages[s_ // pt, :, s_ % pt].reshape(-1), qkv[tok, n_head * d: (n_head + n_kv) * d])
     ops.check_status()
 
 
