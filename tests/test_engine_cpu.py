@@ -32,6 +32,7 @@ def test_generate_matches_plain_greedy(which):
     ecfg = EngineConfig(block_size=8, num_blocks=64, max_batch_size=3, max_num_batched_tokens=16,
                         max_prefill_chunk=7, dtype="float32", device="cpu")
     cfg, tensors, engine = engine_for(which, ecfg)
+    assert engine.warm_up() == {"decode_graphs_captured": 0}      # nothing to capture where steps are not replayed
     prompts = [tokens_for(cfg, n, 40 + i) for i, n in enumerate([5, 1, 23, 12, 2, 17])]
     outs = engine.generate(prompts, SamplingParams(max_tokens=6, temperature=0.0))
     for prompt, out in zip(prompts, outs):
